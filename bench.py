@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Headline benchmark: training positions/sec of the NNUE step (fwd + bwd + AdamW+clip).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: the 768x16 -> 2048 pairwise multi-layer net (8 output buckets, 16 -> 32 -> 1) at a
+GLOBAL batch of 131072 seeded synthetic positions per step, sharded evenly over the N ranks
+(strong scaling); one all-reduce of the flat gradient buffer per step when N > 1.
+
+Prints ONE JSON line on rank 0.  `value` times the step with batches already resident in
+HBM; `e2e` times the public call sequence (upload from host arrays through pinned staging,
+step, loss read-back) with the next batch's packing and copy overlapped with the current
+step.  `roofline` covers the dominant feature-transformer kernel, `cpu_baseline` is the CPU
+oracle on this box's host cores.  `--impl reference` times that CPU oracle alone.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from bullet_b200 import config, synth  # noqa: E402
+from bullet_b200.configs import AdamWParams  # noqa: E402
+
+METRIC = "train positions/sec (fwd+bwd+AdamW)"
+UNIT = "positions/s"
+GLOBAL_BATCH = 131072
+WORKLOAD = "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), global batch 131072"
+N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_host_batches(cfg, n_local, rank, count):
+    from bullet_b200.net import featurise
+
+    out = []
+    for i in range(count):
+        rec = synth.records(cfg.game, n_local, seed=cfg.seed + 1000 * rank + i)
+        out.append(featurise(cfg.game, rec, cfg.desc))
+    return out
+
+
+def oracle_step_time(cfg, sample, steps, warmup):
+    """CPU oracle: fwd+bwd on `sample` positions and AdamW over every parameter, timed apart.
+
+    Returns (seconds per fwd+bwd of `sample` positions, seconds per AdamW, threads)."""
+    from oracle import Oracle
+
+    orc = Oracle("f32")
+    desc = dataclasses.replace(cfg.desc, max_batch=sample)
+    rec = synth.records(cfg.game, sample, seed=cfg.seed + 99)
+    batch = orc.map_batch(cfg.game, rec, desc)
+    w = orc.to_real(synth.init_weights(desc, seed=cfg.seed))
+    m, v = orc.zeros_like(desc), orc.zeros_like(desc)
+    t_fb, t_opt = [], []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        _, g, _ = orc.net_grad(desc, w, *batch)
+        t1 = time.perf_counter()
+        orc.net_update(desc, w, m, v, g, 1.0 / GLOBAL_BATCH, cfg.lr, AdamWParams())
+        t2 = time.perf_counter()
+        if i >= warmup:
+            t_fb.append(t1 - t0)
+            t_opt.append(t2 - t1)
+    return statistics.mean(t_fb), statistics.mean(t_opt), orc.threads()
+
+
+def cpu_positions_per_sec(t_fb, t_opt, sample):
+    # one workload step = fwd+bwd over the whole global batch + one AdamW
+    step_s = t_fb * (GLOBAL_BATCH / sample) + t_opt
+    return GLOBAL_BATCH / step_s, step_s
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    cfg = config(4)
+    sample = args.cpu_sample
+    t_fb, t_opt, threads = oracle_step_time(cfg, sample, max(1, args.steps), max(0, args.warmup))
+    value, step_s = cpu_positions_per_sec(t_fb, t_opt, sample)
+    what = (f"CPU oracle (C port of the reference interpreter's math, OpenMP): fwd+bwd timed on {sample} of the "
+            f"step's {GLOBAL_BATCH} positions and scaled linearly, AdamW over all {cfg.desc.n_params()} parameters "
+            f"timed in full; {args.steps} timed repeats")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "where": "host CPU cores, no GPU"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": what},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def ft_algorithmic_bytes(desc, batch):
+    """Algorithmic bytes of one launch of the FT forward / backward kernel on this batch.
+
+    forward : table rows gathered (one H-float row per active feature of each perspective)
+              + the u16 index slots + the activations written (x, and the pairwise crelu outputs
+              kept for the backward);
+    backward: table-gradient rows updated (one per active feature, read-modify-write counted once)
+              + the incoming gradient of both perspectives (2H floats) + the u16 index slots.
+    """
+    stm, nstm = batch[0], batch[1]
+    n = len(batch[3])
+    H = desc.ft_out
+    rows = int((stm >= 0).sum() + (nstm >= 0).sum())
+    idx = 2 * n * desc.nnz * 2
+    out_elems = n * desc.dense_in0 + (n * 2 * H if desc.pairwise else 0)
+    fwd = rows * H * 4 + idx + out_elems * 4
+    bwd = rows * H * 4 + n * 2 * H * 4 + idx
+    return fwd, bwd, rows
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: bullet_b200 has no CPU fallback "
+                         "(use --impl reference for the CPU oracle)")
+    import torch.distributed as dist
+
+    from bullet_b200.net import Net
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = config(4)
+    if GLOBAL_BATCH % world:
+        raise SystemExit("the global batch must divide evenly over the ranks")
+    n_local = GLOBAL_BATCH // world
+    desc = dataclasses.replace(cfg.desc, max_batch=n_local)
+    cfg = dataclasses.replace(cfg, desc=desc)
+    batches = make_host_batches(cfg, n_local, rank, N_DISTINCT)
+
+    stream = torch.cuda.Stream()
+    net = Net(desc, device=local_rank, stream=stream.cuda_stream)
+    if args.ft_mode:
+        net.set_option("ft_mode", args.ft_mode)
+    net.load_weights(synth.init_weights(desc, seed=cfg.seed))
+    gptr, gcount = net.grad_buffer()
+
+    class _Dev:
+        __cuda_array_interface__ = {"shape": (gcount,), "typestr": "<f4", "data": (gptr, False), "version": 2}
+
+    grad = torch.as_tensor(_Dev(), device=torch.device("cuda", local_rank)) if world > 1 else None
+    lr, gf = cfg.lr, 1.0 / GLOBAL_BATCH
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def one_step(slot):
+        net.backward(slot)
+        if world > 1:
+            dist.all_reduce(grad)
+        net.update(lr, gf)
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.cuda.stream(stream):
+        # ---------------------------------------------- device-resident inputs ("value")
+        for s in range(N_DISTINCT):
+            net.upload(s, *batches[s])
+        net.sync()
+        for i in range(args.warmup):
+            one_step(i % N_DISTINCT)
+        barrier()
+        try:
+            net.timings()  # drop the warm-up steps from the per-kernel averages
+        except Exception:
+            pass
+        launches0 = net.stat("launches")
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for i in range(args.steps):
+            one_step(i % N_DISTINCT)
+        ev1.record(stream)
+        barrier()
+        dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
+        launches = net.stat("launches") - launches0
+        phase = net.timings()
+        loss_resident = net.loss() if world == 1 else None
+
+        # ------------------------------------------------ end to end through the public API
+        net.upload(0, *batches[0])
+        for i in range(max(args.warmup, 1)):
+            one_step(i % N_DISTINCT)
+            net.upload((i + 1) % N_DISTINCT, *batches[(i + 1) % N_DISTINCT])
+            net.loss()
+        h2d0 = net.stat("h2d_bytes")
+        first = max(args.warmup, 1) % N_DISTINCT
+        barrier()
+        t0 = time.perf_counter()
+        last_loss = None
+        for i in range(args.steps):
+            slot = (first + i) % N_DISTINCT
+            one_step(slot)                                              # enqueue only
+            nxt = (slot + 1) % N_DISTINCT
+            net.upload(nxt, *batches[nxt])                               # pack + H2D of the next batch
+            last_loss = net.loss()                                       # D2H read of this step's loss
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        h2d_per_step = (net.stat("h2d_bytes") - h2d0) // max(args.steps, 1)
+        clocks = sampler.stop() if rank == 0 else None
+
+    value = GLOBAL_BATCH * args.steps / (dev_ms * 1e-3)
+    e2e_value = GLOBAL_BATCH * args.steps / e2e_s
+    fwd_b, bwd_b, rows = ft_algorithmic_bytes(desc, batches[0])
+    peak, peak_kind = measured_peak_gbs()
+    kernels = {
+        "ft_forward": {"ms": phase["ft_forward"], "algorithmic_bytes": fwd_b},
+        "ft_backward": {"ms": phase["ft_backward"], "algorithmic_bytes": bwd_b},
+    }
+    for k in kernels.values():
+        k["achieved_gbs"] = k["algorithmic_bytes"] / (k["ms"] * 1e-3) / 1e9 if k["ms"] > 0 else None
+        k["frac_of_hbm_peak"] = k["achieved_gbs"] / peak if k["achieved_gbs"] else None
+    dom = max(kernels, key=lambda n: kernels[n]["ms"])
+    traffic = None
+    try:  # per-launch DRAM bytes of the dominant kernel from the committed ncu summary, if present
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            traffic = json.load(f).get(dom, {}).get(f"n{n_local}")
+    except Exception:
+        pass
+    roofline = {
+        "bound": "hbm", "kernel": dom, "achieved": kernels[dom]["achieved_gbs"], "peak": peak, "unit": "GB/s",
+        "frac": kernels[dom]["frac_of_hbm_peak"], "traffic": traffic, "peak_kind": f"of {peak_kind}",
+        "algorithmic_bytes_per_launch": kernels[dom]["algorithmic_bytes"], "launch_ms": kernels[dom]["ms"],
+        "note": "algorithmic bytes count every gathered/updated table row once per active feature; the tiled "
+                "kernels serve those rows from shared memory, so achieved can exceed the HBM peak",
+    }
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        t_fb, t_opt, threads = oracle_step_time(cfg, args.cpu_sample, 2, 1)
+        cpu_val, _ = cpu_positions_per_sec(t_fb, t_opt, args.cpu_sample)
+        cpu = {"value": cpu_val, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"CPU oracle: fwd+bwd timed on {args.cpu_sample} of the step's {GLOBAL_BATCH} positions "
+                         f"(2 repeats after 1 warm-up) and scaled linearly, AdamW over all {desc.n_params()} "
+                         "parameters timed in full"}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
+                   "parallelism": f"dp{world}", "ft_kernels": "tiled" if net.stat("ft_tiled") else "gather",
+                   "l2": f"inputs larger than L2: {N_DISTINCT} distinct batches cycled, per-step activations "
+                         f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
+                   "active_features_per_position": rows / n_local},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d_per_step) * world,
+                "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_s * 1e3 / args.steps,
+                "loss_per_position": None if last_loss is None else last_loss / GLOBAL_BATCH},
+        "gpu_launches": int(launches),
+        "phases_ms": {k: round(v, 4) for k, v in phase.items() if k != "steps"},
+        "kernels": kernels, "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+        "loss_per_position": None if loss_resident is None else loss_resident / GLOBAL_BATCH,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ft-mode", type=int, default=0, help="0 auto, 1 gather kernels, 2 tiled kernels")
+    ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

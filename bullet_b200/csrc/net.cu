@@ -1,0 +1,848 @@
+// b200_net: device state, staging slots and the fixed step schedule behind the C ABI.
+//
+// Replaces, for the NNUE training step only, what the reference assembles at run time from
+// generated CUDA text: Function::new/prealloc/execute (crates/gpu/src/function.rs:73-280),
+// the per-weight AdamW launches (crates/trainer/src/optimiser/adam.rs:217-291) and the
+// batch copies of PreparedBatchHost (crates/trainer/src/run/dataloader.rs:41-61).  All
+// device memory is allocated once in b200_net_create; a step only enqueues kernels.
+//
+// HBM layout
+//   P, G, M, V   flat fp32 buffers holding every tensor in name order (l0b, l0f, l0w, l1b,
+//                l1w, ...), each tensor starting on a 256-byte boundary.  G carries one
+//                extra element at its end: the summed loss, so a data-parallel host moves
+//                gradients and loss with a single all-reduce.
+//   table        l0w + tiled l0f (only with a factoriser; otherwise an alias of l0w in P)
+//   x, u, dx     activations kept between forward and backward, position-major
+//   slots        per staging slot one pinned host block and one device block holding the
+//                packed u16 index lists, buckets, targets and the two visiting orders
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/bullet_b200.h"
+#include "common.h"
+#include "kernels_dense.cuh"
+#include "kernels_ft.cuh"
+#include "kernels_opt.cuh"
+
+#define CK(call)                                                                                          \
+    do {                                                                                                  \
+        cudaError_t e_ = (call);                                                                          \
+        if (e_ != cudaSuccess)                                                                            \
+            return b200::fail(B200_ERR_CUDA, "%s failed: %s (%d) at %s:%d", #call, cudaGetErrorString(e_), \
+                              (int)e_, __FILE__, __LINE__);                                               \
+    } while (0)
+
+// after every kernel launch: surface a launch error, count the launch
+#define LAUNCHED(net)            \
+    do {                         \
+        CK(cudaGetLastError());  \
+        (net)->launches++;       \
+    } while (0)
+
+namespace {
+
+constexpr int kSmCount = 148;
+constexpr int kTargetCtas = 4 * kSmCount;  // two resident CTAs per SM, two waves
+constexpr int64_t kAlignFloats = 64;       // 256-byte tensor alignment in the flat buffers
+
+struct Tensor {
+    std::string name;
+    int64_t n = 0, off = 0;
+    b200_adamw_params hp{0.01f, 0.9f, 0.999f, -1.98f, 1.98f};
+};
+
+struct Slot {
+    char* d_blob = nullptr;
+    char* h_blob = nullptr;
+    size_t capacity = 0;
+    int n = 0;
+    size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
+           bytes = 0;
+    cudaEvent_t ready = nullptr, consumed = nullptr;
+    bool has_ready = false, has_consumed = false;
+    template <class T>
+    T* dev(size_t off) const { return reinterpret_cast<T*>(d_blob + off); }
+    template <class T>
+    T* host(size_t off) const { return reinterpret_cast<T*>(h_blob + off); }
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct b200_net {
+    int device = 0;
+    cudaStream_t stream = nullptr, copy_stream = nullptr;
+    bool own_stream = false;
+    b200_net_desc d{};
+    std::vector<Tensor> tensors;
+    int64_t n_flat = 0;
+    float *P = nullptr, *G = nullptr, *M = nullptr, *V = nullptr, *table = nullptr;
+    float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr;
+    float* dz[3] = {nullptr, nullptr, nullptr};
+    int* status = nullptr;
+    int* h_status = nullptr;
+    float* h_loss = nullptr;
+    cudaEvent_t loss_ev = nullptr;
+    bool loss_pending = false;
+    Slot slots[B200_NUM_SLOTS];
+    int ft_mode = B200_FT_AUTO;
+    bool tiled_ok = false, table_dirty = true, have_backward = false;
+    int nblocks = 1, nslabs = 1;
+    int last_n = 0;
+    // per-step CUDA events on the compute stream, kept for the last kTimingRing steps
+    static constexpr int kTimingRing = 256, kTimingEvents = 7;
+    cudaEvent_t tev[kTimingRing][kTimingEvents] = {};
+    int64_t steps_begun = 0, steps_done = 0, timing_origin = 0;
+    bool step_open = false;
+    int64_t launches = 0, h2d_bytes = 0;
+    std::vector<void*> allocations;
+
+    int D1() const { return d.pairwise ? d.ft_out : 2 * d.ft_out; }
+    int dense_in(int l) const { return l == 0 ? D1() : d.dense_out[l - 1]; }
+    Tensor* find(const char* name) {
+        for (auto& t : tensors)
+            if (t.name == name) return &t;
+        return nullptr;
+    }
+    bool use_tiled() const { return ft_mode == B200_FT_TILED || (ft_mode == B200_FT_AUTO && tiled_ok); }
+};
+
+namespace {
+
+int set_device(const b200_net* net) {
+    CK(cudaSetDevice(net->device));
+    return 0;
+}
+
+template <class T>
+int dev_alloc(b200_net* net, T** p, size_t count) {
+    void* raw = nullptr;
+    CK(cudaMalloc(&raw, std::max<size_t>(count, 1) * sizeof(T)));
+    net->allocations.push_back(raw);
+    *p = static_cast<T*>(raw);
+    return 0;
+}
+
+bool supported_m(int m) { return m == 1 || m == 2 || m == 4 || m == 8 || m == 16 || m == 32; }
+
+int validate(const b200_net_desc& d) {
+    if (d.n_inputs < 1 || d.n_inputs > 65534) return b200::fail(B200_ERR_UNSUPPORTED, "n_inputs must be in [1, 65534]");
+    if (d.nnz < 1 || d.nnz > 64) return b200::fail(B200_ERR_UNSUPPORTED, "nnz must be in [1, 64]");
+    if (d.ft_out < 8 || d.ft_out % 8) return b200::fail(B200_ERR_UNSUPPORTED, "ft_out must be a positive multiple of 8");
+    if (d.ft_act != B200_ACT_CRELU && d.ft_act != B200_ACT_SCRELU)
+        return b200::fail(B200_ERR_UNSUPPORTED, "ft_act must be CReLU or SCReLU");
+    if (d.pairwise && d.ft_act != B200_ACT_CRELU) return b200::fail(B200_ERR_UNSUPPORTED, "pairwise_mul needs CReLU");
+    if (d.factoriser_rows < 0 || (d.factoriser_rows && d.n_inputs % d.factoriser_rows))
+        return b200::fail(B200_ERR_ARG, "factoriser_rows must tile n_inputs");
+    if (d.n_out_buckets < 1 || d.n_out_buckets > 64) return b200::fail(B200_ERR_UNSUPPORTED, "1..64 output buckets");
+    if (d.n_dense < 1 || d.n_dense > 3) return b200::fail(B200_ERR_UNSUPPORTED, "one to three dense layers");
+    for (int l = 0; l < d.n_dense; l++) {
+        if (d.dense_out[l] < 1 || d.dense_out[l] > 32 || (l == 0 && !supported_m(d.dense_out[l])))
+            return b200::fail(B200_ERR_UNSUPPORTED, "dense layer %d: rows per bucket must be 1,2,4,8,16 or 32", l + 1);
+        if (d.dense_act[l] < 0 || d.dense_act[l] > 2) return b200::fail(B200_ERR_ARG, "dense layer %d: bad activation", l + 1);
+    }
+    for (int l = 1; l < d.n_dense; l++)
+        if (!supported_m(d.dense_out[l])) return b200::fail(B200_ERR_UNSUPPORTED, "dense layer %d: rows per bucket must be a power of two <= 32", l + 1);
+    if (d.dense_out[d.n_dense - 1] != 1 || d.dense_act[d.n_dense - 1] != B200_ACT_NONE)
+        return b200::fail(B200_ERR_UNSUPPORTED, "the last dense layer must have one row per bucket and no activation");
+    if (d.max_batch < 1) return b200::fail(B200_ERR_ARG, "max_batch must be positive");
+    if (d.ft_block_rows < 0) return b200::fail(B200_ERR_ARG, "ft_block_rows must not be negative");
+    return 0;
+}
+
+void slot_layout(const b200_net* net, Slot& s, int n) {
+    const b200_net_desc& d = net->d;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = off;
+        off = align_up(off + bytes, 256);
+        return at;
+    };
+    s.off_stm = take((size_t)n * d.nnz * 2);
+    s.off_nstm = take((size_t)n * d.nnz * 2);
+    s.off_buckets = take((size_t)n * 4);
+    s.off_targets = take((size_t)n * 4);
+    s.off_order = take((size_t)n * 4);
+    s.off_pairs = take((size_t)n * 8);
+    s.off_blocks = take((size_t)(net->nblocks + 1) * 4);
+    s.bytes = off;
+}
+
+template <bool PW>
+int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
+    if (tiled) {
+        const size_t smem = (size_t)t.block_rows * 32 * sizeof(float);
+        b200::ft_forward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nchunks, 512, smem, net->stream>>>(a, t);
+    } else {
+        const int unit = PW ? a.H / 2 : a.H;
+        dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
+        b200::ft_forward_gather_kernel<PW><<<grid, 256, 0, net->stream>>>(a, 64);
+    }
+    LAUNCHED(net);
+    return 0;
+}
+
+template <bool PW>
+int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
+    if (tiled) {
+        const size_t smem = (size_t)t.block_rows * 32 * sizeof(float);
+        b200::ft_backward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nchunks, 512, smem, net->stream>>>(a, t);
+    } else {
+        const int unit = PW ? a.H / 2 : a.H;
+        dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
+        b200::ft_backward_gather_kernel<PW><<<grid, 256, 0, net->stream>>>(a, 64);
+    }
+    LAUNCHED(net);
+    return 0;
+}
+
+#define DISPATCH_M(m, ...)                                                    \
+    switch (m) {                                                              \
+        case 1: { constexpr int MM = 1; __VA_ARGS__; } break;                 \
+        case 2: { constexpr int MM = 2; __VA_ARGS__; } break;                 \
+        case 4: { constexpr int MM = 4; __VA_ARGS__; } break;                 \
+        case 8: { constexpr int MM = 8; __VA_ARGS__; } break;                 \
+        case 16: { constexpr int MM = 16; __VA_ARGS__; } break;               \
+        case 32: { constexpr int MM = 32; __VA_ARGS__; } break;               \
+        default: return b200::fail(B200_ERR_UNSUPPORTED, "rows per bucket %d", m); \
+    }
+
+int tiles_for(const b200_net* net, int n) {
+    // position chunks per (block, slab) so that the grid fills the machine; each chunk
+    // should still amortise its tile load over at least ~64 (position, perspective) pairs
+    const int base = net->nblocks * net->nslabs;
+    int chunks = (kTargetCtas + base - 1) / base;
+    const int most = std::max(1, (2 * n) / (64 * net->nblocks));
+    return std::max(1, std::min(chunks, most));
+}
+
+b200::FtArgs ft_args(b200_net* net, const Slot& s) {
+    b200::FtArgs a{};
+    const b200_net_desc& d = net->d;
+    a.table = net->table;
+    a.bias = net->P + net->find("l0b")->off;
+    a.idx_stm = s.dev<uint16_t>(s.off_stm);
+    a.idx_nstm = s.dev<uint16_t>(s.off_nstm);
+    a.n = s.n;
+    a.nnz = d.nnz;
+    a.H = d.ft_out;
+    a.n_inputs = d.n_inputs;
+    a.act = d.ft_act;
+    a.x = net->x;
+    a.u = net->u;
+    a.dx = net->dx;
+    a.g_table = net->G + net->find("l0w")->off;
+    a.g_bias = net->G + net->find("l0b")->off;
+    return a;
+}
+
+b200::TileArgs tile_args(b200_net* net, const Slot& s, int nchunks) {
+    b200::TileArgs t{};
+    t.block_rows = net->d.ft_block_rows;
+    t.nslabs = net->nslabs;
+    t.nchunks = nchunks;
+    t.pair_order = net->nblocks > 1 ? s.dev<int>(s.off_pairs) : nullptr;
+    t.block_begin = s.dev<int>(s.off_blocks);
+    t.status = net->status;
+    return t;
+}
+
+b200::DenseArgs dense_args(b200_net* net, const Slot& s, bool want_grad) {
+    b200::DenseArgs a{};
+    const b200_net_desc& d = net->d;
+    a.x = net->x;
+    a.buckets = s.dev<int>(s.off_buckets);
+    a.targets = s.dev<float>(s.off_targets);
+    a.n = s.n;
+    a.K1 = net->D1();
+    a.O = d.n_out_buckets;
+    a.n_dense = d.n_dense;
+    for (int l = 0; l < d.n_dense; l++) {
+        a.M[l] = d.dense_out[l];
+        a.act[l] = d.dense_act[l];
+        char name[8];
+        snprintf(name, sizeof name, "l%dw", l + 1);
+        a.W[l] = net->P + net->find(name)->off;
+        snprintf(name, sizeof name, "l%db", l + 1);
+        a.B[l] = net->P + net->find(name)->off;
+        a.dz[l] = net->dz[l];
+    }
+    a.a1 = net->a1;
+    a.a2 = net->a2;
+    a.out = net->out;
+    a.loss = net->G + net->n_flat;
+    a.want_grad = want_grad ? 1 : 0;
+    return a;
+}
+
+int refresh_table(b200_net* net) {
+    if (!net->table_dirty) return 0;
+    if (net->d.factoriser_rows) {
+        const Tensor* w = net->find("l0w");
+        const Tensor* f = net->find("l0f");
+        const size_t n4 = (size_t)w->n / 4, block4 = (size_t)f->n / 4;
+        b200::factoriser_merge_kernel<<<kSmCount * 8, 256, 0, net->stream>>>(
+            reinterpret_cast<const float4*>(net->P + w->off), reinterpret_cast<const float4*>(net->P + f->off),
+            reinterpret_cast<float4*>(net->table), n4, block4);
+        LAUNCHED(net);
+    }
+    net->table_dirty = false;
+    return 0;
+}
+
+int check_slot(b200_net* net, int slot, const char* who) {
+    if (!net) return b200::fail(B200_ERR_ARG, "%s: null net", who);
+    if (slot < 0 || slot >= B200_NUM_SLOTS) return b200::fail(B200_ERR_ARG, "%s: slot %d out of range", who, slot);
+    if (net->slots[slot].n < 1 || !net->slots[slot].has_ready)
+        return b200::fail(B200_ERR_STATE, "%s: slot %d holds no batch", who, slot);
+    return 0;
+}
+
+int forward_part(b200_net* net, Slot& s, bool want_grad) {
+    const b200_net_desc& d = net->d;
+    const bool tiled = net->use_tiled();
+    b200::FtArgs fa = ft_args(net, s);
+    b200::TileArgs ta = tile_args(net, s, tiled ? tiles_for(net, s.n) : 1);
+    int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled) : launch_ft_forward<false>(net, fa, ta, tiled);
+    if (rc) return rc;
+    if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
+    b200::DenseArgs da = dense_args(net, s, want_grad);
+    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<(s.n + 7) / 8, 256, 0, net->stream>>>(da));
+    LAUNCHED(net);
+    return 0;
+}
+
+int launch_wgrad(b200_net* net, const Slot& s, int layer) {
+    const b200_net_desc& d = net->d;
+    b200::WgradArgs w{};
+    w.X = layer == 0 ? net->x : (layer == 1 ? net->a1 : net->a2);
+    w.dY = net->dz[layer];
+    w.order = d.n_out_buckets > 1 ? s.dev<int>(s.off_order) : nullptr;
+    w.buckets = s.dev<int>(s.off_buckets);
+    w.n = s.n;
+    w.K = net->dense_in(layer);
+    w.O = d.n_out_buckets;
+    char name[8];
+    snprintf(name, sizeof name, "l%dw", layer + 1);
+    w.gW = net->G + net->find(name)->off;
+    snprintf(name, sizeof name, "l%db", layer + 1);
+    w.gB = net->G + net->find(name)->off;
+    const int threads = w.K + 1 >= 256 ? 256 : ((w.K + 1 + 31) / 32) * 32;
+    const int gx = (w.K + 1 + threads - 1) / threads;
+    int chunks = std::max(1, std::min((s.n + 63) / 64, kTargetCtas / gx));
+    w.chunk_len = ((s.n + chunks - 1) / chunks + 63) / 64 * 64;
+    chunks = (s.n + w.chunk_len - 1) / w.chunk_len;
+    dim3 grid(gx, chunks);
+    DISPATCH_M(d.dense_out[layer], b200::dense_wgrad_kernel<MM><<<grid, threads, 0, net->stream>>>(w));
+    LAUNCHED(net);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* b200_last_error(void) { return b200::error_buffer(); }
+int b200_version(void) { return 1; }
+
+int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_net** out) {
+    if (!desc || !out) return b200::fail(B200_ERR_ARG, "net_create: null argument");
+    *out = nullptr;
+    if (int rc = validate(*desc)) return rc;
+    int count = 0;
+    CK(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return b200::fail(B200_ERR_CUDA, "net_create: no CUDA device %d (%d visible)", device, count);
+    b200_net* net = new b200_net();
+    net->device = device;
+    net->d = *desc;
+    const b200_net_desc& d = net->d;
+    auto bail = [&](int rc) {
+        b200_net_destroy(net);
+        return rc;
+    };
+    if (int rc = set_device(net)) return bail(rc);
+    if (stream) {
+        net->stream = static_cast<cudaStream_t>(stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&net->stream, cudaStreamNonBlocking) != cudaSuccess)
+            return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create a stream"));
+        net->own_stream = true;
+    }
+    if (cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the copy stream"));
+
+    // flat layout, tensors in name order
+    auto add = [&](const char* name, int64_t n) {
+        Tensor t;
+        t.name = name;
+        t.n = n;
+        net->tensors.push_back(t);
+    };
+    add("l0b", d.ft_out);
+    if (d.factoriser_rows) add("l0f", (int64_t)d.factoriser_rows * d.ft_out);
+    add("l0w", (int64_t)d.n_inputs * d.ft_out);
+    for (int l = 0; l < d.n_dense; l++) {
+        char name[8];
+        const int64_t rows = (int64_t)d.n_out_buckets * d.dense_out[l];
+        snprintf(name, sizeof name, "l%db", l + 1);
+        add(name, rows);
+        snprintf(name, sizeof name, "l%dw", l + 1);
+        add(name, rows * net->dense_in(l));
+    }
+    int64_t off = 0;
+    for (auto& t : net->tensors) {
+        t.off = off;
+        off += (t.n + kAlignFloats - 1) / kAlignFloats * kAlignFloats;
+    }
+    net->n_flat = off;
+
+    net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % 32 == 0 &&
+                    (size_t)d.ft_block_rows * 128 <= 200 * 1024;
+    net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
+    net->nslabs = d.ft_out / 32;
+
+    const size_t B = d.max_batch;
+    int rc = 0;
+    rc = rc ? rc : dev_alloc(net, &net->P, net->n_flat);
+    rc = rc ? rc : dev_alloc(net, &net->G, net->n_flat + kAlignFloats);
+    rc = rc ? rc : dev_alloc(net, &net->M, net->n_flat);
+    rc = rc ? rc : dev_alloc(net, &net->V, net->n_flat);
+    if (d.factoriser_rows) rc = rc ? rc : dev_alloc(net, &net->table, (size_t)d.n_inputs * d.ft_out);
+    rc = rc ? rc : dev_alloc(net, &net->x, B * net->D1());
+    if (d.pairwise) rc = rc ? rc : dev_alloc(net, &net->u, B * 2 * d.ft_out);
+    rc = rc ? rc : dev_alloc(net, &net->dx, B * net->D1());
+    rc = rc ? rc : dev_alloc(net, &net->a1, B * d.dense_out[0]);
+    rc = rc ? rc : dev_alloc(net, &net->a2, B * 32);
+    for (int l = 0; l < 3; l++) rc = rc ? rc : dev_alloc(net, &net->dz[l], B * 32);
+    rc = rc ? rc : dev_alloc(net, &net->out, B);
+    rc = rc ? rc : dev_alloc(net, &net->status, 1);
+    if (rc) return bail(rc);
+    if (!d.factoriser_rows) net->table = net->P + net->find("l0w")->off;
+    cudaMemsetAsync(net->P, 0, net->n_flat * 4, net->stream);
+    cudaMemsetAsync(net->G, 0, (net->n_flat + kAlignFloats) * 4, net->stream);
+    cudaMemsetAsync(net->M, 0, net->n_flat * 4, net->stream);
+    cudaMemsetAsync(net->V, 0, net->n_flat * 4, net->stream);
+    cudaMemsetAsync(net->status, 0, 4, net->stream);
+
+    for (auto& s : net->slots) {
+        slot_layout(net, s, d.max_batch);
+        s.capacity = s.bytes;
+        void* raw = nullptr;
+        if (cudaMalloc(&raw, s.capacity) != cudaSuccess) return bail(b200::fail(B200_ERR_CUDA, "net_create: slot allocation failed"));
+        s.d_blob = static_cast<char*>(raw);
+        if (cudaHostAlloc(&raw, s.capacity, cudaHostAllocDefault) != cudaSuccess)
+            return bail(b200::fail(B200_ERR_CUDA, "net_create: pinned slot allocation failed"));
+        s.h_blob = static_cast<char*>(raw);
+        cudaEventCreateWithFlags(&s.ready, cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&s.consumed, cudaEventDisableTiming);
+        s.n = 0;
+    }
+    void* raw = nullptr;
+    if (cudaHostAlloc(&raw, 64, cudaHostAllocDefault) != cudaSuccess) return bail(b200::fail(B200_ERR_CUDA, "net_create: pinned alloc failed"));
+    net->h_loss = static_cast<float*>(raw);
+    net->h_status = reinterpret_cast<int*>(net->h_loss + 8);
+    cudaEventCreateWithFlags(&net->loss_ev, cudaEventDisableTiming);
+    for (auto& ring : net->tev)
+        for (auto& e : ring) cudaEventCreate(&e);
+
+    if (net->tiled_ok) {
+        const int smem = d.ft_block_rows * 128;
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    }
+    CK(cudaStreamSynchronize(net->stream));
+    CK(cudaGetLastError());
+    *out = net;
+    return 0;
+}
+
+int b200_net_destroy(b200_net* net) {
+    if (!net) return 0;
+    cudaSetDevice(net->device);
+    if (net->stream) cudaStreamSynchronize(net->stream);
+    if (net->copy_stream) cudaStreamSynchronize(net->copy_stream);
+    for (void* p : net->allocations) cudaFree(p);
+    for (auto& s : net->slots) {
+        if (s.d_blob) cudaFree(s.d_blob);
+        if (s.h_blob) cudaFreeHost(s.h_blob);
+        if (s.ready) cudaEventDestroy(s.ready);
+        if (s.consumed) cudaEventDestroy(s.consumed);
+    }
+    if (net->h_loss) cudaFreeHost(net->h_loss);
+    if (net->loss_ev) cudaEventDestroy(net->loss_ev);
+    for (auto& ring : net->tev)
+        for (auto& e : ring)
+            if (e) cudaEventDestroy(e);
+    if (net->own_stream && net->stream) cudaStreamDestroy(net->stream);
+    if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+    delete net;
+    return 0;
+}
+
+int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
+    if (!net || !key) return b200::fail(B200_ERR_ARG, "set_option: null argument");
+    if (!strcmp(key, "ft_mode")) {
+        if (value < B200_FT_AUTO || value > B200_FT_TILED) return b200::fail(B200_ERR_ARG, "ft_mode %lld unknown", (long long)value);
+        if (value == B200_FT_TILED && !net->tiled_ok)
+            return b200::fail(B200_ERR_UNSUPPORTED,
+                              "tiled feature-transformer kernels need ft_block_rows > 0 dividing n_inputs, at most "
+                              "1600 rows per block, and ft_out a multiple of 32");
+        net->ft_mode = (int)value;
+        return 0;
+    }
+    return b200::fail(B200_ERR_ARG, "set_option: unknown key '%s'", key);
+}
+
+int b200_net_tensor_size(b200_net* net, const char* name, int64_t* n) {
+    if (!net || !name || !n) return b200::fail(B200_ERR_ARG, "tensor_size: null argument");
+    const Tensor* t = net->find(name);
+    if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    *n = t->n;
+    return 0;
+}
+
+static float* kind_base(b200_net* net, int kind) {
+    switch (kind) {
+        case B200_KIND_WEIGHT: return net->P;
+        case B200_KIND_MOMENTUM: return net->M;
+        case B200_KIND_VELOCITY: return net->V;
+        case B200_KIND_GRAD: return net->G;
+        default: return nullptr;
+    }
+}
+
+int b200_net_set_tensor(b200_net* net, const char* name, int kind, const float* host, int64_t n) {
+    if (!net || !name || !host) return b200::fail(B200_ERR_ARG, "set_tensor: null argument");
+    const Tensor* t = net->find(name);
+    if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    if (n != t->n) return b200::fail(B200_ERR_ARG, "tensor '%s' holds %lld values, %lld given", name, (long long)t->n, (long long)n);
+    if (kind < B200_KIND_WEIGHT || kind > B200_KIND_VELOCITY) return b200::fail(B200_ERR_ARG, "set_tensor: kind %d is not writable", kind);
+    if (int rc = set_device(net)) return rc;
+    CK(cudaStreamSynchronize(net->stream));
+    CK(cudaMemcpy(kind_base(net, kind) + t->off, host, n * sizeof(float), cudaMemcpyHostToDevice));
+    if (kind == B200_KIND_WEIGHT) net->table_dirty = true;
+    return 0;
+}
+
+int b200_net_get_tensor(b200_net* net, const char* name, int kind, float* host, int64_t n) {
+    if (!net || !name || !host) return b200::fail(B200_ERR_ARG, "get_tensor: null argument");
+    const Tensor* t = net->find(name);
+    if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    if (n != t->n) return b200::fail(B200_ERR_ARG, "tensor '%s' holds %lld values, %lld asked", name, (long long)t->n, (long long)n);
+    float* base = kind_base(net, kind);
+    if (!base) return b200::fail(B200_ERR_ARG, "get_tensor: unknown kind %d", kind);
+    if (int rc = set_device(net)) return rc;
+    CK(cudaStreamSynchronize(net->stream));
+    CK(cudaMemcpy(host, base + t->off, n * sizeof(float), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int b200_net_set_adamw(b200_net* net, const char* name, const b200_adamw_params* params) {
+    if (!net || !params) return b200::fail(B200_ERR_ARG, "set_adamw: null argument");
+    if (!(params->min_weight <= params->max_weight)) return b200::fail(B200_ERR_ARG, "set_adamw: min_weight > max_weight");
+    if (!name) {
+        for (auto& t : net->tensors) t.hp = *params;
+        return 0;
+    }
+    Tensor* t = net->find(name);
+    if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    t->hp = *params;
+    return 0;
+}
+
+int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t* nstm, const int32_t* buckets,
+                      const float* targets, int32_t n) {
+    if (!net || !stm || !nstm || !targets) return b200::fail(B200_ERR_ARG, "batch_upload: null argument");
+    if (slot < 0 || slot >= B200_NUM_SLOTS) return b200::fail(B200_ERR_ARG, "batch_upload: slot %d out of range", slot);
+    const b200_net_desc& d = net->d;
+    if (n < 1 || n > d.max_batch) return b200::fail(B200_ERR_ARG, "batch_upload: %d positions, capacity is %d", n, d.max_batch);
+    if (d.n_out_buckets > 1 && !buckets) return b200::fail(B200_ERR_ARG, "batch_upload: this network needs output buckets");
+    if (int rc = set_device(net)) return rc;
+    Slot& s = net->slots[slot];
+    // the pinned block is free once its last copy has landed and the last step that read
+    // the device block has finished
+    if (s.has_ready) CK(cudaEventSynchronize(s.ready));
+    if (s.has_consumed) CK(cudaEventSynchronize(s.consumed));
+    slot_layout(net, s, n);
+    s.n = 0;
+    const int64_t count = (int64_t)n * d.nnz;
+    uint16_t* h_stm = s.host<uint16_t>(s.off_stm);
+    uint16_t* h_nstm = s.host<uint16_t>(s.off_nstm);
+    const uint32_t limit = (uint32_t)d.n_inputs;
+#pragma omp parallel for schedule(static) if (count > 200000)
+    for (int64_t i = 0; i < count; i++) {
+        const uint32_t a = (uint32_t)stm[i], b = (uint32_t)nstm[i];
+        h_stm[i] = a < limit ? (uint16_t)a : (uint16_t)0xFFFFu;
+        h_nstm[i] = b < limit ? (uint16_t)b : (uint16_t)0xFFFFu;
+    }
+    int* h_buckets = s.host<int>(s.off_buckets);
+    const int O = d.n_out_buckets;
+    if (buckets) {
+        for (int i = 0; i < n; i++) {
+            if ((unsigned)buckets[i] >= (unsigned)O)
+                return b200::fail(B200_ERR_DATA, "batch_upload: position %d has output bucket %d, network has %d", i, buckets[i], O);
+            h_buckets[i] = buckets[i];
+        }
+    } else {
+        memset(h_buckets, 0, (size_t)n * 4);
+    }
+    memcpy(s.host<float>(s.off_targets), targets, (size_t)n * 4);
+    // visiting order of the dense weight-gradient kernel: positions grouped by output bucket
+    int* h_order = s.host<int>(s.off_order);
+    {
+        std::vector<int> begin(O + 1, 0);
+        for (int i = 0; i < n; i++) begin[h_buckets[i] + 1]++;
+        for (int k = 0; k < O; k++) begin[k + 1] += begin[k];
+        for (int i = 0; i < n; i++) h_order[begin[h_buckets[i]]++] = i;
+    }
+    // visiting order of the tiled feature-transformer kernels: (position, perspective)
+    // pairs grouped by the table row block their features live in
+    int* h_pairs = s.host<int>(s.off_pairs);
+    int* h_blocks = s.host<int>(s.off_blocks);
+    const int nb = net->nblocks;
+    if (nb > 1) {
+        const int R = d.ft_block_rows, nnz = d.nnz;
+        std::vector<int> begin(nb + 1, 0);
+        std::vector<uint16_t> blk((size_t)2 * n);
+#pragma omp parallel for schedule(static) if (n > 8192)
+        for (int i = 0; i < n; i++) {
+            for (int p = 0; p < 2; p++) {
+                const uint16_t* list = (p ? h_nstm : h_stm) + (size_t)i * nnz;
+                int b = 0;
+                for (int k = 0; k < nnz; k++)
+                    if (list[k] != 0xFFFFu) {
+                        b = list[k] / R;
+                        break;
+                    }
+                blk[(size_t)2 * i + p] = (uint16_t)b;
+            }
+        }
+        for (size_t i = 0; i < blk.size(); i++) begin[blk[i] + 1]++;
+        for (int k = 0; k < nb; k++) begin[k + 1] += begin[k];
+        memcpy(h_blocks, begin.data(), (size_t)(nb + 1) * 4);
+        for (size_t i = 0; i < blk.size(); i++) h_pairs[begin[blk[i]]++] = (int)i;
+    } else {
+        h_blocks[0] = 0;
+        h_blocks[1] = 2 * n;
+    }
+    CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
+    net->h2d_bytes += (int64_t)s.bytes;
+    CK(cudaEventRecord(s.ready, net->copy_stream));
+    s.has_ready = true;
+    s.has_consumed = false;
+    s.n = n;
+    return 0;
+}
+
+int b200_backward(b200_net* net, int slot) {
+    if (int rc = check_slot(net, slot, "backward")) return rc;
+    if (int rc = set_device(net)) return rc;
+    Slot& s = net->slots[slot];
+    const b200_net_desc& d = net->d;
+    CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
+    if (int rc = refresh_table(net)) return rc;
+    const bool tiled = net->use_tiled();
+    const int chunks = tiled ? tiles_for(net, s.n) : 1;
+    const Tensor* l0w = net->find("l0w");
+    const size_t total = (size_t)net->n_flat + kAlignFloats;
+    if (tiled && chunks == 1) {
+        // every (block, slab) tile of the table gradient is stored whole by its CTA
+        const size_t w_end = (size_t)l0w->off + (size_t)((l0w->n + kAlignFloats - 1) / kAlignFloats * kAlignFloats);
+        CK(cudaMemsetAsync(net->G, 0, (size_t)l0w->off * 4, net->stream));
+        CK(cudaMemsetAsync(net->G + w_end, 0, (total - w_end) * 4, net->stream));
+    } else {
+        CK(cudaMemsetAsync(net->G, 0, total * 4, net->stream));
+    }
+    cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
+    CK(cudaEventRecord(ev[0], net->stream));
+    if (int rc = forward_part(net, s, true)) return rc;
+    CK(cudaEventRecord(ev[2], net->stream));
+    for (int l = d.n_dense - 1; l >= 0; l--)
+        if (int rc = launch_wgrad(net, s, l)) return rc;
+    {
+        b200::DenseArgs da = dense_args(net, s, true);
+        DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<(s.n + 7) / 8, 256, 0, net->stream>>>(da, net->dx));
+        LAUNCHED(net);
+    }
+    CK(cudaEventRecord(ev[3], net->stream));
+    {
+        b200::FtArgs fa = ft_args(net, s);
+        b200::TileArgs ta = tile_args(net, s, chunks);
+        int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled) : launch_ft_backward<false>(net, fa, ta, tiled);
+        if (rc) return rc;
+    }
+    CK(cudaEventRecord(ev[4], net->stream));
+    if (d.factoriser_rows) {
+        const Tensor* f = net->find("l0f");
+        b200::factoriser_grad_kernel<<<kSmCount * 4, 256, 0, net->stream>>>(
+            reinterpret_cast<const float4*>(net->G + l0w->off), reinterpret_cast<float4*>(net->G + f->off),
+            (size_t)f->n / 4, (int)(l0w->n / f->n));
+        LAUNCHED(net);
+    }
+    CK(cudaEventRecord(ev[5], net->stream));
+    CK(cudaEventRecord(s.consumed, net->stream));
+    s.has_consumed = true;
+    net->have_backward = true;
+    net->step_open = true;
+    net->last_n = s.n;
+    return 0;
+}
+
+int b200_update(b200_net* net, float lr, float grad_factor) {
+    if (!net) return b200::fail(B200_ERR_ARG, "update: null net");
+    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update: no gradients yet, call b200_backward first");
+    if (int rc = set_device(net)) return rc;
+    CK(cudaMemcpyAsync(net->h_loss, net->G + net->n_flat, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaMemcpyAsync(net->h_status, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaEventRecord(net->loss_ev, net->stream));
+    net->loss_pending = true;
+    b200::AdamArgs a{};
+    a.p = reinterpret_cast<float4*>(net->P);
+    a.m = reinterpret_cast<float4*>(net->M);
+    a.v = reinterpret_cast<float4*>(net->V);
+    a.g = reinterpret_cast<const float4*>(net->G);
+    a.total4 = net->n_flat / 4;
+    a.rate = lr;
+    a.adj = grad_factor;
+    a.nseg = (int)net->tensors.size();
+    for (int i = 0; i < a.nseg; i++) {
+        const Tensor& t = net->tensors[i];
+        a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
+    }
+    const long long blocks = std::min<long long>((a.total4 + 255) / 256, kSmCount * 16);
+    b200::adamw_flat_kernel<<<(unsigned)blocks, 256, 0, net->stream>>>(a);
+    LAUNCHED(net);
+    net->table_dirty = true;
+    if (int rc = refresh_table(net)) return rc;
+    if (net->step_open) {  // close the timed step begun by the matching backward
+        CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][6], net->stream));
+        net->steps_begun++;
+        net->steps_done = net->steps_begun;
+        net->step_open = false;
+    }
+    return 0;
+}
+
+int b200_step(b200_net* net, int slot, float lr, float grad_factor) {
+    if (int rc = b200_backward(net, slot)) return rc;
+    return b200_update(net, lr, grad_factor);
+}
+
+int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats) {
+    if (!net || !device_ptr || !n_floats) return b200::fail(B200_ERR_ARG, "grad_buffer: null argument");
+    *device_ptr = net->G;
+    *n_floats = net->n_flat + 1;
+    return 0;
+}
+
+int b200_loss(b200_net* net, float* loss_sum) {
+    if (!net || !loss_sum) return b200::fail(B200_ERR_ARG, "loss: null argument");
+    if (!net->loss_pending) return b200::fail(B200_ERR_STATE, "loss: no update has run yet");
+    if (int rc = set_device(net)) return rc;
+    CK(cudaEventSynchronize(net->loss_ev));
+    *loss_sum = *net->h_loss;
+    if (*net->h_status & b200::kStatusOutsideBlock) {
+        *net->h_status = 0;
+        cudaMemsetAsync(net->status, 0, sizeof(int), net->stream);
+        return b200::fail(B200_ERR_DATA,
+                          "a feature index fell outside the row block of its position (ft_block_rows=%d): those "
+                          "features were ignored; create the network with ft_block_rows=0 for such inputs",
+                          net->d.ft_block_rows);
+    }
+    return 0;
+}
+
+int b200_forward(b200_net* net, int slot, float* out_host) {
+    if (int rc = check_slot(net, slot, "forward")) return rc;
+    if (!out_host) return b200::fail(B200_ERR_ARG, "forward: null output");
+    if (int rc = set_device(net)) return rc;
+    Slot& s = net->slots[slot];
+    CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
+    if (int rc = refresh_table(net)) return rc;
+    if (int rc = forward_part(net, s, false)) return rc;
+    CK(cudaEventRecord(s.consumed, net->stream));
+    s.has_consumed = true;
+    net->last_n = s.n;
+    CK(cudaMemcpyAsync(out_host, net->out, (size_t)s.n * sizeof(float), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaStreamSynchronize(net->stream));
+    return 0;
+}
+
+int b200_sync(b200_net* net) {
+    if (!net) return b200::fail(B200_ERR_ARG, "sync: null net");
+    if (int rc = set_device(net)) return rc;
+    CK(cudaStreamSynchronize(net->copy_stream));
+    CK(cudaStreamSynchronize(net->stream));
+    return 0;
+}
+
+int b200_get_timings(b200_net* net, b200_timings* out) {
+    if (!net || !out) return b200::fail(B200_ERR_ARG, "get_timings: null argument");
+    if (int rc = set_device(net)) return rc;
+    memset(out, 0, sizeof *out);
+    const int64_t first = std::max(net->timing_origin, net->steps_done - b200_net::kTimingRing);
+    const int64_t count = net->steps_done - first;
+    net->timing_origin = net->steps_done;
+    if (count < 1) return b200::fail(B200_ERR_STATE, "get_timings: no complete step since the last call");
+    CK(cudaStreamSynchronize(net->stream));
+    double acc[7] = {0, 0, 0, 0, 0, 0, 0};
+    for (int64_t i = first; i < net->steps_done; i++) {
+        cudaEvent_t* ev = net->tev[i % b200_net::kTimingRing];
+        float ms = 0.f;
+        for (int k = 0; k < 6; k++) {
+            CK(cudaEventElapsedTime(&ms, ev[k], ev[k + 1]));
+            acc[k] += ms;
+        }
+        CK(cudaEventElapsedTime(&ms, ev[0], ev[6]));
+        acc[6] += ms;
+    }
+    const double inv = 1.0 / (double)count;
+    out->ft_forward = (float)(acc[0] * inv);
+    out->dense_forward = (float)(acc[1] * inv);
+    out->dense_backward = (float)(acc[2] * inv);
+    out->ft_backward = (float)(acc[3] * inv);
+    out->factoriser_grad = (float)(acc[4] * inv);
+    out->optimiser = (float)(acc[5] * inv);
+    out->total = (float)(acc[6] * inv);
+    out->steps = (int32_t)count;
+    return 0;
+}
+
+int b200_net_get_stat(b200_net* net, const char* key, int64_t* value) {
+    if (!net || !key || !value) return b200::fail(B200_ERR_ARG, "get_stat: null argument");
+    if (!strcmp(key, "launches")) *value = net->launches;
+    else if (!strcmp(key, "h2d_bytes")) *value = net->h2d_bytes;
+    else if (!strcmp(key, "flat_floats")) *value = net->n_flat;
+    else if (!strcmp(key, "ft_tiled")) *value = net->use_tiled() ? 1 : 0;
+    else return b200::fail(B200_ERR_ARG, "get_stat: unknown key '%s'", key);
+    return 0;
+}
+
+int b200_net_get_activation(b200_net* net, int which, float* host, int64_t n) {
+    if (!net || !host) return b200::fail(B200_ERR_ARG, "get_activation: null argument");
+    const int64_t B = net->last_n;
+    const float* src = nullptr;
+    int64_t want = 0;
+    switch (which) {
+        case 0: src = net->x; want = B * net->D1(); break;
+        case 1: src = net->u; want = net->d.pairwise ? B * 2 * net->d.ft_out : 0; break;
+        case 2: src = net->dx; want = B * net->D1(); break;
+        case 3: src = net->out; want = B; break;
+        default: return b200::fail(B200_ERR_ARG, "get_activation: unknown buffer %d", which);
+    }
+    if (!src || want == 0) return b200::fail(B200_ERR_STATE, "get_activation: buffer %d is not used by this network", which);
+    if (n != want) return b200::fail(B200_ERR_ARG, "get_activation: buffer %d holds %lld values, %lld asked", which, (long long)want, (long long)n);
+    if (int rc = set_device(net)) return rc;
+    CK(cudaStreamSynchronize(net->stream));
+    CK(cudaMemcpy(host, src, n * sizeof(float), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+}  // extern "C"

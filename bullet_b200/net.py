@@ -1,0 +1,166 @@
+"""Python host side of the C ABI: `Net` wraps one `b200_net`, `featurise` wraps the mappers.
+
+Method names follow the reference's trainer vocabulary: weights are addressed by their ids
+("l0w", "l1b", ...), `set_params_for_weight` mirrors Optimiser::set_params_for_weight
+(crates/trainer/src/optimiser.rs:204-206), `step` is one pass of the loop in
+crates/trainer/src/run.rs:166-250.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from .configs import KING_BUCKETS_16, AdamWParams, CNetDesc, NetDesc
+
+KIND_WEIGHT, KIND_MOMENTUM, KIND_VELOCITY, KIND_GRAD = 0, 1, 2, 3
+FT_AUTO, FT_GATHER, FT_TILED = 0, 1, 2
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+class Net:
+    def __init__(self, desc: NetDesc, device: int = 0, stream: int | None = None):
+        self.lib = _lib.load()
+        self.desc = desc
+        self._h = ctypes.c_void_p()
+        cdesc = CNetDesc.from_desc(desc)
+        _lib.check(self.lib.b200_net_create(device, ctypes.c_void_p(stream or 0), ctypes.byref(cdesc),
+                                            ctypes.byref(self._h)))
+
+    def close(self) -> None:
+        if self._h:
+            self.lib.b200_net_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ----------------------------------------------------------------- tensors
+    def set_option(self, key: str, value: int) -> None:
+        _lib.check(self.lib.b200_net_set_option(self._h, key.encode(), value))
+
+    def tensor_size(self, name: str) -> int:
+        n = ctypes.c_int64()
+        _lib.check(self.lib.b200_net_tensor_size(self._h, name.encode(), ctypes.byref(n)))
+        return n.value
+
+    def set_tensor(self, name: str, values, kind: int = KIND_WEIGHT) -> None:
+        a = np.ascontiguousarray(values, dtype=np.float32).ravel()
+        _lib.check(self.lib.b200_net_set_tensor(self._h, name.encode(), kind, _p(a), a.size))
+
+    def get_tensor(self, name: str, kind: int = KIND_WEIGHT) -> np.ndarray:
+        out = np.empty(self.tensor_size(name), dtype=np.float32)
+        _lib.check(self.lib.b200_net_get_tensor(self._h, name.encode(), kind, _p(out), out.size))
+        return out
+
+    def load_weights(self, tensors: dict) -> None:
+        for name in self.desc.tensor_shapes():
+            self.set_tensor(name, tensors[name])
+
+    def tensors(self, kind: int = KIND_WEIGHT) -> dict:
+        return {name: self.get_tensor(name, kind) for name in self.desc.tensor_shapes()}
+
+    def set_params_for_weight(self, name: str | None, p: AdamWParams) -> None:
+        c = _lib.CAdamW(p.decay, p.beta1, p.beta2, p.min_weight, p.max_weight)
+        _lib.check(self.lib.b200_net_set_adamw(self._h, name.encode() if name else None, ctypes.byref(c)))
+
+    # ------------------------------------------------------------------- batch
+    def upload(self, slot: int, stm, nstm, buckets, targets) -> None:
+        stm = np.ascontiguousarray(stm, dtype=np.int32)
+        nstm = np.ascontiguousarray(nstm, dtype=np.int32)
+        targets = np.ascontiguousarray(targets, dtype=np.float32)
+        n = targets.size
+        if stm.size != n * self.desc.nnz or nstm.size != n * self.desc.nnz:
+            raise ValueError("index arrays must hold n * nnz slots")
+        b = None if buckets is None else np.ascontiguousarray(buckets, dtype=np.int32)
+        _lib.check(self.lib.b200_batch_upload(self._h, slot, _p(stm), _p(nstm), None if b is None else _p(b),
+                                              _p(targets), n))
+
+    # -------------------------------------------------------------------- step
+    def step(self, slot: int, lr: float, grad_factor: float) -> None:
+        _lib.check(self.lib.b200_step(self._h, slot, lr, grad_factor))
+
+    def backward(self, slot: int) -> None:
+        _lib.check(self.lib.b200_backward(self._h, slot))
+
+    def update(self, lr: float, grad_factor: float) -> None:
+        _lib.check(self.lib.b200_update(self._h, lr, grad_factor))
+
+    def loss(self) -> float:
+        v = ctypes.c_float()
+        _lib.check(self.lib.b200_loss(self._h, ctypes.byref(v)))
+        return v.value
+
+    def forward(self, slot: int, n: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.float32)
+        _lib.check(self.lib.b200_forward(self._h, slot, _p(out)))
+        return out
+
+    def sync(self) -> None:
+        _lib.check(self.lib.b200_sync(self._h))
+
+    def timings(self) -> dict:
+        t = _lib.CTimings()
+        _lib.check(self.lib.b200_get_timings(self._h, ctypes.byref(t)))
+        return {name: getattr(t, name) for name, _ in t._fields_}
+
+    def stat(self, key: str) -> int:
+        v = ctypes.c_int64()
+        _lib.check(self.lib.b200_net_get_stat(self._h, key.encode(), ctypes.byref(v)))
+        return v.value
+
+    def activation(self, which: int, n: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.float32)
+        _lib.check(self.lib.b200_net_get_activation(self._h, which, _p(out), out.size))
+        return out
+
+    def grad_buffer(self):
+        """(device address, number of floats) of the flat gradient buffer; the last float is the loss."""
+        ptr, n = ctypes.c_void_p(), ctypes.c_int64()
+        _lib.check(self.lib.b200_grad_buffer(self._h, ctypes.byref(ptr), ctypes.byref(n)))
+        return ptr.value, n.value
+
+
+def featurise(game: str, records: np.ndarray, desc: NetDesc, scale: float = 400.0, blend: float = 0.5):
+    """records -> (stm, nstm, buckets, targets) in the reference mapper's layout."""
+    lib = _lib.load()
+    n = len(records)
+    records = np.ascontiguousarray(records)
+    stm = np.empty((n, desc.nnz), dtype=np.int32)
+    nstm = np.empty((n, desc.nnz), dtype=np.int32)
+    if game == "chess768":
+        _lib.check(lib.b200_map_chess768(_p(records), n, _p(stm), _p(nstm), desc.nnz))
+    elif game == "chess_buckets":
+        layout = np.asarray(KING_BUCKETS_16, dtype=np.int32)
+        _lib.check(lib.b200_map_chess_buckets_mirrored(_p(records), n, _p(layout), _p(stm), _p(nstm), desc.nnz))
+    elif game == "ataxx147":
+        _lib.check(lib.b200_map_ataxx147(_p(records), n, _p(stm), _p(nstm), desc.nnz))
+    else:
+        raise ValueError(game)
+    buckets = np.zeros(n, dtype=np.int32)
+    if desc.n_out_buckets > 1:
+        _lib.check(lib.b200_material_count(_p(records), n, desc.n_out_buckets, _p(buckets)))
+    targets = np.empty(n, dtype=np.float32)
+    _lib.check(lib.b200_make_targets(_p(records), n, scale, blend, _p(targets)))
+    return stm, nstm, buckets, targets
+
+
+def pack_indices(idx: np.ndarray) -> np.ndarray:
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    out = np.empty(idx.shape, dtype=np.uint16)
+    _lib.check(_lib.load().b200_pack_indices_u16(_p(idx), idx.size, _p(out)))
+    return out
+
+
+def unpack_indices(packed: np.ndarray) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint16)
+    out = np.empty(packed.shape, dtype=np.int32)
+    _lib.check(_lib.load().b200_unpack_indices_u16(_p(packed), packed.size, _p(out)))
+    return out

@@ -1,0 +1,167 @@
+/*
+ * bullet_b200 — C ABI of the B200-native NNUE training step.
+ *
+ * This header is the whole drop-in boundary: plain pointers and sizes, no C++ or
+ * torch types.  A binding for bullet's Rust crates declares exactly these symbols
+ * in an `extern "C"` block; each entry point names the piece of jw1912/bullet it
+ * stands in for (paths relative to that project).
+ *
+ * Conventions
+ *   - every function returns 0 on success, a negative B200_ERR_* otherwise;
+ *     b200_last_error() then holds a message for the calling thread.  Nothing
+ *     aborts, throws across the boundary, or traps on the device.
+ *   - a b200_net is bound to one CUDA device and is not re-entrant; different
+ *     nets (GPUs) may be driven from different host threads at the same time.
+ *   - host pointers are borrowed for the duration of the call only.
+ *   - weights are column-major `rows x cols` (docs/4-saved-networks.md:21-31):
+ *     l0w[feature * H + row]; dense layer i: l{i}w[col * (O*M_i) + bucket*M_i + row].
+ *   - there is no CPU fallback: without a usable CUDA device every entry point
+ *     that needs one fails with B200_ERR_CUDA.
+ */
+#ifndef BULLET_B200_H
+#define BULLET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_ERR_ARG (-1)         /* bad argument, unknown tensor name, size mismatch   */
+#define B200_ERR_STATE (-2)       /* call order violated (e.g. step on an empty slot)    */
+#define B200_ERR_CUDA (-3)        /* a CUDA runtime call failed; message has the code    */
+#define B200_ERR_DATA (-4)        /* batch data violates the declared input structure    */
+#define B200_ERR_UNSUPPORTED (-5) /* network shape outside what the kernels implement    */
+
+#define B200_ACT_NONE 0
+#define B200_ACT_CRELU 1
+#define B200_ACT_SCRELU 2
+
+#define B200_KIND_WEIGHT 0
+#define B200_KIND_MOMENTUM 1
+#define B200_KIND_VELOCITY 2
+#define B200_KIND_GRAD 3
+
+#define B200_NUM_SLOTS 3 /* staging slots for double/triple-buffered upload */
+
+/* Feature-transformer kernel selection (b200_net_set_option "ft_mode") */
+#define B200_FT_AUTO 0
+#define B200_FT_GATHER 1 /* row gather straight from the table in L2/HBM, global vector atomics */
+#define B200_FT_TILED 2  /* table block staged in shared memory, positions grouped by block */
+
+typedef struct b200_net b200_net;
+
+/* The recognised form of the graph built by bullet's ModelBuilder closure
+ * (examples/simple.rs:25-56, examples/progression/4_multi_layer.rs:66-87):
+ * l0 affine on both sparse perspectives -> activation [-> pairwise_mul] ->
+ * concat -> 1..3 dense affines, each followed by select(output bucket) and an
+ * activation -> sigmoid -> squared error, summed over the batch. */
+typedef struct b200_net_desc {
+    int32_t n_inputs;        /* sparse inputs per perspective (SparseInputType::num_inputs)   */
+    int32_t nnz;             /* index slots per position (SparseInputType::max_active), <= 64 */
+    int32_t ft_out;          /* rows of l0 (hidden size H), multiple of 8                     */
+    int32_t ft_act;          /* B200_ACT_CRELU or B200_ACT_SCRELU                             */
+    int32_t pairwise;        /* 1: crelu then pairwise_mul (model/builder.rs:390-393)         */
+    int32_t factoriser_rows; /* 0, or rows of l0f with l0w + l0f.repeat(n) as the table       */
+    int32_t n_out_buckets;   /* OutputBuckets::BUCKETS                                        */
+    int32_t n_dense;         /* 1..3                                                          */
+    int32_t dense_out[3];    /* rows per bucket; <= 32; the last must be 1                    */
+    int32_t dense_act[3];    /* activation after select; the last must be B200_ACT_NONE       */
+    int32_t ft_block_rows;   /* >0 promises that the valid features of one perspective of one
+                                position all fall in one aligned block of this many table rows
+                                (768 for king-bucketed chess inputs); 0 promises nothing      */
+    int32_t max_batch;       /* largest batch a slot will ever hold                           */
+} b200_net_desc;
+
+/* crates/trainer/src/optimiser/adam.rs:20-33 — same fields, same defaults. */
+typedef struct b200_adamw_params {
+    float decay, beta1, beta2, min_weight, max_weight;
+} b200_adamw_params;
+
+/* Device time of the phases of a step (milliseconds, CUDA events on the compute stream). */
+typedef struct b200_timings {
+    float ft_forward, dense_forward, dense_backward, ft_backward, factoriser_grad, optimiser, total;
+    int32_t steps; /* complete steps averaged */
+} b200_timings;
+
+const char* b200_last_error(void);
+int b200_version(void);
+
+/* ---- life cycle.  Stands in for Device::new + Function::new/prealloc
+ * (crates/gpu/src/function.rs:73,180) and Optimiser::new
+ * (crates/trainer/src/optimiser.rs:98-133): allocates every buffer the step
+ * needs, once.  `stream` is a cudaStream_t to run on, or NULL for a private one. */
+int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_net** out);
+int b200_net_destroy(b200_net* net);
+int b200_net_set_option(b200_net* net, const char* key, int64_t value);
+
+/* ---- tensors by reference id ("l0w","l0b","l0f","l1w",...).  Stands in for
+ * Optimiser::load_weights_from_host / Buffer::to_host
+ * (crates/trainer/src/optimiser.rs:208-216).  `kind` selects weight, momentum,
+ * velocity or (read-only) the batch-summed gradient of the last backward pass. */
+int b200_net_tensor_size(b200_net* net, const char* name, int64_t* n);
+int b200_net_set_tensor(b200_net* net, const char* name, int kind, const float* host, int64_t n);
+int b200_net_get_tensor(b200_net* net, const char* name, int kind, float* host, int64_t n);
+/* Optimiser::set_params_for_weight (crates/trainer/src/optimiser.rs:204-206); NULL name = all. */
+int b200_net_set_adamw(b200_net* net, const char* name, const b200_adamw_params* params);
+
+/* ---- batch upload.  Stands in for PreparedBatchHost::copy_to_device_async
+ * (crates/trainer/src/run/dataloader.rs:41-61): takes the mapper's output in
+ * the reference layout (i32 [n][nnz] per perspective, -1 in unused slots, i32
+ * bucket and f32 target per position; crates/bullet_lib/src/value.rs:77-117),
+ * packs it to u16 in pinned memory and starts one asynchronous copy.  Blocks
+ * only while `slot` is still being read by an earlier step. */
+int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t* nstm, const int32_t* buckets,
+                      const float* targets, int32_t n);
+
+/* ---- the step.  b200_step = Function::execute on the backward graph followed by
+ * Optimiser::update (crates/trainer/src/run.rs:185-192).  The split form lets a
+ * data-parallel host all-reduce the flat gradient buffer between the halves:
+ * gradients are batch SUMS and `grad_factor` (1/global batch) is applied in the
+ * update, as in crates/trainer/src/run.rs:130-131.  All calls only enqueue. */
+int b200_step(b200_net* net, int slot, float lr, float grad_factor);
+int b200_backward(b200_net* net, int slot);
+int b200_update(b200_net* net, float lr, float grad_factor);
+/* Device address and length (floats) of the flat gradient buffer; its last
+ * element is the summed loss, so one all-reduce carries both. */
+int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
+/* Summed loss of the most recent update/step (run.rs:212-221); waits for it. */
+int b200_loss(b200_net* net, float* loss_sum);
+/* Forward only: network output per position (ModelEvaluator, crates/trainer/src/model/evaluator.rs:22-81). */
+int b200_forward(b200_net* net, int slot, float* out_host);
+int b200_sync(b200_net* net);
+/* Average device time per phase over the complete steps (backward + update) enqueued since
+ * the previous call, at most the last 256; waits for them.  ft_forward and ft_backward each
+ * span exactly one kernel launch. */
+int b200_get_timings(b200_net* net, b200_timings* out);
+/* Counters: "launches" (kernels launched so far), "h2d_bytes" (batch bytes copied so far),
+ * "flat_floats" (length of the flat parameter buffer), "ft_tiled" (1 if the tiled kernels run). */
+int b200_net_get_stat(b200_net* net, const char* key, int64_t* value);
+/* Debug/inspection: copy an internal activation buffer of the last pass to the host.
+ * which: 0 = dense-stack input x [n][D1], 1 = pairwise crelu outputs u [n][2][H],
+ *        2 = gradient at x [n][D1], 3 = network outputs [n]. */
+int b200_net_get_activation(b200_net* net, int which, float* host, int64_t n);
+
+/* ---- host featurisers (no device needed).  Records are the 32-byte layouts of
+ * bulletformat's ChessBoard / AtaxxBoard as restated in examples/tests/test4.rs:8-36
+ * and examples/ataxx.rs:8-31.  Outputs use the mapper's layout with -1 in every
+ * unused slot.  Return the largest feature count seen. */
+int b200_map_chess768(const void* records, int32_t n, int32_t* stm, int32_t* nstm, int32_t nnz);
+/* ChessBucketsMirrored::{new,map_features} (crates/bullet_lib/src/game/inputs/chess_buckets.rs:57-88) */
+int b200_map_chess_buckets_mirrored(const void* records, int32_t n, const int32_t* layout32, int32_t* stm,
+                                    int32_t* nstm, int32_t nnz);
+/* Ataxx147::map_features (crates/bullet_lib/src/game/inputs/ataxx147.rs:18-27) */
+int b200_map_ataxx147(const void* records, int32_t n, int32_t* stm, int32_t* nstm, int32_t nnz);
+/* MaterialCount<N>::bucket (crates/bullet_lib/src/game/outputs.rs:24-31) */
+int b200_material_count(const void* records, int32_t n, int32_t n_buckets, int32_t* out);
+/* target = blend*result/2 + (1-blend)*sigmoid(score/scale) (crates/bullet_lib/src/value.rs:103-115) */
+int b200_make_targets(const void* records, int32_t n, float scale, float blend, float* out);
+/* The packed index format of a staging slot: u16 per slot, 0xFFFF for "no feature". */
+int b200_pack_indices_u16(const int32_t* idx, int64_t count, uint16_t* out);
+int b200_unpack_indices_u16(const uint16_t* packed, int64_t count, int32_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BULLET_B200_H */

@@ -372,6 +372,25 @@ static int dense_in(const orc_net_desc* d, int layer) {
     return d->dense_out[layer - 1];
 }
 
+/* Grow-only scratch buffers reused across calls: the large temporaries (gradient tables,
+ * activations) would otherwise be mapped, faulted in and unmapped on every step, which
+ * costs more than the arithmetic.  Not thread-safe across concurrent oracle calls. */
+#define ORC_SCRATCH_SLOTS 8
+static real* scratch_buf[ORC_SCRATCH_SLOTS];
+static size_t scratch_len[ORC_SCRATCH_SLOTS];
+static real* scratch(int slot, size_t n) {
+    if (scratch_len[slot] < n) {
+        free(scratch_buf[slot]);
+        scratch_buf[slot] = (real*)malloc(sizeof(real) * n);
+        scratch_len[slot] = n;
+    }
+    return scratch_buf[slot];
+}
+static void zero_parallel(real* p, size_t n) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) p[i] = 0;
+}
+
 /* Forward + backward of one batch.  Gradients are batch SUMS (the 1/B factor
  * lives in AdamW, crates/trainer/src/run.rs:130-131).  `out` (may be NULL)
  * receives the network output per position; `grads` may be NULL for a
@@ -395,14 +414,14 @@ int orc_net_grad(const orc_net_desc* d, const orc_tensors* w, const int32_t* stm
     real* weff = NULL;
     if (d->factoriser_rows > 0) {
         size_t blk = (size_t)d->factoriser_rows * H;
-        weff = (real*)malloc(sizeof(real) * (size_t)NI * H);
+        weff = scratch(0, (size_t)NI * H);
 #pragma omp parallel for schedule(static)
         for (size_t i = 0; i < (size_t)NI * H; i++) weff[i] = w->l0w[i] + w->l0f[i % blk];
         W = weff;
     }
 
-    real* u = (real*)malloc(sizeof(real) * (size_t)B * 2 * H); /* FT activation outputs, stm then nstm */
-    real* x = (real*)malloc(sizeof(real) * (size_t)B * D1);    /* dense-stack input */
+    real* u = scratch(1, (size_t)B * 2 * H); /* FT activation outputs, stm then nstm */
+    real* x = scratch(2, (size_t)B * D1);    /* dense-stack input */
     real* a[3] = {0, 0, 0};                                    /* selected + activated outputs per layer */
     for (int l = 0; l < nd; l++) a[l] = (real*)malloc(sizeof(real) * (size_t)B * d->dense_out[l]);
     real* lossv = (real*)malloc(sizeof(real) * B);
@@ -468,7 +487,7 @@ int orc_net_grad(const orc_net_desc* d, const orc_tensors* w, const int32_t* stm
         const size_t nl0 = (size_t)NI * H;
         real* dz[3] = {0, 0, 0}; /* gradient at each dense layer's selected pre-activation */
         for (int l = 0; l < nd; l++) dz[l] = (real*)malloc(sizeof(real) * (size_t)B * d->dense_out[l]);
-        real* du = (real*)malloc(sizeof(real) * (size_t)B * 2 * H); /* gradient at the FT pre-activation */
+        real* du = scratch(3, (size_t)B * 2 * H); /* gradient at the FT pre-activation */
 
         /* phase A, per position: everything that does not sum over the batch */
 #pragma omp parallel
@@ -534,7 +553,10 @@ int orc_net_grad(const orc_net_desc* d, const orc_tensors* w, const int32_t* stm
         /* the two perspectives fill separate zeroed tables which are then added
          * to a zeroed output one after the other (sparse.rs:253-271) */
         real* tab[2];
-        for (int p = 0; p < 2; p++) tab[p] = (real*)calloc(nl0, sizeof(real));
+        for (int p = 0; p < 2; p++) {
+            tab[p] = scratch(4 + p, nl0);
+            zero_parallel(tab[p], nl0);
+        }
         memset(grads->l0b, 0, sizeof(real) * H);
         {
             const int chunk = 64;
@@ -559,7 +581,6 @@ int orc_net_grad(const orc_net_desc* d, const orc_tensors* w, const int32_t* stm
         }
 #pragma omp parallel for schedule(static)
         for (size_t i = 0; i < nl0; i++) grads->l0w[i] = ((real)0 + tab[0][i]) + tab[1][i];
-        for (int p = 0; p < 2; p++) free(tab[p]);
         /* factoriser gradient = sum over the tiled copies (broadcast.rs:18-20 -> reduce.rs:96-120) */
         if (d->factoriser_rows > 0) {
             size_t blk = (size_t)d->factoriser_rows * H;
@@ -572,15 +593,12 @@ int orc_net_grad(const orc_net_desc* d, const orc_tensors* w, const int32_t* stm
             }
         }
         for (int l = 0; l < nd; l++) free(dz[l]);
-        free(du);
     }
 
-    free(u);
-    free(x);
     for (int l = 0; l < nd; l++) free(a[l]);
     free(lossv);
     free(sig);
-    if (weff) free(weff);
+    (void)weff;
     return 0;
 }
 

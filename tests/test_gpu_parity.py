@@ -1,0 +1,305 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Tolerances (fp32): loss and every parameter tensor within 1e-4 relative after one step and
+within 1e-3 after 100 steps; batch-summed gradients within 2e-5 of the tensor's largest
+entry; the feature-transformer output and the index packing are bit-exact.  "Relative" for
+a tensor is norm-wise: ||a-b|| / ||b|| in both the 2-norm and the max-norm.
+"""
+import dataclasses
+
+import numpy as np
+import pytest
+
+from bullet_b200 import config, synth
+from bullet_b200.configs import ACT_CRELU, ACT_NONE, ACT_SCRELU, AdamWParams, NetDesc
+
+pytestmark = pytest.mark.gpu
+
+FT_GATHER, FT_TILED = 1, 2
+
+
+def rel2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b.astype(np.float64)), 1e-30))
+
+
+def relinf(a, b):
+    return float(np.abs(a.astype(np.float64) - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def small_nets():
+    yield "simple16", NetDesc(n_inputs=768, nnz=32, ft_out=16, ft_act=ACT_SCRELU, ft_block_rows=768), "chess768"
+    yield "simple128", NetDesc(n_inputs=768, nnz=32, ft_out=128, ft_act=ACT_SCRELU, ft_block_rows=768), "chess768"
+    yield "ataxx", NetDesc(n_inputs=147, nnz=49, ft_out=64, ft_act=ACT_CRELU, ft_block_rows=147), "ataxx147"
+    yield "bucketed", NetDesc(n_inputs=12288, nnz=32, ft_out=96, ft_act=ACT_SCRELU, factoriser_rows=768,
+                              n_out_buckets=8, ft_block_rows=768), "chess_buckets"
+    yield "pairwise", NetDesc(n_inputs=12288, nnz=32, ft_out=128, ft_act=ACT_CRELU, pairwise=True,
+                              factoriser_rows=768, n_out_buckets=8, dense_out=(16, 32, 1),
+                              dense_act=(ACT_SCRELU, ACT_SCRELU, ACT_NONE), ft_block_rows=768), "chess_buckets"
+    yield "two-layer", NetDesc(n_inputs=768, nnz=32, ft_out=64, ft_act=ACT_CRELU, n_out_buckets=4,
+                               dense_out=(8, 1), dense_act=(ACT_CRELU, ACT_NONE), ft_block_rows=768), "chess768"
+
+
+NETS = list(small_nets())
+IDS = [n for n, _, _ in NETS]
+
+
+def make_net(desc, mode=0, weights=None):
+    from bullet_b200.net import Net
+
+    net = Net(desc)
+    if mode:
+        net.set_option("ft_mode", mode)
+    if weights is not None:
+        net.load_weights(weights)
+    return net
+
+
+def rich_weights(desc, seed=5, fan_in=8):
+    """Weights with non-zero biases and factoriser, scaled so activations hit both clamps."""
+    w = synth.init_weights(desc, seed=seed, ft_fan_in=fan_in)
+    rng = np.random.default_rng(seed + 1)
+    for k in w:
+        if k.endswith("b") or k == "l0f":
+            w[k] = rng.normal(0, 0.05, w[k].size).astype(np.float32)
+    return w
+
+
+def modes_for(desc):
+    tiled_ok = desc.ft_block_rows > 0 and desc.ft_out % 32 == 0
+    return [FT_GATHER, FT_TILED] if tiled_ok else [FT_GATHER]
+
+
+def oracle_ft_output(orc, desc, w, stm, nstm):
+    """Dense-stack input x composed from the oracle's op-level functions, as the graph does."""
+    H, NI, B = desc.ft_out, desc.n_inputs, len(stm)
+    table = np.asarray(w["l0w"], dtype=np.float32)
+    if desc.factoriser_rows:
+        table = table + orc.broadcast(w["l0f"], 1, desc.factoriser_rows * H, NI // desc.factoriser_rows)
+    halves = []
+    for idx in (stm, nstm):
+        acc = orc.sparse_matmul(table, idx, B, H, NI, H, 0, desc.nnz).reshape(B, H) + w["l0b"][None, :]
+        if desc.pairwise:
+            u = orc.act_forward(ACT_CRELU, acc.ravel()).reshape(B, H)
+            halves.append(u[:, : H // 2] * u[:, H // 2:])
+        else:
+            halves.append(orc.act_forward(desc.ft_act, acc.ravel()).reshape(B, H))
+    return np.concatenate(halves, 1)
+
+
+@pytest.mark.parametrize("name,desc,game", NETS, ids=IDS)
+def test_forward_bit_exact_and_outputs(oracle32, name, desc, game):
+    B = 333
+    desc = dataclasses.replace(desc, max_batch=B)
+    rec = synth.records(game, B, seed=21)
+    stm, nstm, buckets, targets = oracle32.map_batch(game, rec, desc)
+    w = rich_weights(desc)
+    x_ref = oracle_ft_output(oracle32, desc, w, stm, nstm)
+    _, _, out_ref = oracle32.net_grad(desc, w, stm, nstm, buckets, targets, want_grads=False)
+    for mode in modes_for(desc):
+        net = make_net(desc, mode, w)
+        net.upload(0, stm, nstm, buckets, targets)
+        out = net.forward(0, B)
+        x = net.activation(0, B * desc.dense_in0).reshape(B, -1)
+        assert np.array_equal(x, x_ref), f"mode {mode}: feature-transformer output differs"
+        np.testing.assert_allclose(out, out_ref, rtol=2e-5, atol=2e-6)
+        net.close()
+
+
+@pytest.mark.parametrize("name,desc,game", NETS, ids=IDS)
+def test_one_step_parity(oracle32, oracle64, name, desc, game):
+    B = 1000
+    desc = dataclasses.replace(desc, max_batch=B)
+    rec = synth.records(game, B, seed=22)
+    batch = oracle32.map_batch(game, rec, desc)
+    w = rich_weights(desc)
+    hp = AdamWParams()
+    loss_ref, g_ref, _ = oracle32.net_grad(desc, w, *batch)
+    _, g64, _ = oracle64.net_grad(desc, w, *batch)
+    w_ref, m_ref, v_ref, _ = oracle32.train(desc, w, [batch], 1e-3, hp)
+    for mode in modes_for(desc):
+        net = make_net(desc, mode, w)
+        net.upload(1, *batch)
+        net.step(1, 1e-3, 1.0 / B)
+        loss = net.loss()
+        assert abs(loss - loss_ref) <= 1e-4 * abs(loss_ref), (mode, loss, loss_ref)
+        g = net.tensors(kind=3)
+        for k in g_ref:
+            scale = np.abs(g64[k]).max()
+            assert scale > 0, k
+            err = np.abs(g[k] - g64[k]).max() / scale
+            err_ref = np.abs(g_ref[k] - g64[k]).max() / scale
+            assert err <= 2e-5, (mode, k, err, err_ref)
+        p, m, v = net.tensors(0), net.tensors(1), net.tensors(2)
+        for k in w_ref:
+            assert rel2(p[k], w_ref[k]) <= 1e-4 and relinf(p[k], w_ref[k]) <= 1e-4, (mode, k)
+            assert rel2(m[k], m_ref[k]) <= 1e-4, (mode, k)
+            assert rel2(v[k], v_ref[k]) <= 1e-4, (mode, k)
+        net.close()
+
+
+@pytest.mark.parametrize("name,desc,game", [NETS[1], NETS[4]], ids=[IDS[1], IDS[4]])
+def test_hundred_step_parity(oracle32, name, desc, game):
+    B, steps = 512, 100
+    desc = dataclasses.replace(desc, max_batch=B)
+    rec = synth.records(game, B * 4, seed=23)
+    batches = [oracle32.map_batch(game, rec[i * B:(i + 1) * B], desc) for i in range(4)]
+    seq = [batches[i % 4] for i in range(steps)]
+    w = rich_weights(desc)
+    hp = AdamWParams()
+    w_ref, _, _, losses_ref = oracle32.train(desc, w, seq, 1e-3, hp)
+    net = make_net(desc, 0, w)
+    losses = []
+    for i, b in enumerate(seq):
+        net.upload(i % 3, *b)
+        net.step(i % 3, 1e-3, 1.0 / B)
+        losses.append(net.loss())
+    p = net.tensors(0)
+    assert abs(losses[-1] - losses_ref[-1]) <= 1e-3 * abs(losses_ref[-1])
+    assert losses_ref[-1] < losses_ref[0]
+    np.testing.assert_allclose(losses, losses_ref, rtol=1e-3)
+    for k in w_ref:
+        assert rel2(p[k], w_ref[k]) <= 1e-3 and relinf(p[k], w_ref[k]) <= 1e-3, k
+    net.close()
+
+
+def test_per_tensor_adamw_params_and_clipping(oracle32):
+    # 4_multi_layer.rs:90-93 sets stricter clipping on l0w and l0f only
+    name, desc, game = NETS[4]
+    B = 256
+    desc = dataclasses.replace(desc, max_batch=B)
+    batch = oracle32.map_batch(game, synth.records(game, B, seed=24), desc)
+    w = rich_weights(desc)
+    strict = AdamWParams(min_weight=-0.05, max_weight=0.05, decay=0.1)
+    hp = {k: (strict if k in ("l0w", "l0f") else AdamWParams()) for k in oracle32.zeros_like(desc)}
+    hp.update({k: AdamWParams() for k in ("l2w", "l2b", "l3w", "l3b", "l1w", "l1b", "l0b")})
+    w_ref, _, _, _ = oracle32.train(desc, w, [batch, batch], 1e-2, hp)
+    net = make_net(desc, 0, w)
+    net.set_params_for_weight("l0w", strict)
+    net.set_params_for_weight("l0f", strict)
+    for s in (0, 1):
+        net.upload(s, *batch)
+        net.step(s, 1e-2, 1.0 / B)
+    p = net.tensors(0)
+    assert np.abs(p["l0w"]).max() <= 0.05 and np.abs(w_ref["l0w"]).max() == np.float32(0.05)
+    assert np.abs(p["l1w"]).max() > 0.05
+    for k in w_ref:
+        assert rel2(p[k], w_ref[k]) <= 1e-4, k
+    net.close()
+
+
+def test_edge_batches(oracle32):
+    """One position, ragged sizes, empty feature lists, duplicate features, invalid slots."""
+    name, desc, game = NETS[4]
+    w = rich_weights(desc)
+    for B in (1, 7, 33):
+        d = dataclasses.replace(desc, max_batch=64)
+        stm, nstm, buckets, targets = oracle32.map_batch(game, synth.records(game, B, seed=30 + B), d)
+        stm, nstm = stm.copy(), nstm.copy()
+        stm[0, :] = -1                      # a perspective with no active feature at all
+        if B > 1:
+            nstm[1, 5] = nstm[1, 0]         # duplicate feature: counted twice (sparse.rs:300-313 uses one)
+            stm[B - 1, 3] = -1              # hole: later slots still count (interpreter skips, not breaks)
+            nstm[B - 1, 31] = 40000         # out of range: skipped
+        batch = (stm, nstm, buckets, targets)
+        loss_ref, g_ref, _ = oracle32.net_grad(d, w, *batch)
+        for mode in (FT_GATHER, FT_TILED):
+            net = make_net(d, mode, w)
+            net.upload(2, *batch)
+            net.backward(2)
+            net.update(0.0, 0.0)
+            assert abs(net.loss() - loss_ref) <= 1e-4 * abs(loss_ref)
+            g = net.tensors(kind=3)
+            for k in g_ref:
+                assert np.abs(g[k] - g_ref[k]).max() <= 2e-5 * max(np.abs(g_ref[k]).max(), 1e-20), (B, mode, k)
+            net.close()
+
+
+def test_feature_outside_declared_block_is_reported():
+    from bullet_b200._lib import B200Error
+
+    name, desc, game = NETS[4]
+    d = dataclasses.replace(desc, max_batch=16)
+    from oracle import Oracle
+
+    stm, nstm, buckets, targets = Oracle("f32").map_batch(game, synth.records(game, 16, seed=40), d)
+    stm = stm.copy()
+    stm[3, 1] = (stm[3, 0] + 768 * 3) % 12288   # a feature from another king bucket
+    net = make_net(d, FT_TILED, rich_weights(d))
+    net.upload(0, stm, nstm, buckets, targets)
+    net.step(0, 1e-3, 1 / 16)
+    with pytest.raises(B200Error) as e:
+        net.loss()
+    assert e.value.code == -4
+    # the gather kernels promise nothing about blocks and take the same batch
+    net2 = make_net(dataclasses.replace(d, ft_block_rows=0), 0, rich_weights(d))
+    net2.upload(0, stm, nstm, buckets, targets)
+    net2.step(0, 1e-3, 1 / 16)
+    assert np.isfinite(net2.loss())
+    net.close()
+    net2.close()
+
+
+def test_api_misuse_returns_errors():
+    from bullet_b200._lib import B200Error
+
+    d = dataclasses.replace(NETS[0][1], max_batch=8)
+    net = make_net(d)
+    with pytest.raises(B200Error) as e:
+        net.step(0, 1e-3, 1.0)          # nothing uploaded
+    assert e.value.code == -2
+    with pytest.raises(B200Error) as e:
+        net.get_tensor("l9w")
+    assert e.value.code == -1
+    with pytest.raises(B200Error) as e:
+        net.set_tensor("l0b", np.zeros(3, np.float32))
+    assert e.value.code == -1
+    stm = np.full((9, 32), -1, np.int32)
+    with pytest.raises(B200Error) as e:
+        net.upload(0, stm, stm, None, np.zeros(9, np.float32))   # over capacity
+    assert e.value.code == -1
+    from bullet_b200.net import Net
+
+    with pytest.raises(B200Error) as e:
+        Net(dataclasses.replace(d, ft_out=12))
+    assert e.value.code == -5
+    net.close()
+
+
+@pytest.mark.parametrize("ci", [0, 1, 2, 3])
+def test_full_size_configs_one_step(oracle32, ci):
+    """The benchmark configurations at their full batch size: loss, gradients, parameters."""
+    c = config(ci)
+    B = c.batch
+    rec = synth.records(c.game, B, seed=c.seed)
+    batch = oracle32.map_batch(c.game, rec, c.desc)
+    w = synth.init_weights(c.desc, seed=c.seed)
+    if c.desc.factoriser_rows:
+        w["l0f"] = np.random.default_rng(1).normal(0, 0.02, w["l0f"].size).astype(np.float32)
+    hp = AdamWParams()
+    loss_ref, g_ref, _ = oracle32.net_grad(c.desc, w, *batch)
+    w_ref = oracle32.to_real(w)
+    m_ref, v_ref = oracle32.zeros_like(c.desc), oracle32.zeros_like(c.desc)
+    oracle32.net_update(c.desc, w_ref, m_ref, v_ref, g_ref, 1.0 / B, c.lr, hp)
+    for mode in modes_for(c.desc):
+        net = make_net(c.desc, mode, w)
+        net.upload(0, *batch)
+        net.step(0, c.lr, 1.0 / B)
+        loss = net.loss()
+        assert abs(loss - loss_ref) <= 1e-4 * abs(loss_ref)
+        g, p = net.tensors(kind=3), net.tensors(0)
+        for k in g_ref:
+            assert rel2(g[k], g_ref[k]) <= 3e-5, (mode, k, rel2(g[k], g_ref[k]))
+            assert rel2(p[k], w_ref[k]) <= 1e-4 and relinf(p[k], w_ref[k]) <= 1e-4, (mode, k)
+        # size-independent properties: factoriser gradient is the bucket-sum of the table gradient
+        # in fixed order (bit-exact), and every row no position touched has an exactly zero gradient
+        if c.desc.factoriser_rows:
+            blocks = g["l0w"].reshape(-1, c.desc.factoriser_rows * c.desc.ft_out)
+            acc = blocks[0].copy()
+            for r in range(1, blocks.shape[0]):
+                acc = acc + blocks[r]
+            assert np.array_equal(acc, g["l0f"])
+        used = np.zeros(c.desc.n_inputs, bool)
+        for idx in batch[:2]:
+            used[idx[idx >= 0]] = True
+        assert not g["l0w"].reshape(c.desc.n_inputs, -1)[~used].any()
+        net.close()
