@@ -37,8 +37,8 @@ from bullet_b200.configs import AdamWParams  # noqa: E402
 
 METRIC = "train positions/sec (fwd+bwd+AdamW)"
 UNIT = "positions/s"
-GLOBAL_BATCH = 131072
-WORKLOAD = "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), global batch 131072"
+GLOBAL_BATCH = 131072  # --global-batch overrides it for profiling runs on a smaller case
+WORKLOAD = "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), global batch {}"
 N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)
 
 
@@ -163,7 +163,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "where": "host CPU cores, no GPU"},
+        "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "where": "host CPU cores, no GPU"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": what},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -334,7 +334,7 @@ def run_ours(args, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
+        "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
                    "parallelism": f"dp{world}", "ft_kernels": "tiled" if net.stat("ft_tiled") else "gather",
                    "l2": f"inputs larger than L2: {N_DISTINCT} distinct batches cycled, per-step activations "
                          f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
@@ -361,7 +361,10 @@ def main():
     ap.add_argument("--ft-mode", type=int, default=0, help="0 auto, 1 gather kernels, 2 tiled kernels")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="positions per step over all ranks (default: the benchmark's 131072)")
     args = ap.parse_args()
+    globals()["GLOBAL_BATCH"] = args.global_batch
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -17,19 +17,24 @@
 
 namespace b200 {
 
+constexpr int kDenseTile = 4;  // positions of one output bucket handled together by one warp
+
 struct DenseArgs {
     const float* x;        // [n][K1] dense-stack input
     const int* buckets;    // [n] output bucket per position
     const float* targets;  // [n]
-    int n, K1, O, n_dense;
+    const int* order;      // [n] position ids grouped by output bucket
+    const int2* tiles;     // [ntiles] (begin, count <= kDenseTile) ranges of `order`, one bucket each
+    int n, ntiles, K1, O, n_dense;
     int M[3], act[3];
     const float* W[3];
     const float* B[3];
-    float* a1;     // [n][M1] activated layer-1 output (kept for the weight gradients)
-    float* a2;     // [n][M2]
-    float* dz[3];  // gradient at each layer's selected pre-activation: [n][M_i]
-    float* out;    // [n] network output
-    float* loss;   // scalar, accumulated
+    const float* W1g;  // first-layer weights regrouped as [bucket][column][row]
+    float* a1;         // [n][M1] activated layer-1 output (kept for the weight gradients)
+    float* a2;         // [n][M2]
+    float* dz[3];      // gradient at each layer's selected pre-activation: [n][M_i]
+    float* out;        // [n] network output
+    float* loss;       // scalar, accumulated
     int want_grad;
 };
 
@@ -42,74 +47,102 @@ __device__ __forceinline__ float warp_sum(float v) {
 __device__ __forceinline__ float act_fwd(int act, float v) { return act == 0 ? v : ft_act_fwd(act, v); }
 __device__ __forceinline__ float act_bwd(int act, float y) { return act == 0 ? 1.f : ft_act_bwd(act, y); }
 
-// One warp per position: first layer as a K1-long dot product per selected row, the tiny
-// remaining layers, the loss, and the backward pass down to the first layer's
-// pre-activation gradient.  grid = ceil(n/8), block = 256.
+// l1w is stored column-major over ALL buckets' rows, so the M1 rows of one bucket for
+// consecutive columns lie O*M1 floats apart.  The kernels below read the regrouped copy
+// W1g[bucket][column][row], where a warp's 32 lanes x 4 columns x M1 rows are contiguous.
+__global__ void dense_regroup_kernel(const float* __restrict__ W1, float* __restrict__ W1g, int K1, int O, int M1) {
+    const int total = K1 * O * M1;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int r = i % M1, c = (i / M1) % K1, k = i / (M1 * K1);
+        W1g[i] = W1[(size_t)c * (O * M1) + k * M1 + r];
+    }
+}
+
+// One warp per tile of up to kDenseTile positions of the same output bucket.  The first
+// layer is a K1-long dot product per selected row with the columns split over the lanes
+// (each weight is loaded once per tile and used for every position of the tile); the tiny
+// remaining layers, the loss and the backward pass down to the first layer's
+// pre-activation gradient follow per position.  grid = ceil(ntiles/8), block = 256.
 template <int M1>
 __global__ void __launch_bounds__(256) dense_forward_kernel(DenseArgs a) {
+    constexpr int P = kDenseTile;
     __shared__ float loss_part[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int b = blockIdx.x * 8 + warp;
+    const int tile = blockIdx.x * 8 + warp;
     float my_loss = 0.f;
-    if (b < a.n) {
-        const int k = a.buckets[b];
-        const int OM1 = a.O * M1;
-        float acc[M1];
+    if (tile < a.ntiles) {
+        const int2 t = a.tiles[tile];
+        int pos[P];
 #pragma unroll
-        for (int r = 0; r < M1; r++) acc[r] = 0.f;
-        const float* xb = a.x + (size_t)b * a.K1;
-        const float* w1 = a.W[0] + k * M1;
+        for (int j = 0; j < P; j++) pos[j] = a.order[t.x + min(j, t.y - 1)];
+        const int k = a.buckets[pos[0]];
+        float acc[P][M1];
+#pragma unroll
+        for (int j = 0; j < P; j++)
+#pragma unroll
+            for (int r = 0; r < M1; r++) acc[j][r] = 0.f;
+        const float* wk = a.W1g + (size_t)k * a.K1 * M1;
         for (int c0 = lane * 4; c0 < a.K1; c0 += 128) {
-            const float4 xv = *reinterpret_cast<const float4*>(xb + c0);
-            const float xs[4] = {xv.x, xv.y, xv.z, xv.w};
+            float xs[P][4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float* wc = w1 + (size_t)(c0 + j) * OM1;
+            for (int j = 0; j < P; j++) {
+                const float4 v = *reinterpret_cast<const float4*>(a.x + (size_t)pos[j] * a.K1 + c0);
+                xs[j][0] = v.x, xs[j][1] = v.y, xs[j][2] = v.z, xs[j][3] = v.w;
+            }
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                float w[M1];
+                const float* wc = wk + (size_t)(c0 + jj) * M1;
                 if (M1 % 4 == 0) {
 #pragma unroll
                     for (int r = 0; r < M1; r += 4) {
                         const float4 wv = __ldg(reinterpret_cast<const float4*>(wc + r));
-                        acc[r] += wv.x * xs[j];
-                        acc[r + 1] += wv.y * xs[j];
-                        acc[r + 2] += wv.z * xs[j];
-                        acc[r + 3] += wv.w * xs[j];
+                        w[r] = wv.x, w[r + 1] = wv.y, w[r + 2] = wv.z, w[r + 3] = wv.w;
                     }
                 } else {
 #pragma unroll
-                    for (int r = 0; r < M1; r++) acc[r] += __ldg(wc + r) * xs[j];
+                    for (int r = 0; r < M1; r++) w[r] = __ldg(wc + r);
+                }
+#pragma unroll
+                for (int j = 0; j < P; j++)
+#pragma unroll
+                    for (int r = 0; r < M1; r++) acc[j][r] += w[r] * xs[j][jj];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < P; j++) {
+            if (j >= t.y) break;  // warp-uniform
+            const int b = pos[j];
+            float a1v[M1];
+#pragma unroll
+            for (int r = 0; r < M1; r++) a1v[r] = act_fwd(a.act[0], warp_sum(acc[j][r]) + a.B[0][k * M1 + r]);
+
+            float o;        // network output
+            float a2v = 0;  // lane r2 holds a2[r2] when there are three layers
+            if (a.n_dense == 1) {
+                o = a1v[0];
+            } else {
+                const int M2 = a.M[1], OM2 = a.O * M2;
+                float z2 = 0.f;
+                if (lane < M2) {
+#pragma unroll
+                    for (int c = 0; c < M1; c++) z2 += a.W[1][c * OM2 + k * M2 + lane] * a1v[c];
+                    z2 += a.B[1][k * M2 + lane];
+                }
+                if (a.n_dense == 2) {
+                    o = __shfl_sync(0xffffffffu, z2, 0);
+                } else {
+                    a2v = lane < M2 ? act_fwd(a.act[1], z2) : 0.f;
+                    const float term = lane < M2 ? a.W[2][lane * a.O + k] * a2v : 0.f;
+                    o = warp_sum(term) + a.B[2][k];
                 }
             }
-        }
-        float a1v[M1];
-#pragma unroll
-        for (int r = 0; r < M1; r++) a1v[r] = act_fwd(a.act[0], warp_sum(acc[r]) + a.B[0][k * M1 + r]);
+            if (lane == 0) a.out[b] = o;
+            if (!a.want_grad) continue;
 
-        float o;        // network output
-        float a2v = 0;  // lane r2 holds a2[r2] when there are three layers
-        if (a.n_dense == 1) {
-            o = a1v[0];
-        } else {
-            const int M2 = a.M[1], OM2 = a.O * M2;
-            float z2 = 0.f;
-            if (lane < M2) {
-#pragma unroll
-                for (int c = 0; c < M1; c++) z2 += a.W[1][c * OM2 + k * M2 + lane] * a1v[c];
-                z2 += a.B[1][k * M2 + lane];
-            }
-            if (a.n_dense == 2) {
-                o = __shfl_sync(0xffffffffu, z2, 0);
-            } else {
-                a2v = lane < M2 ? act_fwd(a.act[1], z2) : 0.f;
-                const float term = lane < M2 ? a.W[2][lane * a.O + k] * a2v : 0.f;
-                o = warp_sum(term) + a.B[2][k];
-            }
-        }
-        if (lane == 0) a.out[b] = o;
-
-        if (a.want_grad) {
             const float s = 1.f / (1.f + expf(-o));
             const float diff = s - a.targets[b];
-            my_loss = diff * diff;
+            my_loss += diff * diff;
             const float dout = (diff + diff) * (s * (1.f - s));
             float dz1[M1];
             if (a.n_dense == 1) {
@@ -153,41 +186,53 @@ __global__ void __launch_bounds__(256) dense_forward_kernel(DenseArgs a) {
 }
 
 // dx[b][c] = sum_r W1[c][k_b][r] * dz1[b][r]   (Matmul::backward, matmul.rs:99-126, on the
-// selected rows).  One warp per position; grid = ceil(n/8), block = 256.
+// selected rows).  One warp per tile, lanes over columns; grid = ceil(ntiles/8), block = 256.
 template <int M1>
 __global__ void __launch_bounds__(256) dense_dx_kernel(DenseArgs a, float* dx) {
+    constexpr int P = kDenseTile;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int b = blockIdx.x * 8 + warp;
-    if (b >= a.n) return;
-    const int k = a.buckets[b];
-    const int OM1 = a.O * M1;
-    float g[M1];
+    const int tile = blockIdx.x * 8 + warp;
+    if (tile >= a.ntiles) return;
+    const int2 t = a.tiles[tile];
+    int pos[P];
 #pragma unroll
-    for (int r = 0; r < M1; r++) g[r] = a.dz[0][(size_t)b * M1 + r];
-    const float* w1 = a.W[0] + k * M1;
-    float* out = dx + (size_t)b * a.K1;
+    for (int j = 0; j < P; j++) pos[j] = a.order[t.x + min(j, t.y - 1)];
+    const int k = a.buckets[pos[0]];
+    float g[P][M1];
+#pragma unroll
+    for (int j = 0; j < P; j++)
+#pragma unroll
+        for (int r = 0; r < M1; r++) g[j][r] = a.dz[0][(size_t)pos[j] * M1 + r];
+    const float* wk = a.W1g + (size_t)k * a.K1 * M1;
     for (int c0 = lane * 4; c0 < a.K1; c0 += 128) {
-        float res[4];
+        float res[P][4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float* wc = w1 + (size_t)(c0 + j) * OM1;
-            float s = 0.f;
+        for (int jj = 0; jj < 4; jj++) {
+            float w[M1];
+            const float* wc = wk + (size_t)(c0 + jj) * M1;
             if (M1 % 4 == 0) {
 #pragma unroll
                 for (int r = 0; r < M1; r += 4) {
                     const float4 wv = __ldg(reinterpret_cast<const float4*>(wc + r));
-                    s += wv.x * g[r];
-                    s += wv.y * g[r + 1];
-                    s += wv.z * g[r + 2];
-                    s += wv.w * g[r + 3];
+                    w[r] = wv.x, w[r + 1] = wv.y, w[r + 2] = wv.z, w[r + 3] = wv.w;
                 }
             } else {
 #pragma unroll
-                for (int r = 0; r < M1; r++) s += __ldg(wc + r) * g[r];
+                for (int r = 0; r < M1; r++) w[r] = __ldg(wc + r);
             }
-            res[j] = s;
+#pragma unroll
+            for (int j = 0; j < P; j++) {
+                float s = 0.f;
+#pragma unroll
+                for (int r = 0; r < M1; r++) s += w[r] * g[j][r];
+                res[j][jj] = s;
+            }
         }
-        *reinterpret_cast<float4*>(out + c0) = make_float4(res[0], res[1], res[2], res[3]);
+#pragma unroll
+        for (int j = 0; j < P; j++)
+            if (j < t.y)
+                *reinterpret_cast<float4*>(dx + (size_t)pos[j] * a.K1 + c0) =
+                    make_float4(res[j][0], res[j][1], res[j][2], res[j][3]);
     }
 }
 
@@ -261,6 +306,65 @@ __global__ void __launch_bounds__(256) dense_wgrad_kernel(WgradArgs a) {
                     for (int r = 0; r < M; r++) acc[r] += s_dy[j][r] * xv[u];
                 }
             }
+        }
+    }
+    flush();
+}
+
+// The same gradients for the narrow layers after the first (K <= 64 inputs): too few columns
+// to give every thread one, so a thread owns up to kSmallOutputs (row, column) entries of
+// the current bucket's gradient block instead.  grid = chunks, block = 256.
+constexpr int kSmallOutputs = 9;  // ceil(32 * 65 / 256)
+
+__global__ void __launch_bounds__(256) dense_wgrad_small_kernel(WgradArgs a, int M) {
+    constexpr int S = 32;
+    __shared__ int s_bucket[S];
+    __shared__ float s_x[S][65], s_dy[S][32];
+    const int K = a.K, OM = a.O * M, outputs = M * (K + 1);
+    const int begin = blockIdx.x * a.chunk_len, end = min(a.n, begin + a.chunk_len);
+    float acc[kSmallOutputs];
+    int row[kSmallOutputs], col[kSmallOutputs];
+#pragma unroll
+    for (int q = 0; q < kSmallOutputs; q++) {
+        const int o = threadIdx.x + 256 * q;
+        acc[q] = 0.f;
+        row[q] = o % M;
+        col[q] = o < outputs ? o / M : -1;
+    }
+    int cur = -1;
+    auto flush = [&]() {
+        if (cur < 0) return;
+#pragma unroll
+        for (int q = 0; q < kSmallOutputs; q++) {
+            if (col[q] >= 0 && acc[q] != 0.f)
+                atomicAdd(col[q] < K ? a.gW + (size_t)col[q] * OM + cur * M + row[q] : a.gB + cur * M + row[q], acc[q]);
+            acc[q] = 0.f;
+        }
+    };
+    for (int base = begin; base < end; base += S) {
+        const int cnt = min(S, end - base);
+        __syncthreads();
+        for (int i = threadIdx.x; i < cnt * (K + 1); i += blockDim.x) {
+            const int j = i / (K + 1), c = i % (K + 1);
+            const int pos = a.order ? a.order[base + j] : base + j;
+            s_x[j][c] = c < K ? a.X[(size_t)pos * K + c] : 1.f;
+            if (c == 0) s_bucket[j] = a.buckets[pos];
+        }
+        for (int i = threadIdx.x; i < cnt * M; i += blockDim.x) {
+            const int j = i / M, r = i % M;
+            const int pos = a.order ? a.order[base + j] : base + j;
+            s_dy[j][r] = a.dY[(size_t)pos * M + r];
+        }
+        __syncthreads();
+        for (int j = 0; j < cnt; j++) {
+            const int k = s_bucket[j];
+            if (k != cur) {
+                flush();
+                cur = k;
+            }
+#pragma unroll
+            for (int q = 0; q < kSmallOutputs; q++)
+                if (col[q] >= 0) acc[q] += s_dy[j][row[q]] * s_x[j][col[q]];
         }
     }
     flush();

@@ -15,10 +15,11 @@
 //              straight from the table (L2/HBM), gradients go out as 128-bit
 //              global reductions.  Works for any index set.
 //   *_tiled  : for inputs whose active features of one perspective all lie in one
-//              aligned block of R table rows (king buckets).  A CTA stages one
-//              R x 32-column tile in shared memory and serves every (position,
-//              perspective) of that block from it; the backward accumulates the
-//              gradient tile in shared memory and writes it out once.
+//              aligned block of R table rows (king buckets).  A forward CTA stages one
+//              R x 64-column tile of the table in shared memory and serves every
+//              (position, perspective) of that block from it; a backward CTA keeps the
+//              matching tile of the table gradient in registers and feeds it from
+//              per-row position lists built in shared memory.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -43,7 +44,7 @@ struct FtArgs {
 
 struct TileArgs {
     int block_rows;          // R
-    int nslabs, nchunks;     // H/32 column slabs; position chunks per (block, slab)
+    int nslabs, nsplit;      // H/64 column slabs; position ranges (CTAs) per (block, slab)
     const int* pair_order;   // [2n] pair ids (position*2 + perspective) grouped by block, or null = identity
     const int* block_begin;  // [nblocks+1] offsets into pair_order
     int* status;
@@ -208,19 +209,16 @@ __global__ void __launch_bounds__(256) ft_backward_gather_kernel(FtArgs a, int p
 }
 
 // ------------------------------------------------------------------ tiled kernels
-// A tile row holds 32 floats of one table row: columns [32s, 32s+32), or with
-// pairwise the 16 low-half columns [16s, 16s+16) followed by their 16 partners
-// [H/2 + 16s, H/2 + 16s + 16).  Lane l owns tile column l throughout.
+// A tile holds, for every row of one table block, 64 floats: half A then half B, 32 each.
+// Lane l owns column A[l] and column B[l].  Without pairwise A|B are 64 consecutive
+// columns [64s, 64s+64); with pairwise A is the low-half columns [32s, 32s+32) and B their
+// partners [H/2 + 32s, H/2 + 32s + 32), so a lane holds both factors of one product.
+constexpr int kTileCols = 64;
+
 template <bool PAIRWISE>
-__device__ __forceinline__ int tile_quad_col(int q, int slab, int H) {  // first column of 16-byte quad q of a tile row
-    if (PAIRWISE) return q < 4 ? slab * 16 + q * 4 : H / 2 + slab * 16 + (q - 4) * 4;
-    return slab * 32 + q * 4;
-}
+__device__ __forceinline__ int tile_col_a(int slab, int H) { return PAIRWISE ? slab * 32 : slab * 64; }
 template <bool PAIRWISE>
-__device__ __forceinline__ int tile_lane_col(int lane, int slab, int H) {
-    if (PAIRWISE) return lane < 16 ? slab * 16 + lane : H / 2 + slab * 16 + (lane - 16);
-    return slab * 32 + lane;
-}
+__device__ __forceinline__ int tile_col_b(int slab, int H) { return PAIRWISE ? H / 2 + slab * 32 : slab * 64 + 32; }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -233,21 +231,20 @@ struct TileWork {
 };
 __device__ __forceinline__ TileWork tile_work(const TileArgs& t) {
     TileWork w;
-    const int chunk = blockIdx.x % t.nchunks;
-    const int rest = blockIdx.x / t.nchunks;
+    const int split = blockIdx.x % t.nsplit;
+    const int rest = blockIdx.x / t.nsplit;
     w.slab = rest % t.nslabs;
     w.block = rest / t.nslabs;
     const int b0 = t.block_begin[w.block], cnt = t.block_begin[w.block + 1] - b0;
-    w.begin = b0 + (int)(((long long)cnt * chunk) / t.nchunks);
-    w.end = b0 + (int)(((long long)cnt * (chunk + 1)) / t.nchunks);
+    w.begin = b0 + (int)(((long long)cnt * split) / t.nsplit);
+    w.end = b0 + (int)(((long long)cnt * (split + 1)) / t.nsplit);
     return w;
 }
 
-// Loads one position's slots and turns them into tile offsets (row * 32).  Returns
-// the masks of usable slots; a valid feature outside the block raises the status
-// bit and is dropped rather than read out of bounds.
-__device__ __forceinline__ void tile_slots(const FtArgs& a, const TileArgs& t, int block, int pair, int lane,
-                                           int (&off)[2], unsigned (&mask)[2]) {
+// One position's slots as table rows local to `block`.  A valid feature outside the block
+// raises the status bit and is dropped rather than read out of bounds.
+__device__ __forceinline__ void tile_rows(const FtArgs& a, const TileArgs& t, int block, int pair, int lane,
+                                          int (&row)[2], unsigned (&mask)[2]) {
     const int b = pair >> 1, p = pair & 1;
     const uint16_t* list = (p ? a.idx_nstm : a.idx_stm) + (size_t)b * a.nnz;
     uint32_t slot[2];
@@ -255,134 +252,236 @@ __device__ __forceinline__ void tile_slots(const FtArgs& a, const TileArgs& t, i
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const bool valid = slot[h] < (uint32_t)a.n_inputs;
-        const int local = (int)slot[h] - block * t.block_rows;
-        const bool inside = valid && (unsigned)local < (unsigned)t.block_rows;
+        row[h] = (int)slot[h] - block * t.block_rows;
+        const bool inside = valid && (unsigned)row[h] < (unsigned)t.block_rows;
         if (valid && !inside) atomicOr(t.status, kStatusOutsideBlock);
-        off[h] = inside ? local * 32 : 0;
         mask[h] = __ballot_sync(0xffffffffu, inside);
     }
 }
 
-// grid = nblocks * nslabs * nchunks CTAs of 512 threads; dynamic smem = R*32 floats.
+// Forward.  grid = nblocks * nslabs * nsplit CTAs of 1024 threads (one per SM); dynamic
+// shared memory = R*64 floats for the tile + 32 warps * 72 ints of per-warp offset lists.
+// Each warp serves one (position, perspective) at a time: its lanes compact the position's
+// valid rows into the warp's offset list, then every lane adds its two tile columns over
+// that list in slot order — the same order and arithmetic as the interpreter.
 template <bool PAIRWISE>
-__global__ void __launch_bounds__(512, 2) ft_forward_tiled_kernel(FtArgs a, TileArgs t) {
-    extern __shared__ __align__(16) float tile[];
+__global__ void __launch_bounds__(1024, 1) ft_forward_tiled_kernel(FtArgs a, TileArgs t) {
+    extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const TileWork w = tile_work(t);
     const int R = t.block_rows;
-    for (int i = threadIdx.x; i < R * 8; i += blockDim.x) {
-        const int row = i >> 3, q = i & 7;
-        cp_async16(&tile[row * 32 + q * 4],
-                   a.table + (size_t)(w.block * R + row) * a.H + tile_quad_col<PAIRWISE>(q, w.slab, a.H));
+    float* tile = smem;
+    int* offs = reinterpret_cast<int*>(smem + (size_t)R * kTileCols) + warp * 72;
+    const int col_a = tile_col_a<PAIRWISE>(w.slab, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, a.H);
+    for (int i = threadIdx.x; i < R * 16; i += blockDim.x) {
+        const int row = i >> 4, q = i & 15;
+        const int col = q < 8 ? col_a + q * 4 : col_b + (q - 8) * 4;
+        cp_async16(&tile[row * kTileCols + q * 4], a.table + (size_t)(w.block * R + row) * a.H + col);
     }
-    const int col = tile_lane_col<PAIRWISE>(lane, w.slab, a.H);
-    const float bias = a.bias[col];
+    for (int i = lane; i < 72; i += 32) offs[i] = 0;
+    const float bias_a = a.bias[col_a + lane], bias_b = a.bias[col_b + lane];
     cp_async_wait_all();
     __syncthreads();
     const float* mine = tile + lane;
     for (int i = w.begin + warp; i < w.end; i += nwarps) {
         const int pair = t.pair_order ? t.pair_order[i] : i;
-        int off[2];
+        int row[2];
         unsigned mask[2];
-        tile_slots(a, t, w.block, pair, lane, off, mask);
-        float acc = 0.f;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            unsigned m = mask[h];
-            if (m == 0) continue;
-            const int cnt = __popc(m);
-            if (m == (cnt == 32 ? 0xffffffffu : (1u << cnt) - 1u)) {  // usual case: a prefix of the slots
-                for (int k = 0; k < cnt; k += 4) {
-                    const int o0 = __shfl_sync(0xffffffffu, off[h], k);
-                    const int o1 = __shfl_sync(0xffffffffu, off[h], (k + 1) & 31);
-                    const int o2 = __shfl_sync(0xffffffffu, off[h], (k + 2) & 31);
-                    const int o3 = __shfl_sync(0xffffffffu, off[h], (k + 3) & 31);
-                    const float v0 = mine[o0], v1 = mine[o1], v2 = mine[o2], v3 = mine[o3];
-                    acc += v0;
-                    if (k + 1 < cnt) acc += v1;
-                    if (k + 2 < cnt) acc += v2;
-                    if (k + 3 < cnt) acc += v3;
-                }
-            } else {
-                while (m) {
-                    const int s = __ffs(m) - 1;
-                    m &= m - 1;
-                    acc += mine[__shfl_sync(0xffffffffu, off[h], s)];
-                }
-            }
+        tile_rows(a, t, w.block, pair, lane, row, mask);
+        const unsigned lt = (1u << lane) - 1u;
+        const int cnt0 = __popc(mask[0]), cnt = cnt0 + __popc(mask[1]);
+        __syncwarp();  // the previous position's list has been read by every lane
+        if (mask[0] >> lane & 1) offs[__popc(mask[0] & lt)] = row[0] * kTileCols;
+        if (mask[1] >> lane & 1) offs[cnt0 + __popc(mask[1] & lt)] = row[1] * kTileCols;
+        __syncwarp();
+        float acc_a = 0.f, acc_b = 0.f;
+        for (int k = 0; k < cnt; k += 4) {
+            const int4 o = *reinterpret_cast<const int4*>(offs + k);  // entries past cnt are stale but in range
+            const float a0 = mine[o.x], b0 = mine[o.x + 32];
+            const float a1 = mine[o.y], b1 = mine[o.y + 32];
+            const float a2 = mine[o.z], b2 = mine[o.z + 32];
+            const float a3 = mine[o.w], b3 = mine[o.w + 32];
+            acc_a += a0, acc_b += b0;
+            if (k + 1 < cnt) acc_a += a1, acc_b += b1;
+            if (k + 2 < cnt) acc_a += a2, acc_b += b2;
+            if (k + 3 < cnt) acc_a += a3, acc_b += b3;
         }
-        const float v = acc + bias;
+        const float va = acc_a + bias_a, vb = acc_b + bias_b;
         const int b = pair >> 1, p = pair & 1;
         if (PAIRWISE) {
-            const float uval = crelu_f(v);
-            a.u[(size_t)pair * a.H + col] = uval;
-            const float other = __shfl_xor_sync(0xffffffffu, uval, 16);
-            if (lane < 16) a.x[(size_t)b * a.H + (size_t)p * (a.H / 2) + w.slab * 16 + lane] = uval * other;
+            const float ua = crelu_f(va), ub = crelu_f(vb);
+            a.u[(size_t)pair * a.H + col_a + lane] = ua;
+            a.u[(size_t)pair * a.H + col_b + lane] = ub;
+            a.x[(size_t)b * a.H + (size_t)p * (a.H / 2) + col_a + lane] = ua * ub;
         } else {
-            a.x[(size_t)b * 2 * a.H + (size_t)p * a.H + col] = ft_act_fwd(a.act, v);
+            float* xp = a.x + (size_t)b * 2 * a.H + (size_t)p * a.H;
+            xp[col_a + lane] = ft_act_fwd(a.act, va);
+            xp[col_b + lane] = ft_act_fwd(a.act, vb);
         }
     }
 }
 
-// Same grid.  With nchunks == 1 each CTA owns its tile of the table gradient and
-// stores it (no zeroing needed); otherwise tiles are added into a zeroed table.
+// Backward.  Same grid, 512 threads.  The CTA's slice of the table gradient (R rows x 64
+// columns) lives in registers: warp w owns rows w, w+16, ... (up to 48), lane l their
+// columns A[l] and B[l].  Positions are taken in chunks; per chunk the CTA
+//   1. builds in shared memory a row-major list (CSR) of which positions of the chunk hold
+//      each row — a count pass, a scan and a fill pass over the chunk's slots, and
+//   2. stages the chunk's pre-activation gradients (from dx and the kept activations), then
+//   3. every warp walks the lists of its own rows and adds the staged gradients into its
+//      registers: no atomics on the accumulators, no shared-memory copy of the tile.
+// With nsplit == 1 the finished slice is stored (no zeroing needed); otherwise slices of
+// different position ranges are added into a zeroed table.
+constexpr int kBwdThreads = 512, kBwdRowsPerWarp = 48;
+
+__host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? 512 : 256; }
+__host__ __device__ inline size_t ft_bwd_smem(int R, int nnz) {
+    const int cp = ft_bwd_chunk(nnz);
+    return (size_t)cp * kTileCols * 4 + (size_t)cp * nnz * 2 + (size_t)(2 * R + 2 + 32) * 4;
+}
+
 template <bool PAIRWISE>
-__global__ void __launch_bounds__(512, 2) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
-    extern __shared__ __align__(16) float tile[];
-    __shared__ float bias_red[16][32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+__global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
+    extern __shared__ __align__(16) float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int NW = kBwdThreads / 32;
     const TileWork w = tile_work(t);
-    const int R = t.block_rows;
-    for (int i = threadIdx.x; i < R * 8; i += blockDim.x) reinterpret_cast<float4*>(tile)[i] = make_float4(0, 0, 0, 0);
-    __syncthreads();
-    const int col = tile_lane_col<PAIRWISE>(lane, w.slab, a.H);
-    float* mine = tile + lane;
-    float bsum = 0.f;
-    for (int i = w.begin + warp; i < w.end; i += nwarps) {
-        const int pair = t.pair_order ? t.pair_order[i] : i;
-        const int b = pair >> 1, p = pair & 1;
-        float g;
-        if (PAIRWISE) {
-            const float uval = a.u[(size_t)pair * a.H + col];
-            const float other = __shfl_xor_sync(0xffffffffu, uval, 16);
-            const float d = a.dx[(size_t)b * a.H + (size_t)p * (a.H / 2) + w.slab * 16 + (lane & 15)];
-            g = (d * other) * ft_act_bwd(1, uval);
-        } else {
-            const size_t at = (size_t)b * 2 * a.H + (size_t)p * a.H + col;
-            g = a.dx[at] * ft_act_bwd(a.act, a.x[at]);
-        }
-        if (!__any_sync(0xffffffffu, g != 0.f)) continue;  // the reference skips zero gradients too
-        bsum += g;
-        int off[2];
-        unsigned mask[2];
-        tile_slots(a, t, w.block, pair, lane, off, mask);
+    const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz);
+    float* g_s = smem;                                                       // [CP][64]
+    uint16_t* ent = reinterpret_cast<uint16_t*>(smem + (size_t)CP * kTileCols);  // [CP * nnz]
+    int* start = reinterpret_cast<int*>(ent + (size_t)CP * a.nnz);           // [R + 1]
+    int* cursor = start + R + 1;                                             // [R]
+    int* warp_tot = cursor + R + 1;                                          // [NW] (+ slack)
+    const int col_a = tile_col_a<PAIRWISE>(w.slab, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, a.H);
+
+    float acc_a[kBwdRowsPerWarp], acc_b[kBwdRowsPerWarp];
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            unsigned m = mask[h];
-            while (m) {
-                const int s = __ffs(m) - 1;
-                m &= m - 1;
-                const int o = __shfl_sync(0xffffffffu, off[h], s);
-                if (g != 0.f) atomicAdd(mine + o, g);
+    for (int j = 0; j < kBwdRowsPerWarp; j++) acc_a[j] = acc_b[j] = 0.f;
+    float bsum_a = 0.f, bsum_b = 0.f;
+
+    for (int c0 = w.begin; c0 < w.end; c0 += CP) {
+        const int cn = min(CP, w.end - c0);
+        for (int r = threadIdx.x; r < R; r += kBwdThreads) cursor[r] = 0;
+        __syncthreads();
+        // count rows, and stage this chunk's gradients at the feature-transformer pre-activation
+        for (int pl = warp; pl < cn; pl += NW) {
+            const int pair = t.pair_order ? t.pair_order[c0 + pl] : c0 + pl;
+            int row[2];
+            unsigned mask[2];
+            tile_rows(a, t, w.block, pair, lane, row, mask);
+            if (mask[0] >> lane & 1) atomicAdd(&cursor[row[0]], 1);
+            if (mask[1] >> lane & 1) atomicAdd(&cursor[row[1]], 1);
+            const int b = pair >> 1, p = pair & 1;
+            float ga, gb;
+            if (PAIRWISE) {
+                const float ua = a.u[(size_t)pair * a.H + col_a + lane], ub = a.u[(size_t)pair * a.H + col_b + lane];
+                const float d = a.dx[(size_t)b * a.H + (size_t)p * (a.H / 2) + col_a + lane];
+                ga = (d * ub) * ft_act_bwd(1, ua);
+                gb = (d * ua) * ft_act_bwd(1, ub);
+            } else {
+                const size_t at = (size_t)b * 2 * a.H + (size_t)p * a.H;
+                ga = a.dx[at + col_a + lane] * ft_act_bwd(a.act, a.x[at + col_a + lane]);
+                gb = a.dx[at + col_b + lane] * ft_act_bwd(a.act, a.x[at + col_b + lane]);
+            }
+            g_s[pl * kTileCols + lane] = ga;
+            g_s[pl * kTileCols + 32 + lane] = gb;
+            bsum_a += ga;
+            bsum_b += gb;
+        }
+        __syncthreads();
+        // exclusive scan of the row counts -> start[], cursor[] = start[]
+        {
+            int carry = 0;  // rows are scanned in rounds of kBwdThreads
+            for (int base = 0; base < R; base += kBwdThreads) {
+                const int r = base + threadIdx.x;
+                const int v = r < R ? cursor[r] : 0;
+                int incl = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += n;
+                }
+                if (lane == 31) warp_tot[warp] = incl;
+                __syncthreads();
+                int before = carry;
+                for (int k = 0; k < warp; k++) before += warp_tot[k];
+                int total = 0;
+                for (int k = 0; k < NW; k++) total += warp_tot[k];
+                if (r < R) {
+                    start[r] = before + incl - v;
+                    cursor[r] = before + incl - v;
+                }
+                carry += total;
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) start[R] = carry;
+        }
+        __syncthreads();
+        // fill: entry = position of the chunk, grouped by row
+        for (int pl = warp; pl < cn; pl += NW) {
+            const int pair = t.pair_order ? t.pair_order[c0 + pl] : c0 + pl;
+            const int b = pair >> 1, p = pair & 1;
+            const uint16_t* list = (p ? a.idx_nstm : a.idx_stm) + (size_t)b * a.nnz;
+            uint32_t slot[2];
+            load_slots(list, a.nnz, lane, slot[0], slot[1]);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int row = (int)slot[h] - w.block * R;
+                if (slot[h] < (uint32_t)a.n_inputs && (unsigned)row < (unsigned)R)
+                    ent[atomicAdd(&cursor[row], 1)] = (uint16_t)pl;
             }
         }
+        __syncthreads();
+        // accumulate: each warp walks the lists of the rows it owns
+#pragma unroll
+        for (int j = 0; j < kBwdRowsPerWarp; j++) {
+            const int row = warp + NW * j;
+            if (row < R) {
+                const int e1 = start[row + 1];
+                const float* gl = g_s + lane;
+                int e = start[row];
+                for (; e + 4 <= e1; e += 4) {
+                    const int p0 = ent[e], p1 = ent[e + 1], p2 = ent[e + 2], p3 = ent[e + 3];
+                    const float a0 = gl[p0 * kTileCols], b0 = gl[p0 * kTileCols + 32];
+                    const float a1 = gl[p1 * kTileCols], b1 = gl[p1 * kTileCols + 32];
+                    const float a2 = gl[p2 * kTileCols], b2 = gl[p2 * kTileCols + 32];
+                    const float a3 = gl[p3 * kTileCols], b3 = gl[p3 * kTileCols + 32];
+                    acc_a[j] += a0, acc_b[j] += b0;
+                    acc_a[j] += a1, acc_b[j] += b1;
+                    acc_a[j] += a2, acc_b[j] += b2;
+                    acc_a[j] += a3, acc_b[j] += b3;
+                }
+                for (; e < e1; e++) {
+                    const int p0 = ent[e];
+                    acc_a[j] += gl[p0 * kTileCols];
+                    acc_b[j] += gl[p0 * kTileCols + 32];
+                }
+            }
+        }
+        __syncthreads();
     }
-    bias_red[warp][lane] = bsum;
+    // bias gradient: every position's gradient once, summed over the warps
+    g_s[warp * kTileCols + lane] = bsum_a;
+    g_s[warp * kTileCols + 32 + lane] = bsum_b;
     __syncthreads();
-    if (warp == 0) {
+    if (threadIdx.x < kTileCols) {
         float s = 0.f;
-        for (int k = 0; k < nwarps; k++) s += bias_red[k][lane];
+        for (int k = 0; k < NW; k++) s += g_s[k * kTileCols + threadIdx.x];
+        const int col = threadIdx.x < 32 ? col_a + threadIdx.x : col_b + threadIdx.x - 32;
         if (s != 0.f) atomicAdd(a.g_bias + col, s);
     }
-    for (int i = threadIdx.x; i < R * 8; i += blockDim.x) {
-        const int row = i >> 3, q = i & 7;
-        const float4 v = reinterpret_cast<const float4*>(tile)[i];
-        float4* dst = reinterpret_cast<float4*>(a.g_table + (size_t)(w.block * R + row) * a.H +
-                                                tile_quad_col<PAIRWISE>(q, w.slab, a.H));
-        if (t.nchunks == 1)
-            *dst = v;
-        else if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f)
-            atomicAdd(dst, v);
+#pragma unroll
+    for (int j = 0; j < kBwdRowsPerWarp; j++) {
+        const int row = warp + NW * j;
+        if (row < R) {
+            float* dst = a.g_table + (size_t)(w.block * R + row) * a.H;
+            if (t.nsplit == 1) {
+                dst[col_a + lane] = acc_a[j];
+                dst[col_b + lane] = acc_b[j];
+            } else {
+                if (acc_a[j] != 0.f) atomicAdd(dst + col_a + lane, acc_a[j]);
+                if (acc_b[j] != 0.f) atomicAdd(dst + col_b + lane, acc_b[j]);
+            }
+        }
     }
 }
 

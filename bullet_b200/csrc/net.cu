@@ -60,8 +60,9 @@ struct Slot {
     char* h_blob = nullptr;
     size_t capacity = 0;
     int n = 0;
+    int n_dtiles = 0;  // warp tiles of the dense kernels held in off_dtiles
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
-           bytes = 0;
+           off_dtiles = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
     bool has_ready = false, has_consumed = false;
     template <class T>
@@ -82,7 +83,7 @@ struct b200_net {
     std::vector<Tensor> tensors;
     int64_t n_flat = 0;
     float *P = nullptr, *G = nullptr, *M = nullptr, *V = nullptr, *table = nullptr;
-    float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr;
+    float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr, *w1g = nullptr;
     float* dz[3] = {nullptr, nullptr, nullptr};
     int* status = nullptr;
     int* h_status = nullptr;
@@ -170,14 +171,16 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.off_order = take((size_t)n * 4);
     s.off_pairs = take((size_t)n * 8);
     s.off_blocks = take((size_t)(net->nblocks + 1) * 4);
+    s.off_dtiles = take(((size_t)n / b200::kDenseTile + d.n_out_buckets + 1) * 8);
     s.bytes = off;
 }
+
+size_t fwd_tile_smem(int block_rows) { return (size_t)block_rows * b200::kTileCols * 4 + 32 * 72 * 4; }
 
 template <bool PW>
 int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
     if (tiled) {
-        const size_t smem = (size_t)t.block_rows * 32 * sizeof(float);
-        b200::ft_forward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nchunks, 512, smem, net->stream>>>(a, t);
+        b200::ft_forward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nsplit, 1024, fwd_tile_smem(t.block_rows), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -190,8 +193,8 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
     if (tiled) {
-        const size_t smem = (size_t)t.block_rows * 32 * sizeof(float);
-        b200::ft_backward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nchunks, 512, smem, net->stream>>>(a, t);
+        b200::ft_backward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nsplit, b200::kBwdThreads,
+                                             b200::ft_bwd_smem(t.block_rows, a.nnz), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -212,13 +215,24 @@ int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArg
         default: return b200::fail(B200_ERR_UNSUPPORTED, "rows per bucket %d", m); \
     }
 
-int tiles_for(const b200_net* net, int n) {
-    // position chunks per (block, slab) so that the grid fills the machine; each chunk
-    // should still amortise its tile load over at least ~64 (position, perspective) pairs
-    const int base = net->nblocks * net->nslabs;
-    int chunks = (kTargetCtas + base - 1) / base;
-    const int most = std::max(1, (2 * n) / (64 * net->nblocks));
-    return std::max(1, std::min(chunks, most));
+// Position ranges (CTAs) per (block, slab) tile.  One CTA is resident per SM, so the grid
+// runs in waves of kSmCount; splitting a tile's positions over more CTAs evens out the last
+// wave but repeats the tile's fixed cost (`overhead`, as a fraction of a whole tile's work:
+// the tile load in the forward, the atomic flush in the backward).
+int splits_for(const b200_net* net, int n, double overhead) {
+    const int tiles = net->nblocks * net->nslabs;
+    const int most = std::max(1, std::min(512, (2 * n) / (128 * net->nblocks)));
+    int best = 1;
+    double best_cost = 1e30;
+    for (int sp = 1; sp <= most; sp++) {
+        const double waves = (double)((tiles * sp + kSmCount - 1) / kSmCount);
+        const double cost = waves * (1.0 / sp + overhead);
+        if (cost < best_cost * 0.98) {
+            best_cost = cost;
+            best = sp;
+        }
+    }
+    return best;
 }
 
 b200::FtArgs ft_args(b200_net* net, const Slot& s) {
@@ -241,11 +255,11 @@ b200::FtArgs ft_args(b200_net* net, const Slot& s) {
     return a;
 }
 
-b200::TileArgs tile_args(b200_net* net, const Slot& s, int nchunks) {
+b200::TileArgs tile_args(b200_net* net, const Slot& s, int nsplit) {
     b200::TileArgs t{};
     t.block_rows = net->d.ft_block_rows;
     t.nslabs = net->nslabs;
-    t.nchunks = nchunks;
+    t.nsplit = nsplit;
     t.pair_order = net->nblocks > 1 ? s.dev<int>(s.off_pairs) : nullptr;
     t.block_begin = s.dev<int>(s.off_blocks);
     t.status = net->status;
@@ -272,6 +286,10 @@ b200::DenseArgs dense_args(b200_net* net, const Slot& s, bool want_grad) {
         a.B[l] = net->P + net->find(name)->off;
         a.dz[l] = net->dz[l];
     }
+    a.order = s.dev<int>(s.off_order);
+    a.tiles = s.dev<int2>(s.off_dtiles);
+    a.ntiles = s.n_dtiles;
+    a.W1g = net->w1g;
     a.a1 = net->a1;
     a.a2 = net->a2;
     a.out = net->out;
@@ -291,6 +309,12 @@ int refresh_table(b200_net* net) {
             reinterpret_cast<float4*>(net->table), n4, block4);
         LAUNCHED(net);
     }
+    {
+        const Tensor* w1 = net->find("l1w");
+        b200::dense_regroup_kernel<<<std::min<int>(kSmCount * 4, (int)((w1->n + 255) / 256)), 256, 0, net->stream>>>(
+            net->P + w1->off, net->w1g, net->D1(), net->d.n_out_buckets, net->d.dense_out[0]);
+        LAUNCHED(net);
+    }
     net->table_dirty = false;
     return 0;
 }
@@ -307,12 +331,12 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
     const b200_net_desc& d = net->d;
     const bool tiled = net->use_tiled();
     b200::FtArgs fa = ft_args(net, s);
-    b200::TileArgs ta = tile_args(net, s, tiled ? tiles_for(net, s.n) : 1);
+    b200::TileArgs ta = tile_args(net, s, tiled ? splits_for(net, s.n, 0.1) : 1);
     int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled) : launch_ft_forward<false>(net, fa, ta, tiled);
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
     b200::DenseArgs da = dense_args(net, s, want_grad);
-    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<(s.n + 7) / 8, 256, 0, net->stream>>>(da));
+    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<(s.n_dtiles + 7) / 8, 256, 0, net->stream>>>(da));
     LAUNCHED(net);
     return 0;
 }
@@ -332,6 +356,13 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
     w.gW = net->G + net->find(name)->off;
     snprintf(name, sizeof name, "l%db", layer + 1);
     w.gB = net->G + net->find(name)->off;
+    if (layer > 0) {  // narrow layers: one CTA per chunk of positions, threads over (row, column)
+        const int chunks = std::max(1, std::min((s.n + 63) / 64, 2 * kSmCount));
+        w.chunk_len = ((s.n + chunks - 1) / chunks + 31) / 32 * 32;
+        b200::dense_wgrad_small_kernel<<<(s.n + w.chunk_len - 1) / w.chunk_len, 256, 0, net->stream>>>(w, d.dense_out[layer]);
+        LAUNCHED(net);
+        return 0;
+    }
     const int threads = w.K + 1 >= 256 ? 256 : ((w.K + 1 + 31) / 32) * 32;
     const int gx = (w.K + 1 + threads - 1) / threads;
     int chunks = std::max(1, std::min((s.n + 63) / 64, kTargetCtas / gx));
@@ -401,10 +432,10 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     }
     net->n_flat = off;
 
-    net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % 32 == 0 &&
-                    (size_t)d.ft_block_rows * 128 <= 200 * 1024;
+    net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
+                    d.ft_block_rows <= b200::kBwdRowsPerWarp * (b200::kBwdThreads / 32);
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
-    net->nslabs = d.ft_out / 32;
+    net->nslabs = d.ft_out / b200::kTileCols;
 
     const size_t B = d.max_batch;
     int rc = 0;
@@ -420,6 +451,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     rc = rc ? rc : dev_alloc(net, &net->a2, B * 32);
     for (int l = 0; l < 3; l++) rc = rc ? rc : dev_alloc(net, &net->dz[l], B * 32);
     rc = rc ? rc : dev_alloc(net, &net->out, B);
+    rc = rc ? rc : dev_alloc(net, &net->w1g, (size_t)d.n_out_buckets * d.dense_out[0] * net->D1());
     rc = rc ? rc : dev_alloc(net, &net->status, 1);
     if (rc) return bail(rc);
     if (!d.factoriser_rows) net->table = net->P + net->find("l0w")->off;
@@ -451,11 +483,11 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         for (auto& e : ring) cudaEventCreate(&e);
 
     if (net->tiled_ok) {
-        const int smem = d.ft_block_rows * 128;
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        const int fs = (int)fwd_tile_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
     }
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaGetLastError());
@@ -493,7 +525,7 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
         if (value == B200_FT_TILED && !net->tiled_ok)
             return b200::fail(B200_ERR_UNSUPPORTED,
                               "tiled feature-transformer kernels need ft_block_rows > 0 dividing n_inputs, at most "
-                              "1600 rows per block, and ft_out a multiple of 32");
+                              "768 rows per block, and ft_out a multiple of 64");
         net->ft_mode = (int)value;
         return 0;
     }
@@ -601,6 +633,15 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         for (int i = 0; i < n; i++) begin[h_buckets[i] + 1]++;
         for (int k = 0; k < O; k++) begin[k + 1] += begin[k];
         for (int i = 0; i < n; i++) h_order[begin[h_buckets[i]]++] = i;
+        // warp tiles of the dense kernels: runs of up to kDenseTile positions of one bucket;
+        // after the scatter begin[k] is the END of bucket k's run
+        int2* h_tiles = s.host<int2>(s.off_dtiles);
+        int nt = 0, at = 0;
+        for (int k = 0; k < O; k++) {
+            for (; at < begin[k]; at += b200::kDenseTile) h_tiles[nt++] = make_int2(at, std::min(b200::kDenseTile, begin[k] - at));
+            at = begin[k];
+        }
+        s.n_dtiles = nt;
     }
     // visiting order of the tiled feature-transformer kernels: (position, perspective)
     // pairs grouped by the table row block their features live in
@@ -649,7 +690,7 @@ int b200_backward(b200_net* net, int slot) {
     CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
     if (int rc = refresh_table(net)) return rc;
     const bool tiled = net->use_tiled();
-    const int chunks = tiled ? tiles_for(net, s.n) : 1;
+    const int chunks = tiled ? splits_for(net, s.n, 0.3) : 1;
     const Tensor* l0w = net->find("l0w");
     const size_t total = (size_t)net->n_flat + kAlignFloats;
     if (tiled && chunks == 1) {
@@ -668,7 +709,7 @@ int b200_backward(b200_net* net, int slot) {
         if (int rc = launch_wgrad(net, s, l)) return rc;
     {
         b200::DenseArgs da = dense_args(net, s, true);
-        DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<(s.n + 7) / 8, 256, 0, net->stream>>>(da, net->dx));
+        DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<(s.n_dtiles + 7) / 8, 256, 0, net->stream>>>(da, net->dx));
         LAUNCHED(net);
     }
     CK(cudaEventRecord(ev[3], net->stream));

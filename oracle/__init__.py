@@ -57,6 +57,10 @@ class Oracle:
     def _i(a):
         return np.ascontiguousarray(a, dtype=np.int32)
 
+    def _scalar(self, v):
+        """Scalars reach the reference's kernels as f32; the f64 arbiter gets the same rounded values."""
+        return self.creal(float(np.float32(v)))
+
     def threads(self) -> int:
         return int(self.lib.orc_max_threads())
 
@@ -132,7 +136,7 @@ class Oracle:
 
     def adamw(self, p, m, v, g, adj, rate, hp):
         """In place on p, m, v (arrays of this oracle's precision)."""
-        c = self.creal
+        c = self._scalar
         self.lib.orc_adamw(_ptr(p), _ptr(m), _ptr(v), _ptr(g), ctypes.c_size_t(p.size), c(adj), c(rate),
                            c(hp.decay), c(hp.beta1), c(hp.beta2), c(hp.min_weight), c(hp.max_weight))
 
@@ -242,7 +246,7 @@ class Oracle:
         table = (HP * 9)()
         for i, name in enumerate(_HP_ORDER):
             p = hp[name] if isinstance(hp, dict) else hp
-            table[i] = HP(p.decay, p.beta1, p.beta2, p.min_weight, p.max_weight)
+            table[i] = HP(*[float(np.float32(x)) for x in (p.decay, p.beta1, p.beta2, p.min_weight, p.max_weight)])
         for d in (weights, m, v, grads):
             for k, a in d.items():
                 assert a.dtype == self.real and a.flags.c_contiguous, k
@@ -251,7 +255,7 @@ class Oracle:
         vs, _ = self._pack(desc, v)
         gs, _ = self._pack(desc, grads)
         self.lib.orc_net_update(ctypes.byref(cdesc), ctypes.byref(ws), ctypes.byref(ms), ctypes.byref(vs),
-                                ctypes.byref(gs), self.creal(adj), self.creal(rate), table)
+                                ctypes.byref(gs), self._scalar(adj), self._scalar(rate), table)
 
     def train(self, desc, weights, batches, lr, hp, grad_factor=None):
         """Run AdamW steps over `batches` (iterable of (stm, nstm, buckets, targets)).

@@ -80,18 +80,20 @@ def test_adamw_formula(oracle32, oracle64):
     p0, g = rng.normal(0, 0.05, n), rng.normal(0, 1, n)
     m0, v0 = rng.normal(0, 0.1, n), rng.random(n)
     adj, lr = 1.0 / 16384, 1e-3
-    gg = adj * g
-    pe = p0 * (1 - hp.decay * lr)
-    me = hp.beta1 * m0 + (1 - hp.beta1) * gg
-    ve = hp.beta2 * v0 + (1 - hp.beta2) * gg * gg
-    pe = np.clip(pe - lr * me / (np.sqrt(ve) + 1e-8), hp.min_weight, hp.max_weight)
+    # every scalar reaches the kernel as an f32 (adam.rs:97-110 formats them into the source)
+    f = lambda v: float(np.float32(v))  # noqa: E731
+    gg = f(adj) * g
+    pe = p0 * (1 - f(hp.decay) * f(lr))
+    me = f(hp.beta1) * m0 + (1 - f(hp.beta1)) * gg
+    ve = f(hp.beta2) * v0 + (1 - f(hp.beta2)) * gg * gg
+    pe = np.clip(pe - f(lr) * me / (np.sqrt(ve) + f(1e-8)), f(hp.min_weight), f(hp.max_weight))
     for orc, tol in ((oracle64, 1e-12), (oracle32, 1e-6)):
         p, m, v = (np.array(a, dtype=orc.real) for a in (p0, m0, v0))
         orc.adamw(p, m, v, np.array(g, dtype=orc.real), adj, lr, hp)
         np.testing.assert_allclose(p, pe, rtol=tol, atol=tol)
         np.testing.assert_allclose(m, me, rtol=tol, atol=tol)
         np.testing.assert_allclose(v, ve, rtol=tol, atol=tol)
-    assert np.any(pe == hp.max_weight) and np.any(pe == hp.min_weight)
+    assert np.any(pe == f(hp.max_weight)) and np.any(pe == f(hp.min_weight))
 
 
 def _small_nets():
