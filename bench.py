@@ -216,6 +216,10 @@ def run_ours(args, rank, world, local_rank):
     net = Net(desc, device=local_rank, stream=stream.cuda_stream)
     if args.ft_mode:
         net.set_option("ft_mode", args.ft_mode)
+    if args.ft_fwd_mode:
+        net.set_option("ft_fwd_mode", args.ft_fwd_mode)
+    if args.ft_bwd_mode:
+        net.set_option("ft_bwd_mode", args.ft_bwd_mode)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
     gptr, gcount = net.grad_buffer()
 
@@ -335,7 +339,8 @@ def run_ours(args, rank, world, local_rank):
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
-                   "parallelism": f"dp{world}", "ft_kernels": "tiled" if net.stat("ft_tiled") else "gather",
+                   "parallelism": f"dp{world}", "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
+                                  "backward": "tiled" if net.stat("ft_tiled") & 2 else "gather"},
                    "l2": f"inputs larger than L2: {N_DISTINCT} distinct batches cycled, per-step activations "
                          f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
                    "active_features_per_position": rows / n_local},
@@ -359,6 +364,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ft-mode", type=int, default=0, help="0 auto, 1 gather kernels, 2 tiled kernels")
+    ap.add_argument("--ft-fwd-mode", type=int, default=0)
+    ap.add_argument("--ft-bwd-mode", type=int, default=0)
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,

@@ -243,12 +243,8 @@ __device__ __forceinline__ TileWork tile_work(const TileArgs& t) {
 
 // One position's slots as table rows local to `block`.  A valid feature outside the block
 // raises the status bit and is dropped rather than read out of bounds.
-__device__ __forceinline__ void tile_rows(const FtArgs& a, const TileArgs& t, int block, int pair, int lane,
+__device__ __forceinline__ void tile_rows(const FtArgs& a, const TileArgs& t, int block, const uint32_t (&slot)[2],
                                           int (&row)[2], unsigned (&mask)[2]) {
-    const int b = pair >> 1, p = pair & 1;
-    const uint16_t* list = (p ? a.idx_nstm : a.idx_stm) + (size_t)b * a.nnz;
-    uint32_t slot[2];
-    load_slots(list, a.nnz, lane, slot[0], slot[1]);
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const bool valid = slot[h] < (uint32_t)a.n_inputs;
@@ -257,6 +253,9 @@ __device__ __forceinline__ void tile_rows(const FtArgs& a, const TileArgs& t, in
         if (valid && !inside) atomicOr(t.status, kStatusOutsideBlock);
         mask[h] = __ballot_sync(0xffffffffu, inside);
     }
+}
+__device__ __forceinline__ const uint16_t* pair_list(const FtArgs& a, int pair) {
+    return ((pair & 1) ? a.idx_nstm : a.idx_stm) + (size_t)(pair >> 1) * a.nnz;
 }
 
 // Forward.  grid = nblocks * nslabs * nsplit CTAs of 1024 threads (one per SM); dynamic
@@ -283,11 +282,20 @@ __global__ void __launch_bounds__(1024, 1) ft_forward_tiled_kernel(FtArgs a, Til
     cp_async_wait_all();
     __syncthreads();
     const float* mine = tile + lane;
-    for (int i = w.begin + warp; i < w.end; i += nwarps) {
-        const int pair = t.pair_order ? t.pair_order[i] : i;
+    // the pair id is fetched two positions ahead and the slots one ahead, so their global
+    // latency overlaps the shared-memory work on the current position
+    auto pair_at = [&](int i) { return i < w.end ? (t.pair_order ? t.pair_order[i] : i) : 0; };
+    int i = w.begin + warp;
+    int pair = pair_at(i), pair_next = pair_at(i + nwarps);
+    uint32_t slot[2] = {kNoFeature, kNoFeature};
+    if (i < w.end) load_slots(pair_list(a, pair), a.nnz, lane, slot[0], slot[1]);
+    for (; i < w.end; i += nwarps) {
+        const int pair_next2 = pair_at(i + 2 * nwarps);
+        uint32_t slot_next[2] = {kNoFeature, kNoFeature};
+        if (i + nwarps < w.end) load_slots(pair_list(a, pair_next), a.nnz, lane, slot_next[0], slot_next[1]);
         int row[2];
         unsigned mask[2];
-        tile_rows(a, t, w.block, pair, lane, row, mask);
+        tile_rows(a, t, w.block, slot, row, mask);
         const unsigned lt = (1u << lane) - 1u;
         const int cnt0 = __popc(mask[0]), cnt = cnt0 + __popc(mask[1]);
         __syncwarp();  // the previous position's list has been read by every lane
@@ -318,6 +326,10 @@ __global__ void __launch_bounds__(1024, 1) ft_forward_tiled_kernel(FtArgs a, Til
             xp[col_a + lane] = ft_act_fwd(a.act, va);
             xp[col_b + lane] = ft_act_fwd(a.act, vb);
         }
+        pair = pair_next;
+        pair_next = pair_next2;
+        slot[0] = slot_next[0];
+        slot[1] = slot_next[1];
     }
 }
 
@@ -325,7 +337,7 @@ __global__ void __launch_bounds__(1024, 1) ft_forward_tiled_kernel(FtArgs a, Til
 // columns) lives in registers: warp w owns rows w, w+16, ... (up to 48), lane l their
 // columns A[l] and B[l].  Positions are taken in chunks; per chunk the CTA
 //   1. builds in shared memory a row-major list (CSR) of which positions of the chunk hold
-//      each row — a count pass, a scan and a fill pass over the chunk's slots, and
+//      each row: a count pass, a scan and a fill pass over the chunk's slots, and
 //   2. stages the chunk's pre-activation gradients (from dx and the kept activations), then
 //   3. every warp walks the lists of its own rows and adds the staged gradients into its
 //      registers: no atomics on the accumulators, no shared-memory copy of the tile.
@@ -336,7 +348,7 @@ constexpr int kBwdThreads = 512, kBwdRowsPerWarp = 48;
 __host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? 512 : 256; }
 __host__ __device__ inline size_t ft_bwd_smem(int R, int nnz) {
     const int cp = ft_bwd_chunk(nnz);
-    return (size_t)cp * kTileCols * 4 + (size_t)cp * nnz * 2 + (size_t)(2 * R + 2 + 32) * 4;
+    return (size_t)cp * kTileCols * 4 + (size_t)cp * nnz * 2 + (size_t)(2 * R + 2 + 32 + cp) * 4;
 }
 
 template <bool PAIRWISE>
@@ -351,6 +363,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
     int* start = reinterpret_cast<int*>(ent + (size_t)CP * a.nnz);           // [R + 1]
     int* cursor = start + R + 1;                                             // [R]
     int* warp_tot = cursor + R + 1;                                          // [NW] (+ slack)
+    int* pairs_s = warp_tot + 32;                                            // [CP] pair ids of the chunk
     const int col_a = tile_col_a<PAIRWISE>(w.slab, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, a.H);
 
     float acc_a[kBwdRowsPerWarp], acc_b[kBwdRowsPerWarp];
@@ -358,34 +371,68 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
     for (int j = 0; j < kBwdRowsPerWarp; j++) acc_a[j] = acc_b[j] = 0.f;
     float bsum_a = 0.f, bsum_b = 0.f;
 
+    const int sp_shift = a.nnz <= 32 ? 5 : 6;  // slots per position padded to 32 or 64
     for (int c0 = w.begin; c0 < w.end; c0 += CP) {
         const int cn = min(CP, w.end - c0);
         for (int r = threadIdx.x; r < R; r += kBwdThreads) cursor[r] = 0;
+        for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
         __syncthreads();
-        // count rows, and stage this chunk's gradients at the feature-transformer pre-activation
-        for (int pl = warp; pl < cn; pl += NW) {
-            const int pair = t.pair_order ? t.pair_order[c0 + pl] : c0 + pl;
-            int row[2];
-            unsigned mask[2];
-            tile_rows(a, t, w.block, pair, lane, row, mask);
-            if (mask[0] >> lane & 1) atomicAdd(&cursor[row[0]], 1);
-            if (mask[1] >> lane & 1) atomicAdd(&cursor[row[1]], 1);
-            const int b = pair >> 1, p = pair & 1;
-            float ga, gb;
-            if (PAIRWISE) {
-                const float ua = a.u[(size_t)pair * a.H + col_a + lane], ub = a.u[(size_t)pair * a.H + col_b + lane];
-                const float d = a.dx[(size_t)b * a.H + (size_t)p * (a.H / 2) + col_a + lane];
-                ga = (d * ub) * ft_act_bwd(1, ua);
-                gb = (d * ua) * ft_act_bwd(1, ub);
-            } else {
-                const size_t at = (size_t)b * 2 * a.H + (size_t)p * a.H;
-                ga = a.dx[at + col_a + lane] * ft_act_bwd(a.act, a.x[at + col_a + lane]);
-                gb = a.dx[at + col_b + lane] * ft_act_bwd(a.act, a.x[at + col_b + lane]);
+        // count how often each row occurs in the chunk; loads are issued four at a time
+        const int total = cn << sp_shift;
+        for (int e0 = threadIdx.x; e0 < total; e0 += 4 * kBwdThreads) {
+            uint32_t v[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int e = e0 + k * kBwdThreads, sl = e & ((1 << sp_shift) - 1);
+                v[k] = (e < total && sl < a.nnz) ? __ldg(pair_list(a, pairs_s[e >> sp_shift]) + sl) : kNoFeature;
             }
-            g_s[pl * kTileCols + lane] = ga;
-            g_s[pl * kTileCols + 32 + lane] = gb;
-            bsum_a += ga;
-            bsum_b += gb;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int row = (int)v[k] - w.block * R;
+                if (v[k] < (uint32_t)a.n_inputs) {
+                    if ((unsigned)row < (unsigned)R)
+                        atomicAdd(&cursor[row], 1);
+                    else
+                        atomicOr(t.status, kStatusOutsideBlock);
+                }
+            }
+        }
+        // stage this chunk's gradients at the feature-transformer pre-activation
+        for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
+            float q0[4], q1[4], q2[4];
+            q2[0] = q2[1] = q2[2] = q2[3] = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int pl = pl0 + k * NW;
+                q0[k] = q1[k] = 0.f;
+                if (pl < cn) {
+                    const int pair = pairs_s[pl], b = pair >> 1, p = pair & 1;
+                    if (PAIRWISE) {
+                        q0[k] = a.u[(size_t)pair * a.H + col_a + lane];
+                        q1[k] = a.u[(size_t)pair * a.H + col_b + lane];
+                        q2[k] = a.dx[(size_t)b * a.H + (size_t)p * (a.H / 2) + col_a + lane];
+                    } else {
+                        const size_t at = (size_t)b * 2 * a.H + (size_t)p * a.H;
+                        q0[k] = a.dx[at + col_a + lane] * ft_act_bwd(a.act, a.x[at + col_a + lane]);
+                        q1[k] = a.dx[at + col_b + lane] * ft_act_bwd(a.act, a.x[at + col_b + lane]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int pl = pl0 + k * NW;
+                if (pl < cn) {
+                    float ga = q0[k], gb = q1[k];
+                    if (PAIRWISE) {
+                        ga = (q2[k] * q1[k]) * ft_act_bwd(1, q0[k]);
+                        gb = (q2[k] * q0[k]) * ft_act_bwd(1, q1[k]);
+                    }
+                    g_s[pl * kTileCols + lane] = ga;
+                    g_s[pl * kTileCols + 32 + lane] = gb;
+                    bsum_a += ga;
+                    bsum_b += gb;
+                }
+            }
         }
         __syncthreads();
         // exclusive scan of the row counts -> start[], cursor[] = start[]
@@ -417,17 +464,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
         }
         __syncthreads();
         // fill: entry = position of the chunk, grouped by row
-        for (int pl = warp; pl < cn; pl += NW) {
-            const int pair = t.pair_order ? t.pair_order[c0 + pl] : c0 + pl;
-            const int b = pair >> 1, p = pair & 1;
-            const uint16_t* list = (p ? a.idx_nstm : a.idx_stm) + (size_t)b * a.nnz;
-            uint32_t slot[2];
-            load_slots(list, a.nnz, lane, slot[0], slot[1]);
+        for (int e0 = threadIdx.x; e0 < total; e0 += 4 * kBwdThreads) {
+            uint32_t v[4];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int row = (int)slot[h] - w.block * R;
-                if (slot[h] < (uint32_t)a.n_inputs && (unsigned)row < (unsigned)R)
-                    ent[atomicAdd(&cursor[row], 1)] = (uint16_t)pl;
+            for (int k = 0; k < 4; k++) {
+                const int e = e0 + k * kBwdThreads, sl = e & ((1 << sp_shift) - 1);
+                v[k] = (e < total && sl < a.nnz) ? __ldg(pair_list(a, pairs_s[e >> sp_shift]) + sl) : kNoFeature;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int row = (int)v[k] - w.block * R;
+                if (v[k] < (uint32_t)a.n_inputs && (unsigned)row < (unsigned)R)
+                    ent[atomicAdd(&cursor[row], 1)] = (uint16_t)((e0 + k * kBwdThreads) >> sp_shift);
             }
         }
         __syncthreads();

@@ -45,7 +45,8 @@ extern "C" {
 
 #define B200_NUM_SLOTS 3 /* staging slots for double/triple-buffered upload */
 
-/* Feature-transformer kernel selection (b200_net_set_option "ft_mode") */
+/* Feature-transformer kernel selection: b200_net_set_option "ft_mode" sets both passes,
+ * "ft_fwd_mode" / "ft_bwd_mode" one of them */
 #define B200_FT_AUTO 0
 #define B200_FT_GATHER 1 /* row gather straight from the table in L2/HBM, global vector atomics */
 #define B200_FT_TILED 2  /* table block staged in shared memory, positions grouped by block */
@@ -136,7 +137,8 @@ int b200_sync(b200_net* net);
  * span exactly one kernel launch. */
 int b200_get_timings(b200_net* net, b200_timings* out);
 /* Counters: "launches" (kernels launched so far), "h2d_bytes" (batch bytes copied so far),
- * "flat_floats" (length of the flat parameter buffer), "ft_tiled" (1 if the tiled kernels run). */
+ * "flat_floats" (length of the flat parameter buffer), "ft_tiled" (bit 0: the forward runs the
+ * tiled kernel, bit 1: the backward does). */
 int b200_net_get_stat(b200_net* net, const char* key, int64_t* value);
 /* Debug/inspection: copy an internal activation buffer of the last pass to the host.
  * which: 0 = dense-stack input x [n][D1], 1 = pairwise crelu outputs u [n][2][H],
