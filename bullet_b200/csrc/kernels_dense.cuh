@@ -17,7 +17,9 @@
 
 namespace b200 {
 
-constexpr int kDenseTile = 4;  // positions of one output bucket handled together by one warp
+constexpr int kDenseTile = 32;    // positions of one output bucket handled by one CTA (8 warps)
+constexpr int kDenseWarpPos = 4;  // of which each warp takes four
+constexpr int kDenseChunk = 128;  // first-layer columns staged in shared memory per round
 
 struct DenseArgs {
     const float* x;        // [n][K1] dense-stack input
@@ -49,7 +51,7 @@ __device__ __forceinline__ float act_bwd(int act, float y) { return act == 0 ? 1
 
 // l1w is stored column-major over ALL buckets' rows, so the M1 rows of one bucket for
 // consecutive columns lie O*M1 floats apart.  The kernels below read the regrouped copy
-// W1g[bucket][column][row], where a warp's 32 lanes x 4 columns x M1 rows are contiguous.
+// W1g[bucket][column][row], in which one bucket's weights for a run of columns are contiguous.
 __global__ void dense_regroup_kernel(const float* __restrict__ W1, float* __restrict__ W1g, int K1, int O, int M1) {
     const int total = K1 * O * M1;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -58,121 +60,176 @@ __global__ void dense_regroup_kernel(const float* __restrict__ W1, float* __rest
     }
 }
 
-// One warp per tile of up to kDenseTile positions of the same output bucket.  The first
-// layer is a K1-long dot product per selected row with the columns split over the lanes
-// (each weight is loaded once per tile and used for every position of the tile); the tiny
-// remaining layers, the loss and the backward pass down to the first layer's
-// pre-activation gradient follow per position.  grid = ceil(ntiles/8), block = 256.
+// Shared-memory stride of one column's M1 weights: padded so that the 128-bit reads of
+// eight neighbouring lanes (neighbouring columns) fall into different banks.
 template <int M1>
-__global__ void __launch_bounds__(256) dense_forward_kernel(DenseArgs a) {
-    constexpr int P = kDenseTile;
+__host__ __device__ constexpr int dense_col_stride() { return M1 % 8 == 0 ? M1 + 4 : M1; }
+
+__device__ __forceinline__ void dense_cp_async16(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void dense_cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void dense_cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Stages columns [chunk*128, chunk*128+128) of bucket k's first-layer weights; columns past
+// K1 are zero-filled.  All 256 threads take part.
+template <int M1>
+__device__ __forceinline__ void dense_stage_chunk(const DenseArgs& a, int k, int chunk, float* buf) {
+    constexpr int MP = dense_col_stride<M1>();
+    const int c_begin = chunk * kDenseChunk;
+    const float* src = a.W1g + ((size_t)k * a.K1 + c_begin) * M1;
+    if (M1 % 4 == 0) {
+        constexpr int Q = M1 / 4;  // 16-byte pieces per column
+        for (int i = threadIdx.x; i < kDenseChunk * Q; i += blockDim.x) {
+            const int c = i / Q, q = i % Q;
+            float* dst = buf + c * MP + q * 4;
+            if (c_begin + c < a.K1)
+                dense_cp_async16(dst, src + (size_t)c * M1 + q * 4);
+            else
+                *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
+        }
+    } else {
+        for (int i = threadIdx.x; i < kDenseChunk * M1; i += blockDim.x)
+            buf[i] = c_begin + i / M1 < a.K1 ? __ldg(src + i) : 0.f;
+    }
+    dense_cp_commit();
+}
+
+template <int M1>
+__device__ __forceinline__ void dense_read_weights(const float* buf, int c, float (&w)[M1]) {
+    constexpr int MP = dense_col_stride<M1>();
+    if (M1 % 4 == 0) {
+#pragma unroll
+        for (int r = 0; r < M1; r += 4) {
+            const float4 wv = *reinterpret_cast<const float4*>(buf + c * MP + r);
+            w[r] = wv.x, w[r + 1] = wv.y, w[r + 2] = wv.z, w[r + 3] = wv.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < M1; r++) w[r] = buf[c * MP + r];
+    }
+}
+
+// One CTA per tile of up to 32 positions of the same output bucket, four per warp.  The
+// bucket's first-layer weights stream through shared memory in 128-column chunks (double
+// buffered with cp.async) and are shared by all 32 positions; lane l takes columns l, l+32,
+// l+64, l+96 of a chunk, so x is read coalesced.  After the K1-long dot products the tiny
+// remaining layers, the loss and the backward pass down to the first layer's pre-activation
+// gradient follow per position.  grid = ntiles, block = 256.
+template <int M1>
+__global__ void __launch_bounds__(256, (M1 > 16 ? 1 : 2)) dense_forward_kernel(DenseArgs a) {
+    constexpr int P = kDenseWarpPos, MP = dense_col_stride<M1>();
+    __shared__ __align__(16) float wbuf[2][kDenseChunk * MP];
     __shared__ float loss_part[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tile = blockIdx.x * 8 + warp;
-    float my_loss = 0.f;
-    if (tile < a.ntiles) {
-        const int2 t = a.tiles[tile];
-        int pos[P];
+    const int2 t = a.tiles[blockIdx.x];
+    const int k = a.buckets[a.order[t.x]];
+    const int npos = max(0, min(P, t.y - warp * P));
+    int pos[P];
 #pragma unroll
-        for (int j = 0; j < P; j++) pos[j] = a.order[t.x + min(j, t.y - 1)];
-        const int k = a.buckets[pos[0]];
-        float acc[P][M1];
+    for (int j = 0; j < P; j++) pos[j] = a.order[npos ? t.x + warp * P + min(j, npos - 1) : t.x];
+    float acc[P][M1];
+#pragma unroll
+    for (int j = 0; j < P; j++)
+#pragma unroll
+        for (int r = 0; r < M1; r++) acc[j][r] = 0.f;
+    const int nchunks = (a.K1 + kDenseChunk - 1) / kDenseChunk;
+    dense_stage_chunk<M1>(a, k, 0, wbuf[0]);
+    for (int ch = 0; ch < nchunks; ch++) {
+        if (ch + 1 < nchunks) dense_stage_chunk<M1>(a, k, ch + 1, wbuf[(ch + 1) & 1]);
+        float xs[P][4];
 #pragma unroll
         for (int j = 0; j < P; j++)
 #pragma unroll
-            for (int r = 0; r < M1; r++) acc[j][r] = 0.f;
-        const float* wk = a.W1g + (size_t)k * a.K1 * M1;
-        for (int c0 = lane * 4; c0 < a.K1; c0 += 128) {
-            float xs[P][4];
-#pragma unroll
-            for (int j = 0; j < P; j++) {
-                const float4 v = *reinterpret_cast<const float4*>(a.x + (size_t)pos[j] * a.K1 + c0);
-                xs[j][0] = v.x, xs[j][1] = v.y, xs[j][2] = v.z, xs[j][3] = v.w;
+            for (int jj = 0; jj < 4; jj++) {
+                const int c = ch * kDenseChunk + jj * 32 + lane;
+                xs[j][jj] = (npos && c < a.K1) ? a.x[(size_t)pos[j] * a.K1 + c] : 0.f;
             }
+        if (ch + 1 < nchunks)
+            dense_cp_wait<1>();
+        else
+            dense_cp_wait<0>();
+        __syncthreads();
+        if (npos) {
+            const float* buf = wbuf[ch & 1];
 #pragma unroll
             for (int jj = 0; jj < 4; jj++) {
                 float w[M1];
-                const float* wc = wk + (size_t)(c0 + jj) * M1;
-                if (M1 % 4 == 0) {
-#pragma unroll
-                    for (int r = 0; r < M1; r += 4) {
-                        const float4 wv = __ldg(reinterpret_cast<const float4*>(wc + r));
-                        w[r] = wv.x, w[r + 1] = wv.y, w[r + 2] = wv.z, w[r + 3] = wv.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int r = 0; r < M1; r++) w[r] = __ldg(wc + r);
-                }
+                dense_read_weights<M1>(buf, jj * 32 + lane, w);
 #pragma unroll
                 for (int j = 0; j < P; j++)
 #pragma unroll
                     for (int r = 0; r < M1; r++) acc[j][r] += w[r] * xs[j][jj];
             }
         }
+        __syncthreads();
+    }
+    float my_loss = 0.f;
 #pragma unroll
-        for (int j = 0; j < P; j++) {
-            if (j >= t.y) break;  // warp-uniform
-            const int b = pos[j];
-            float a1v[M1];
+    for (int j = 0; j < P; j++) {
+        if (j >= npos) break;  // warp-uniform
+        const int b = pos[j];
+        float a1v[M1];
 #pragma unroll
-            for (int r = 0; r < M1; r++) a1v[r] = act_fwd(a.act[0], warp_sum(acc[j][r]) + a.B[0][k * M1 + r]);
+        for (int r = 0; r < M1; r++) a1v[r] = act_fwd(a.act[0], warp_sum(acc[j][r]) + a.B[0][k * M1 + r]);
 
-            float o;        // network output
-            float a2v = 0;  // lane r2 holds a2[r2] when there are three layers
-            if (a.n_dense == 1) {
-                o = a1v[0];
-            } else {
-                const int M2 = a.M[1], OM2 = a.O * M2;
-                float z2 = 0.f;
-                if (lane < M2) {
+        float o;        // network output
+        float a2v = 0;  // lane r2 holds a2[r2] when there are three layers
+        if (a.n_dense == 1) {
+            o = a1v[0];
+        } else {
+            const int M2 = a.M[1], OM2 = a.O * M2;
+            float z2 = 0.f;
+            if (lane < M2) {
 #pragma unroll
-                    for (int c = 0; c < M1; c++) z2 += a.W[1][c * OM2 + k * M2 + lane] * a1v[c];
-                    z2 += a.B[1][k * M2 + lane];
-                }
-                if (a.n_dense == 2) {
-                    o = __shfl_sync(0xffffffffu, z2, 0);
-                } else {
-                    a2v = lane < M2 ? act_fwd(a.act[1], z2) : 0.f;
-                    const float term = lane < M2 ? a.W[2][lane * a.O + k] * a2v : 0.f;
-                    o = warp_sum(term) + a.B[2][k];
-                }
+                for (int c = 0; c < M1; c++) z2 += a.W[1][c * OM2 + k * M2 + lane] * a1v[c];
+                z2 += a.B[1][k * M2 + lane];
             }
-            if (lane == 0) a.out[b] = o;
-            if (!a.want_grad) continue;
-
-            const float s = 1.f / (1.f + expf(-o));
-            const float diff = s - a.targets[b];
-            my_loss += diff * diff;
-            const float dout = (diff + diff) * (s * (1.f - s));
-            float dz1[M1];
-            if (a.n_dense == 1) {
-                dz1[0] = dout;  // M1 == 1, no activation on the last layer
-            } else if (a.n_dense == 2) {
-                if (lane == 0) a.dz[1][b] = dout;
-#pragma unroll
-                for (int c = 0; c < M1; c++) dz1[c] = (a.W[1][c * a.O + k] * dout) * act_bwd(a.act[0], a1v[c]);
+            if (a.n_dense == 2) {
+                o = __shfl_sync(0xffffffffu, z2, 0);
             } else {
-                const int M2 = a.M[1], OM2 = a.O * M2;
-                if (lane == 0) a.dz[2][b] = dout;
-                float dz2 = 0.f;
-                if (lane < M2) {
-                    dz2 = (a.W[2][lane * a.O + k] * dout) * act_bwd(a.act[1], a2v);
-                    a.dz[1][(size_t)b * M2 + lane] = dz2;
-                    a.a2[(size_t)b * M2 + lane] = a2v;
-                }
-#pragma unroll
-                for (int c = 0; c < M1; c++) {
-                    const float term = lane < M2 ? a.W[1][c * OM2 + k * M2 + lane] * dz2 : 0.f;
-                    dz1[c] = warp_sum(term) * act_bwd(a.act[0], a1v[c]);
-                }
+                a2v = lane < M2 ? act_fwd(a.act[1], z2) : 0.f;
+                const float term = lane < M2 ? a.W[2][lane * a.O + k] * a2v : 0.f;
+                o = warp_sum(term) + a.B[2][k];
             }
-#pragma unroll
-            for (int c = 0; c < M1; c++)
-                if (lane == (c & 31)) {
-                    a.dz[0][(size_t)b * M1 + c] = dz1[c];
-                    if (a.n_dense > 1) a.a1[(size_t)b * M1 + c] = a1v[c];
-                }
         }
+        if (lane == 0) a.out[b] = o;
+        if (!a.want_grad) continue;
+
+        const float s = 1.f / (1.f + expf(-o));
+        const float diff = s - a.targets[b];
+        my_loss += diff * diff;
+        const float dout = (diff + diff) * (s * (1.f - s));
+        float dz1[M1];
+        if (a.n_dense == 1) {
+            dz1[0] = dout;  // M1 == 1, no activation on the last layer
+        } else if (a.n_dense == 2) {
+            if (lane == 0) a.dz[1][b] = dout;
+#pragma unroll
+            for (int c = 0; c < M1; c++) dz1[c] = (a.W[1][c * a.O + k] * dout) * act_bwd(a.act[0], a1v[c]);
+        } else {
+            const int M2 = a.M[1], OM2 = a.O * M2;
+            if (lane == 0) a.dz[2][b] = dout;
+            float dz2 = 0.f;
+            if (lane < M2) {
+                dz2 = (a.W[2][lane * a.O + k] * dout) * act_bwd(a.act[1], a2v);
+                a.dz[1][(size_t)b * M2 + lane] = dz2;
+                a.a2[(size_t)b * M2 + lane] = a2v;
+            }
+#pragma unroll
+            for (int c = 0; c < M1; c++) {
+                const float term = lane < M2 ? a.W[1][c * OM2 + k * M2 + lane] * dz2 : 0.f;
+                dz1[c] = warp_sum(term) * act_bwd(a.act[0], a1v[c]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < M1; c++)
+            if (lane == (c & 31)) {
+                a.dz[0][(size_t)b * M1 + c] = dz1[c];
+                if (a.n_dense > 1) a.a1[(size_t)b * M1 + c] = a1v[c];
+            }
     }
     if (a.want_grad) {
         if (lane == 0) loss_part[warp] = my_loss;
@@ -186,53 +243,50 @@ __global__ void __launch_bounds__(256) dense_forward_kernel(DenseArgs a) {
 }
 
 // dx[b][c] = sum_r W1[c][k_b][r] * dz1[b][r]   (Matmul::backward, matmul.rs:99-126, on the
-// selected rows).  One warp per tile, lanes over columns; grid = ceil(ntiles/8), block = 256.
+// selected rows).  Same tiling and weight staging as the forward; grid = ntiles, block = 256.
 template <int M1>
-__global__ void __launch_bounds__(256) dense_dx_kernel(DenseArgs a, float* dx) {
-    constexpr int P = kDenseTile;
+__global__ void __launch_bounds__(256, (M1 > 16 ? 1 : 2)) dense_dx_kernel(DenseArgs a, float* dx) {
+    constexpr int P = kDenseWarpPos, MP = dense_col_stride<M1>();
+    __shared__ __align__(16) float wbuf[2][kDenseChunk * MP];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tile = blockIdx.x * 8 + warp;
-    if (tile >= a.ntiles) return;
-    const int2 t = a.tiles[tile];
+    const int2 t = a.tiles[blockIdx.x];
+    const int k = a.buckets[a.order[t.x]];
+    const int npos = max(0, min(P, t.y - warp * P));
     int pos[P];
 #pragma unroll
-    for (int j = 0; j < P; j++) pos[j] = a.order[t.x + min(j, t.y - 1)];
-    const int k = a.buckets[pos[0]];
+    for (int j = 0; j < P; j++) pos[j] = a.order[npos ? t.x + warp * P + min(j, npos - 1) : t.x];
     float g[P][M1];
 #pragma unroll
     for (int j = 0; j < P; j++)
 #pragma unroll
         for (int r = 0; r < M1; r++) g[j][r] = a.dz[0][(size_t)pos[j] * M1 + r];
-    const float* wk = a.W1g + (size_t)k * a.K1 * M1;
-    for (int c0 = lane * 4; c0 < a.K1; c0 += 128) {
-        float res[P][4];
+    const int nchunks = (a.K1 + kDenseChunk - 1) / kDenseChunk;
+    dense_stage_chunk<M1>(a, k, 0, wbuf[0]);
+    for (int ch = 0; ch < nchunks; ch++) {
+        if (ch + 1 < nchunks) {
+            dense_stage_chunk<M1>(a, k, ch + 1, wbuf[(ch + 1) & 1]);
+            dense_cp_wait<1>();
+        } else {
+            dense_cp_wait<0>();
+        }
+        __syncthreads();
+        if (npos) {
+            const float* buf = wbuf[ch & 1];
 #pragma unroll
-        for (int jj = 0; jj < 4; jj++) {
-            float w[M1];
-            const float* wc = wk + (size_t)(c0 + jj) * M1;
-            if (M1 % 4 == 0) {
+            for (int jj = 0; jj < 4; jj++) {
+                const int c = ch * kDenseChunk + jj * 32 + lane;
+                float w[M1];
+                dense_read_weights<M1>(buf, jj * 32 + lane, w);
 #pragma unroll
-                for (int r = 0; r < M1; r += 4) {
-                    const float4 wv = __ldg(reinterpret_cast<const float4*>(wc + r));
-                    w[r] = wv.x, w[r + 1] = wv.y, w[r + 2] = wv.z, w[r + 3] = wv.w;
+                for (int j = 0; j < P; j++) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int r = 0; r < M1; r++) s += w[r] * g[j][r];
+                    if (j < npos && c < a.K1) dx[(size_t)pos[j] * a.K1 + c] = s;
                 }
-            } else {
-#pragma unroll
-                for (int r = 0; r < M1; r++) w[r] = __ldg(wc + r);
-            }
-#pragma unroll
-            for (int j = 0; j < P; j++) {
-                float s = 0.f;
-#pragma unroll
-                for (int r = 0; r < M1; r++) s += w[r] * g[j][r];
-                res[j][jj] = s;
             }
         }
-#pragma unroll
-        for (int j = 0; j < P; j++)
-            if (j < t.y)
-                *reinterpret_cast<float4*>(dx + (size_t)pos[j] * a.K1 + c0) =
-                    make_float4(res[j][0], res[j][1], res[j][2], res[j][3]);
+        __syncthreads();
     }
 }
 

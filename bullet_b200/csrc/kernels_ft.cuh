@@ -209,22 +209,32 @@ __global__ void __launch_bounds__(256) ft_backward_gather_kernel(FtArgs a, int p
 }
 
 // ------------------------------------------------------------------ tiled kernels
-// A tile holds, for every row of one table block, 64 floats: half A then half B, 32 each.
-// Lane l owns column A[l] and column B[l].  Without pairwise A|B are 64 consecutive
-// columns [64s, 64s+64); with pairwise A is the low-half columns [32s, 32s+32) and B their
-// partners [H/2 + 32s, H/2 + 32s + 32), so a lane holds both factors of one product.
+// A tile row holds 64 floats of one table row as 32 (A, B) pairs; lane l owns pair l and
+// moves it with one 64-bit shared-memory access and one packed f32x2 add.  Without pairwise
+// the pair is two neighbouring columns (64s + 2l, 64s + 2l + 1); with pairwise it is the
+// low-half column 32s + l and its partner H/2 + 32s + l, i.e. both factors of one product.
 constexpr int kTileCols = 64;
+constexpr int kTileRowBytes = kTileCols * 4;
 
-template <bool PAIRWISE>
-__device__ __forceinline__ int tile_col_a(int slab, int H) { return PAIRWISE ? slab * 32 : slab * 64; }
-template <bool PAIRWISE>
-__device__ __forceinline__ int tile_col_b(int slab, int H) { return PAIRWISE ? H / 2 + slab * 32 : slab * 64 + 32; }
+typedef unsigned long long f32x2;  // two packed floats: low word = A, high word = B
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {  // two IEEE fp32 adds in one instruction
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    return (f32x2)__float_as_uint(a) | ((f32x2)__float_as_uint(b) << 32);
+}
+__device__ __forceinline__ float lo2(f32x2 v) { return __uint_as_float((unsigned)v); }
+__device__ __forceinline__ float hi2(f32x2 v) { return __uint_as_float((unsigned)(v >> 32)); }
+
+template <bool PAIRWISE>
+__device__ __forceinline__ int tile_col_a(int slab, int lane, int H) { return PAIRWISE ? slab * 32 + lane : slab * 64 + 2 * lane; }
+template <bool PAIRWISE>
+__device__ __forceinline__ int tile_col_b(int slab, int lane, int H) {
+    return PAIRWISE ? H / 2 + slab * 32 + lane : slab * 64 + 2 * lane + 1;
+}
 
 struct TileWork {
     int block, slab, begin, end;  // pair_order range [begin, end) served by this CTA
@@ -241,137 +251,140 @@ __device__ __forceinline__ TileWork tile_work(const TileArgs& t) {
     return w;
 }
 
-// One position's slots as table rows local to `block`.  A valid feature outside the block
-// raises the status bit and is dropped rather than read out of bounds.
-__device__ __forceinline__ void tile_rows(const FtArgs& a, const TileArgs& t, int block, const uint32_t (&slot)[2],
-                                          int (&row)[2], unsigned (&mask)[2]) {
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-        const bool valid = slot[h] < (uint32_t)a.n_inputs;
-        row[h] = (int)slot[h] - block * t.block_rows;
-        const bool inside = valid && (unsigned)row[h] < (unsigned)t.block_rows;
-        if (valid && !inside) atomicOr(t.status, kStatusOutsideBlock);
-        mask[h] = __ballot_sync(0xffffffffu, inside);
-    }
-}
 __device__ __forceinline__ const uint16_t* pair_list(const FtArgs& a, int pair) {
     return ((pair & 1) ? a.idx_nstm : a.idx_stm) + (size_t)(pair >> 1) * a.nnz;
 }
 
 // Forward.  grid = nblocks * nslabs * nsplit CTAs of 1024 threads (one per SM); dynamic
-// shared memory = R*64 floats for the tile + 32 warps * 72 ints of per-warp offset lists.
+// shared memory = (R+1) tile rows (the extra row is all zero) + 32 warps * 72 ints.
 // Each warp serves one (position, perspective) at a time: its lanes compact the position's
-// valid rows into the warp's offset list, then every lane adds its two tile columns over
-// that list in slot order — the same order and arithmetic as the interpreter.
+// valid rows into the warp's list of tile byte offsets, padded to a multiple of four with
+// the zero row, then every lane adds its column pair over that list in slot order — the
+// same order and arithmetic as the interpreter (adding the zero row changes nothing).
+constexpr int kFwdThreads = 1024, kFwdListInts = 72;
+__host__ __device__ inline size_t ft_fwd_smem(int R) { return (size_t)(R + 1) * kTileRowBytes + 32 * kFwdListInts * 4; }
+
 template <bool PAIRWISE>
-__global__ void __launch_bounds__(1024, 1) ft_forward_tiled_kernel(FtArgs a, TileArgs t) {
-    extern __shared__ __align__(16) float smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+__global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs a, TileArgs t) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int NW = kFwdThreads / 32;
     const TileWork w = tile_work(t);
     const int R = t.block_rows;
-    float* tile = smem;
-    int* offs = reinterpret_cast<int*>(smem + (size_t)R * kTileCols) + warp * 72;
-    const int col_a = tile_col_a<PAIRWISE>(w.slab, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, a.H);
-    for (int i = threadIdx.x; i < R * 16; i += blockDim.x) {
-        const int row = i >> 4, q = i & 15;
-        const int col = q < 8 ? col_a + q * 4 : col_b + (q - 8) * 4;
-        cp_async16(&tile[row * kTileCols + q * 4], a.table + (size_t)(w.block * R + row) * a.H + col);
+    float* tile = reinterpret_cast<float*>(smem_raw);
+    int* offs = reinterpret_cast<int*>(smem_raw + (size_t)(R + 1) * kTileRowBytes) + warp * kFwdListInts;
+    {   // fill the tile: 8 work items per row, each 8 floats of the row
+        const float* src = a.table + (size_t)w.block * R * a.H;
+        for (int i = threadIdx.x; i < R * 8; i += kFwdThreads) {
+            const int row = i >> 3, q = i & 7;
+            float4* dst = reinterpret_cast<float4*>(tile + row * kTileCols + q * 8);
+            if (PAIRWISE) {
+                const float4 lo = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + w.slab * 32 + q * 4));
+                const float4 hi = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + a.H / 2 + w.slab * 32 + q * 4));
+                dst[0] = make_float4(lo.x, hi.x, lo.y, hi.y);
+                dst[1] = make_float4(lo.z, hi.z, lo.w, hi.w);
+            } else {
+                const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + w.slab * 64 + q * 8);
+                dst[0] = __ldg(g);
+                dst[1] = __ldg(g + 1);
+            }
+        }
+        if (threadIdx.x < kTileCols) tile[R * kTileCols + threadIdx.x] = 0.f;
     }
-    for (int i = lane; i < 72; i += 32) offs[i] = 0;
-    const float bias_a = a.bias[col_a + lane], bias_b = a.bias[col_b + lane];
-    cp_async_wait_all();
+    const int col_a = tile_col_a<PAIRWISE>(w.slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, lane, a.H);
+    const f32x2 bias = pack2(a.bias[col_a], a.bias[col_b]);
+    const int zero_row = R * kTileRowBytes;
     __syncthreads();
-    const float* mine = tile + lane;
+    const unsigned char* mine = smem_raw + lane * 8;
     // the pair id is fetched two positions ahead and the slots one ahead, so their global
     // latency overlaps the shared-memory work on the current position
     auto pair_at = [&](int i) { return i < w.end ? (t.pair_order ? t.pair_order[i] : i) : 0; };
     int i = w.begin + warp;
-    int pair = pair_at(i), pair_next = pair_at(i + nwarps);
-    uint32_t slot[2] = {kNoFeature, kNoFeature};
-    if (i < w.end) load_slots(pair_list(a, pair), a.nnz, lane, slot[0], slot[1]);
-    for (; i < w.end; i += nwarps) {
-        const int pair_next2 = pair_at(i + 2 * nwarps);
-        uint32_t slot_next[2] = {kNoFeature, kNoFeature};
-        if (i + nwarps < w.end) load_slots(pair_list(a, pair_next), a.nnz, lane, slot_next[0], slot_next[1]);
-        int row[2];
-        unsigned mask[2];
-        tile_rows(a, t, w.block, slot, row, mask);
-        const unsigned lt = (1u << lane) - 1u;
-        const int cnt0 = __popc(mask[0]), cnt = cnt0 + __popc(mask[1]);
+    int pair = pair_at(i), pair_next = pair_at(i + NW);
+    uint32_t slot0 = kNoFeature, slot1 = kNoFeature;
+    if (i < w.end) load_slots(pair_list(a, pair), a.nnz, lane, slot0, slot1);
+    const unsigned lt = (1u << lane) - 1u;
+    for (; i < w.end; i += NW) {
+        const int pair_next2 = pair_at(i + 2 * NW);
+        uint32_t next0 = kNoFeature, next1 = kNoFeature;
+        if (i + NW < w.end) load_slots(pair_list(a, pair_next), a.nnz, lane, next0, next1);
+        const int row0 = (int)slot0 - w.block * R, row1 = (int)slot1 - w.block * R;
+        const bool in0 = slot0 < (uint32_t)a.n_inputs && (unsigned)row0 < (unsigned)R;
+        const bool in1 = slot1 < (uint32_t)a.n_inputs && (unsigned)row1 < (unsigned)R;
+        if ((slot0 < (uint32_t)a.n_inputs && !in0) || (slot1 < (uint32_t)a.n_inputs && !in1))
+            atomicOr(t.status, kStatusOutsideBlock);  // dropped rather than read out of bounds
+        const unsigned m0 = __ballot_sync(0xffffffffu, in0), m1 = __ballot_sync(0xffffffffu, in1);
+        const int cnt0 = __popc(m0), cnt = cnt0 + __popc(m1), cnt4 = (cnt + 3) & ~3;
         __syncwarp();  // the previous position's list has been read by every lane
-        if (mask[0] >> lane & 1) offs[__popc(mask[0] & lt)] = row[0] * kTileCols;
-        if (mask[1] >> lane & 1) offs[cnt0 + __popc(mask[1] & lt)] = row[1] * kTileCols;
+        if (in0) offs[__popc(m0 & lt)] = row0 * kTileRowBytes;
+        if (in1) offs[cnt0 + __popc(m1 & lt)] = row1 * kTileRowBytes;
+        if (lane < cnt4 - cnt) offs[cnt + lane] = zero_row;
         __syncwarp();
-        float acc_a = 0.f, acc_b = 0.f;
-        for (int k = 0; k < cnt; k += 4) {
-            const int4 o = *reinterpret_cast<const int4*>(offs + k);  // entries past cnt are stale but in range
-            const float a0 = mine[o.x], b0 = mine[o.x + 32];
-            const float a1 = mine[o.y], b1 = mine[o.y + 32];
-            const float a2 = mine[o.z], b2 = mine[o.z + 32];
-            const float a3 = mine[o.w], b3 = mine[o.w + 32];
-            acc_a += a0, acc_b += b0;
-            if (k + 1 < cnt) acc_a += a1, acc_b += b1;
-            if (k + 2 < cnt) acc_a += a2, acc_b += b2;
-            if (k + 3 < cnt) acc_a += a3, acc_b += b3;
+        f32x2 acc = 0;  // (+0.0f, +0.0f)
+        for (int k = 0; k < cnt4; k += 4) {
+            const int4 o = *reinterpret_cast<const int4*>(offs + k);
+            const f32x2 v0 = *reinterpret_cast<const f32x2*>(mine + o.x);
+            const f32x2 v1 = *reinterpret_cast<const f32x2*>(mine + o.y);
+            const f32x2 v2 = *reinterpret_cast<const f32x2*>(mine + o.z);
+            const f32x2 v3 = *reinterpret_cast<const f32x2*>(mine + o.w);
+            acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
         }
-        const float va = acc_a + bias_a, vb = acc_b + bias_b;
+        acc = add2(acc, bias);
         const int b = pair >> 1, p = pair & 1;
         if (PAIRWISE) {
-            const float ua = crelu_f(va), ub = crelu_f(vb);
-            a.u[(size_t)pair * a.H + col_a + lane] = ua;
-            a.u[(size_t)pair * a.H + col_b + lane] = ub;
-            a.x[(size_t)b * a.H + (size_t)p * (a.H / 2) + col_a + lane] = ua * ub;
+            const float ua = crelu_f(lo2(acc)), ub = crelu_f(hi2(acc));
+            float* up = a.u + (size_t)pair * a.H;
+            up[col_a] = ua;
+            up[col_b] = ub;
+            a.x[(size_t)b * a.H + p * (a.H / 2) + col_a] = ua * ub;
         } else {
-            float* xp = a.x + (size_t)b * 2 * a.H + (size_t)p * a.H;
-            xp[col_a + lane] = ft_act_fwd(a.act, va);
-            xp[col_b + lane] = ft_act_fwd(a.act, vb);
+            *reinterpret_cast<float2*>(a.x + (size_t)b * 2 * a.H + p * a.H + col_a) =
+                make_float2(ft_act_fwd(a.act, lo2(acc)), ft_act_fwd(a.act, hi2(acc)));
         }
         pair = pair_next;
         pair_next = pair_next2;
-        slot[0] = slot_next[0];
-        slot[1] = slot_next[1];
+        slot0 = next0;
+        slot1 = next1;
     }
 }
 
-// Backward.  Same grid, 512 threads.  The CTA's slice of the table gradient (R rows x 64
-// columns) lives in registers: warp w owns rows w, w+16, ... (up to 48), lane l their
-// columns A[l] and B[l].  Positions are taken in chunks; per chunk the CTA
+// Backward.  Same grid and block size.  Positions are taken in chunks of CP; per chunk the CTA
 //   1. builds in shared memory a row-major list (CSR) of which positions of the chunk hold
-//      each row: a count pass, a scan and a fill pass over the chunk's slots, and
-//   2. stages the chunk's pre-activation gradients (from dx and the kept activations), then
-//   3. every warp walks the lists of its own rows and adds the staged gradients into its
-//      registers: no atomics on the accumulators, no shared-memory copy of the tile.
-// With nsplit == 1 the finished slice is stored (no zeroing needed); otherwise slices of
-// different position ranges are added into a zeroed table.
-constexpr int kBwdThreads = 512, kBwdRowsPerWarp = 48;
+//      each table row: a count pass, a scan and a fill pass over the chunk's slots; every
+//      row's list is padded to a multiple of four entries that point at an all-zero line,
+//   2. stages the chunk's pre-activation gradients (from dx and the kept activations) as one
+//      64-float line per position, then
+//   3. every warp walks the lists of the rows it owns (row = warp, warp + 32, ...), sums the
+//      staged lines in registers and adds the row's total to the table gradient with one
+//      global reduction per lane.
+// Shared-memory accumulators need no atomics, and the table gradient sees one reduction per
+// (row, chunk) instead of one per (row, position).  The table gradient must be zero on entry.
+constexpr int kBwdThreads = 1024;
 
 __host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? 512 : 256; }
 __host__ __device__ inline size_t ft_bwd_smem(int R, int nnz) {
     const int cp = ft_bwd_chunk(nnz);
-    return (size_t)cp * kTileCols * 4 + (size_t)cp * nnz * 2 + (size_t)(2 * R + 2 + 32 + cp) * 4;
+    return (size_t)(cp + 1) * kTileRowBytes + ((size_t)cp * nnz + 4 * (size_t)R) * 2 + (size_t)(2 * R + 4 + 32 + cp) * 4;
 }
 
 template <bool PAIRWISE>
 __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
-    extern __shared__ __align__(16) float smem[];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int NW = kBwdThreads / 32;
     const TileWork w = tile_work(t);
     const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz);
-    float* g_s = smem;                                                       // [CP][64]
-    uint16_t* ent = reinterpret_cast<uint16_t*>(smem + (size_t)CP * kTileCols);  // [CP * nnz]
-    int* start = reinterpret_cast<int*>(ent + (size_t)CP * a.nnz);           // [R + 1]
-    int* cursor = start + R + 1;                                             // [R]
-    int* warp_tot = cursor + R + 1;                                          // [NW] (+ slack)
-    int* pairs_s = warp_tot + 32;                                            // [CP] pair ids of the chunk
-    const int col_a = tile_col_a<PAIRWISE>(w.slab, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, a.H);
-
-    float acc_a[kBwdRowsPerWarp], acc_b[kBwdRowsPerWarp];
-#pragma unroll
-    for (int j = 0; j < kBwdRowsPerWarp; j++) acc_a[j] = acc_b[j] = 0.f;
-    float bsum_a = 0.f, bsum_b = 0.f;
-
+    f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                              // [CP + 1][32] (A, B) pairs
+    uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists
+    int* start = reinterpret_cast<int*>(ent + (size_t)CP * a.nnz + 4 * (size_t)R);  // [R + 1]
+    int* cursor = start + R + 2;                                                  // [R]
+    int* warp_tot = cursor + R + 2;                                               // [32]
+    int* pairs_s = warp_tot + 32;                                                 // [CP] pair ids of the chunk
+    const int col_a = tile_col_a<PAIRWISE>(w.slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, lane, a.H);
     const int sp_shift = a.nnz <= 32 ? 5 : 6;  // slots per position padded to 32 or 64
+    float bsum_a = 0.f, bsum_b = 0.f;
+    if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line
+
     for (int c0 = w.begin; c0 < w.end; c0 += CP) {
         const int cn = min(CP, w.end - c0);
         for (int r = threadIdx.x; r < R; r += kBwdThreads) cursor[r] = 0;
@@ -400,21 +413,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
         // stage this chunk's gradients at the feature-transformer pre-activation
         for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
             float q0[4], q1[4], q2[4];
-            q2[0] = q2[1] = q2[2] = q2[3] = 0.f;
 #pragma unroll
             for (int k = 0; k < 4; k++) {
                 const int pl = pl0 + k * NW;
-                q0[k] = q1[k] = 0.f;
+                q0[k] = q1[k] = q2[k] = 0.f;
                 if (pl < cn) {
                     const int pair = pairs_s[pl], b = pair >> 1, p = pair & 1;
                     if (PAIRWISE) {
-                        q0[k] = a.u[(size_t)pair * a.H + col_a + lane];
-                        q1[k] = a.u[(size_t)pair * a.H + col_b + lane];
-                        q2[k] = a.dx[(size_t)b * a.H + (size_t)p * (a.H / 2) + col_a + lane];
+                        q0[k] = a.u[(size_t)pair * a.H + col_a];
+                        q1[k] = a.u[(size_t)pair * a.H + col_b];
+                        q2[k] = a.dx[(size_t)b * a.H + p * (a.H / 2) + col_a];
                     } else {
-                        const size_t at = (size_t)b * 2 * a.H + (size_t)p * a.H;
-                        q0[k] = a.dx[at + col_a + lane] * ft_act_bwd(a.act, a.x[at + col_a + lane]);
-                        q1[k] = a.dx[at + col_b + lane] * ft_act_bwd(a.act, a.x[at + col_b + lane]);
+                        const size_t at = (size_t)b * 2 * a.H + p * a.H + col_a;
+                        const float2 d = *reinterpret_cast<const float2*>(a.dx + at);
+                        const float2 y = *reinterpret_cast<const float2*>(a.x + at);
+                        q0[k] = d.x * ft_act_bwd(a.act, y.x);
+                        q1[k] = d.y * ft_act_bwd(a.act, y.y);
                     }
                 }
             }
@@ -427,40 +441,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
                         ga = (q2[k] * q1[k]) * ft_act_bwd(1, q0[k]);
                         gb = (q2[k] * q0[k]) * ft_act_bwd(1, q1[k]);
                     }
-                    g_s[pl * kTileCols + lane] = ga;
-                    g_s[pl * kTileCols + 32 + lane] = gb;
+                    g_s[pl * 32 + lane] = pack2(ga, gb);
                     bsum_a += ga;
                     bsum_b += gb;
                 }
             }
         }
         __syncthreads();
-        // exclusive scan of the row counts -> start[], cursor[] = start[]
+        // exclusive scan of the row counts, each rounded up to a multiple of four
         {
-            int carry = 0;  // rows are scanned in rounds of kBwdThreads
-            for (int base = 0; base < R; base += kBwdThreads) {
-                const int r = base + threadIdx.x;
-                const int v = r < R ? cursor[r] : 0;
-                int incl = v;
+            const int r = threadIdx.x;
+            const int cnt = r < R ? cursor[r] : 0;
+            const int v = (cnt + 3) & ~3;
+            int incl = v;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int n = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += n;
-                }
-                if (lane == 31) warp_tot[warp] = incl;
-                __syncthreads();
-                int before = carry;
-                for (int k = 0; k < warp; k++) before += warp_tot[k];
-                int total = 0;
-                for (int k = 0; k < NW; k++) total += warp_tot[k];
-                if (r < R) {
-                    start[r] = before + incl - v;
-                    cursor[r] = before + incl - v;
-                }
-                carry += total;
-                __syncthreads();
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
             }
-            if (threadIdx.x == 0) start[R] = carry;
+            if (lane == 31) warp_tot[warp] = incl;
+            __syncthreads();
+            int before = 0;
+            for (int k = 0; k < warp; k++) before += warp_tot[k];
+            if (r < R) {
+                start[r] = before + incl - v;
+                cursor[r] = before + incl - v;
+                if (r == R - 1) start[R] = before + incl;
+            }
         }
         __syncthreads();
         // fill: entry = position of the chunk, grouped by row
@@ -479,57 +486,46 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
             }
         }
         __syncthreads();
+        if (threadIdx.x < R)  // pad every list to its rounded length with the all-zero line
+            for (int e = cursor[threadIdx.x]; e < start[threadIdx.x + 1]; e++) ent[e] = (uint16_t)CP;
+        __syncthreads();
         // accumulate: each warp walks the lists of the rows it owns
-#pragma unroll
-        for (int j = 0; j < kBwdRowsPerWarp; j++) {
-            const int row = warp + NW * j;
-            if (row < R) {
-                const int e1 = start[row + 1];
-                const float* gl = g_s + lane;
-                int e = start[row];
-                for (; e + 4 <= e1; e += 4) {
-                    const int p0 = ent[e], p1 = ent[e + 1], p2 = ent[e + 2], p3 = ent[e + 3];
-                    const float a0 = gl[p0 * kTileCols], b0 = gl[p0 * kTileCols + 32];
-                    const float a1 = gl[p1 * kTileCols], b1 = gl[p1 * kTileCols + 32];
-                    const float a2 = gl[p2 * kTileCols], b2 = gl[p2 * kTileCols + 32];
-                    const float a3 = gl[p3 * kTileCols], b3 = gl[p3 * kTileCols + 32];
-                    acc_a[j] += a0, acc_b[j] += b0;
-                    acc_a[j] += a1, acc_b[j] += b1;
-                    acc_a[j] += a2, acc_b[j] += b2;
-                    acc_a[j] += a3, acc_b[j] += b3;
-                }
-                for (; e < e1; e++) {
-                    const int p0 = ent[e];
-                    acc_a[j] += gl[p0 * kTileCols];
-                    acc_b[j] += gl[p0 * kTileCols + 32];
-                }
+        const unsigned char* gl = smem_raw + lane * 8;
+        for (int row = warp; row < R; row += NW) {
+            const int e1 = start[row + 1];
+            f32x2 acc = 0;
+            for (int e = start[row]; e < e1; e += 4) {
+                const uint2 q = *reinterpret_cast<const uint2*>(ent + e);
+                const f32x2 v0 = *reinterpret_cast<const f32x2*>(gl + (q.x & 0xffffu) * kTileRowBytes);
+                const f32x2 v1 = *reinterpret_cast<const f32x2*>(gl + (q.x >> 16) * kTileRowBytes);
+                const f32x2 v2 = *reinterpret_cast<const f32x2*>(gl + (q.y & 0xffffu) * kTileRowBytes);
+                const f32x2 v3 = *reinterpret_cast<const f32x2*>(gl + (q.y >> 16) * kTileRowBytes);
+                acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
+            }
+            float* dst = a.g_table + (size_t)(w.block * R + row) * a.H;
+            const float ga = lo2(acc), gb = hi2(acc);
+            if (PAIRWISE) {
+                if (ga != 0.f) atomicAdd(dst + col_a, ga);
+                if (gb != 0.f) atomicAdd(dst + col_b, gb);
+            } else if (ga != 0.f || gb != 0.f) {
+                atomicAdd(reinterpret_cast<float2*>(dst + col_a), make_float2(ga, gb));
             }
         }
         __syncthreads();
     }
     // bias gradient: every position's gradient once, summed over the warps
-    g_s[warp * kTileCols + lane] = bsum_a;
-    g_s[warp * kTileCols + 32 + lane] = bsum_b;
+    float* red = reinterpret_cast<float*>(smem_raw);
+    red[warp * kTileCols + lane] = bsum_a;
+    red[warp * kTileCols + 32 + lane] = bsum_b;
     __syncthreads();
-    if (threadIdx.x < kTileCols) {
-        float s = 0.f;
-        for (int k = 0; k < NW; k++) s += g_s[k * kTileCols + threadIdx.x];
-        const int col = threadIdx.x < 32 ? col_a + threadIdx.x : col_b + threadIdx.x - 32;
-        if (s != 0.f) atomicAdd(a.g_bias + col, s);
-    }
-#pragma unroll
-    for (int j = 0; j < kBwdRowsPerWarp; j++) {
-        const int row = warp + NW * j;
-        if (row < R) {
-            float* dst = a.g_table + (size_t)(w.block * R + row) * a.H;
-            if (t.nsplit == 1) {
-                dst[col_a + lane] = acc_a[j];
-                dst[col_b + lane] = acc_b[j];
-            } else {
-                if (acc_a[j] != 0.f) atomicAdd(dst + col_a + lane, acc_a[j]);
-                if (acc_b[j] != 0.f) atomicAdd(dst + col_b + lane, acc_b[j]);
-            }
+    if (warp == 0) {
+        float sa = 0.f, sb = 0.f;
+        for (int k = 0; k < NW; k++) {
+            sa += red[k * kTileCols + lane];
+            sb += red[k * kTileCols + 32 + lane];
         }
+        if (sa != 0.f) atomicAdd(a.g_bias + col_a, sa);
+        if (sb != 0.f) atomicAdd(a.g_bias + col_b, sb);
     }
 }
 

@@ -60,7 +60,7 @@ struct Slot {
     char* h_blob = nullptr;
     size_t capacity = 0;
     int n = 0;
-    int n_dtiles = 0;  // warp tiles of the dense kernels held in off_dtiles
+    int n_dtiles = 0;  // CTA tiles of the dense kernels held in off_dtiles
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
            off_dtiles = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
@@ -110,11 +110,10 @@ struct b200_net {
             if (t.name == name) return &t;
         return nullptr;
     }
-    // AUTO: the forward takes the shared-memory tile whenever the inputs allow it; the backward
-    // uses 128-bit global reductions, which the L2 of this part sustains faster than the
-    // register-tile kernel runs (0.61 ms against 1.23 ms at 16384 positions, H = 2048)
+    // AUTO: both passes take the shared-memory kernels whenever the inputs allow it (measured
+    // at 16384 positions, H = 2048: backward 0.50 ms against 0.61 ms for global vector reductions)
     bool fwd_tiled() const { return ft_fwd_mode == B200_FT_TILED || (ft_fwd_mode == B200_FT_AUTO && tiled_ok); }
-    bool bwd_tiled() const { return ft_bwd_mode == B200_FT_TILED; }
+    bool bwd_tiled() const { return ft_bwd_mode == B200_FT_TILED || (ft_bwd_mode == B200_FT_AUTO && tiled_ok); }
 };
 
 namespace {
@@ -179,12 +178,11 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.bytes = off;
 }
 
-size_t fwd_tile_smem(int block_rows) { return (size_t)block_rows * b200::kTileCols * 4 + 32 * 72 * 4; }
-
 template <bool PW>
 int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
     if (tiled) {
-        b200::ft_forward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nsplit, 1024, fwd_tile_smem(t.block_rows), net->stream>>>(a, t);
+        b200::ft_forward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nsplit, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows),
+                                            net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -340,7 +338,7 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
     b200::DenseArgs da = dense_args(net, s, want_grad);
-    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<(s.n_dtiles + 7) / 8, 256, 0, net->stream>>>(da));
+    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<s.n_dtiles, 256, 0, net->stream>>>(da));
     LAUNCHED(net);
     return 0;
 }
@@ -436,8 +434,10 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     }
     net->n_flat = off;
 
+    constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
-                    d.ft_block_rows <= b200::kBwdRowsPerWarp * (b200::kBwdThreads / 32);
+                    d.ft_block_rows <= b200::kBwdThreads && b200::ft_fwd_smem(d.ft_block_rows) <= kMaxSmem &&
+                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz) <= kMaxSmem;
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
 
@@ -487,7 +487,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         for (auto& e : ring) cudaEventCreate(&e);
 
     if (net->tiled_ok) {
-        const int fs = (int)fwd_tile_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz);
+        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
@@ -529,7 +529,7 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
         if (value == B200_FT_TILED && !net->tiled_ok)
             return b200::fail(B200_ERR_UNSUPPORTED,
                               "tiled feature-transformer kernels need ft_block_rows > 0 dividing n_inputs, at most "
-                              "768 rows per block, and ft_out a multiple of 64");
+                              "about 800 rows per block, and ft_out a multiple of 64");
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
         return 0;
@@ -638,7 +638,7 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         for (int i = 0; i < n; i++) begin[h_buckets[i] + 1]++;
         for (int k = 0; k < O; k++) begin[k + 1] += begin[k];
         for (int i = 0; i < n; i++) h_order[begin[h_buckets[i]]++] = i;
-        // warp tiles of the dense kernels: runs of up to kDenseTile positions of one bucket;
+        // CTA tiles of the dense kernels: runs of up to kDenseTile positions of one bucket;
         // after the scatter begin[k] is the END of bucket k's run
         int2* h_tiles = s.host<int2>(s.off_dtiles);
         int nt = 0, at = 0;
@@ -698,14 +698,7 @@ int b200_backward(b200_net* net, int slot) {
     const int chunks = tiled ? splits_for(net, s.n, 0.3) : 1;
     const Tensor* l0w = net->find("l0w");
     const size_t total = (size_t)net->n_flat + kAlignFloats;
-    if (tiled && chunks == 1) {
-        // every (block, slab) tile of the table gradient is stored whole by its CTA
-        const size_t w_end = (size_t)l0w->off + (size_t)((l0w->n + kAlignFloats - 1) / kAlignFloats * kAlignFloats);
-        CK(cudaMemsetAsync(net->G, 0, (size_t)l0w->off * 4, net->stream));
-        CK(cudaMemsetAsync(net->G + w_end, 0, (total - w_end) * 4, net->stream));
-    } else {
-        CK(cudaMemsetAsync(net->G, 0, total * 4, net->stream));
-    }
+    CK(cudaMemsetAsync(net->G, 0, total * 4, net->stream));  // every gradient is accumulated with reductions
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[0], net->stream));
     if (int rc = forward_part(net, s, true)) return rc;
@@ -714,7 +707,7 @@ int b200_backward(b200_net* net, int slot) {
         if (int rc = launch_wgrad(net, s, l)) return rc;
     {
         b200::DenseArgs da = dense_args(net, s, true);
-        DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<(s.n_dtiles + 7) / 8, 256, 0, net->stream>>>(da, net->dx));
+        DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<s.n_dtiles, 256, 0, net->stream>>>(da, net->dx));
         LAUNCHED(net);
     }
     CK(cudaEventRecord(ev[3], net->stream));
