@@ -199,6 +199,7 @@ def run_ours(args, rank, world, local_rank):
                          "(use --impl reference for the CPU oracle)")
     import torch.distributed as dist
 
+    from bullet_b200.dp import DataParallelStep, NetEngine
     from bullet_b200.net import Net
 
     torch.cuda.set_device(local_rank)
@@ -221,13 +222,8 @@ def run_ours(args, rank, world, local_rank):
     if args.ft_bwd_mode:
         net.set_option("ft_bwd_mode", args.ft_bwd_mode)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
-    gptr, gcount = net.grad_buffer()
-
-    class _Dev:
-        __cuda_array_interface__ = {"shape": (gcount,), "typestr": "<f4", "data": (gptr, False), "version": 2}
-
-    grad = torch.as_tensor(_Dev(), device=torch.device("cuda", local_rank)) if world > 1 else None
-    lr, gf = cfg.lr, 1.0 / GLOBAL_BATCH
+    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH)
+    lr = cfg.lr
 
     def barrier():
         torch.cuda.synchronize()
@@ -236,10 +232,7 @@ def run_ours(args, rank, world, local_rank):
             torch.cuda.synchronize()
 
     def one_step(slot):
-        net.backward(slot)
-        if world > 1:
-            dist.all_reduce(grad)
-        net.update(lr, gf)
+        dp.step(slot, lr)  # backward, all-reduce of the flat gradient buffer when N > 1, AdamW
 
     def max_over_ranks(x: float) -> float:
         if world == 1:
