@@ -81,7 +81,7 @@ __device__ __forceinline__ void dense_stage_chunk(const DenseArgs& a, int k, int
     const int c_begin = chunk * kDenseChunk;
     const float* src = a.W1g + ((size_t)k * a.K1 + c_begin) * M1;
     if (M1 % 4 == 0) {
-        constexpr int Q = M1 / 4;  // 16-byte pieces per column
+        constexpr int Q = M1 >= 4 ? M1 / 4 : 1;  // 16-byte pieces per column
         for (int i = threadIdx.x; i < kDenseChunk * Q; i += blockDim.x) {
             const int c = i / Q, q = i % Q;
             float* dst = buf + c * MP + q * 4;

@@ -531,13 +531,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
 
 // ------------------------------------------------------- factoriser helper kernels
 // table[i] = l0w[i] + l0f[i mod block]   (model/builder.rs:421-424 `repeat`, then `+`)
-__global__ void factoriser_merge_kernel(const float4* __restrict__ l0w, const float4* __restrict__ l0f,
+static __global__ void factoriser_merge_kernel(const float4* __restrict__ l0w, const float4* __restrict__ l0f,
                                         float4* __restrict__ table, size_t n4, size_t block4) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
         table[i] = add4(l0w[i], l0f[i % block4]);
 }
 // g_l0f[i] = sum over the tiled copies of g_l0w, first copy first (reduce.rs:96-120)
-__global__ void factoriser_grad_kernel(const float4* __restrict__ g_l0w, float4* __restrict__ g_l0f, size_t block4,
+static __global__ void factoriser_grad_kernel(const float4* __restrict__ g_l0w, float4* __restrict__ g_l0f, size_t block4,
                                        int copies) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < block4; i += (size_t)gridDim.x * blockDim.x) {
         float4 acc = g_l0w[i];

@@ -145,6 +145,26 @@ int b200_net_get_stat(b200_net* net, const char* key, int64_t* value);
  *        2 = gradient at x [n][D1], 3 = network outputs [n]. */
 int b200_net_get_activation(b200_net* net, int which, float* host, int64_t n);
 
+/* ---- operator level: the feature-transformer forward on caller-owned DEVICE memory, without a
+ * b200_net.  For both perspectives of n positions: the sparse affine of SparseMatmul::evaluate
+ * (crates/compiler/src/tensor/operation/linear/sparse.rs:86-119), the bias
+ * (crates/compiler/src/model/builder.rs:145-147), the activation (autograd/dfo.rs:47-88), the
+ * optional pairwise product (model/builder.rs:390-393) and the stm|nstm concat (builder.rs:375-388).
+ * Needs the block structure (ft_block_rows > 0 dividing n_inputs) and ft_out a multiple of 64.
+ * Groups the positions by row block on the device, in scratch memory taken from cudaMalloc for
+ * the duration of the call; runs on `stream` (NULL = default stream) and waits for it. */
+typedef struct b200_ft_op {
+    int32_t n_inputs, nnz, ft_out, ft_act, pairwise, ft_block_rows;
+    int32_t n;                /* positions */
+    const float* table;       /* [n_inputs][ft_out] weights, l0w layout (plus the factoriser if any) */
+    const float* bias;        /* [ft_out] */
+    const uint16_t* idx_stm;  /* [n][nnz] packed indices, 0xFFFF = empty (b200_pack_indices_u16) */
+    const uint16_t* idx_nstm;
+    float* x;                 /* out: [n][2*ft_out], or [n][ft_out] with pairwise */
+    float* u;                 /* out, pairwise only: crelu outputs [n][2][ft_out] */
+} b200_ft_op;
+int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op);
+
 /* ---- host featurisers (no device needed).  Records are the 32-byte layouts of
  * bulletformat's ChessBoard / AtaxxBoard as restated in examples/tests/test4.rs:8-36
  * and examples/ataxx.rs:8-31.  Outputs use the mapper's layout with -1 in every
