@@ -139,17 +139,17 @@ def test_one_step_parity(oracle32, oracle64, name, desc, game):
 
 @pytest.mark.parametrize("name,desc,game", [NETS[1], NETS[4]], ids=[IDS[1], IDS[4]])
 def test_hundred_step_parity(oracle32, oracle64, name, desc, game):
-    """100 AdamW steps: loss and parameters within 1e-3 (norm-wise) of the oracle.
+    """100 AdamW steps on 100 fresh batches: loss within 1e-3 of the oracle at every step,
+    parameters within 1e-3 norm-wise.
 
-    AdamW without bias correction takes near sign-sized steps at first, so rounding noise is
-    amplified along the way: the fp32 oracle itself drifts from its fp64 twin by up to ~2e-3 on
-    some tensors of these nets.  The bound per tensor is therefore 1e-3 or three times that
-    inherent fp32 drift, whichever is larger, measured against the fp64 arbiter."""
-    B, steps = 512, 100
+    AdamW without bias correction takes near sign-sized steps on entries with tiny gradients,
+    which amplifies rounding noise in the sparse tensors: the fp32 oracle itself drifts from its
+    fp64 twin by about 1e-3 on l0f of the bucketed nets.  The bound per tensor is therefore 1e-3
+    or three times that inherent fp32 drift, whichever is larger, against the fp64 arbiter."""
+    B, steps = 1024, 100
     desc = dataclasses.replace(desc, max_batch=B)
-    rec = synth.records(game, B * 4, seed=23)
-    batches = [oracle32.map_batch(game, rec[i * B:(i + 1) * B], desc) for i in range(4)]
-    seq = [batches[i % 4] for i in range(steps)]
+    rec = synth.records(game, B * steps, seed=23)
+    seq = [oracle32.map_batch(game, rec[i * B:(i + 1) * B], desc) for i in range(steps)]
     w = rich_weights(desc)
     hp = AdamWParams()
     w32, _, _, losses32 = oracle32.train(desc, w, seq, 1e-3, hp)
@@ -161,10 +161,9 @@ def test_hundred_step_parity(oracle32, oracle64, name, desc, game):
         net.step(i % 3, 1e-3, 1.0 / B)
         losses.append(net.loss())
     p = net.tensors(0)
-    assert losses64[-1] < 0.8 * losses64[0]
-    drift = abs(losses32[-1] - losses64[-1]) / losses64[-1]
-    assert abs(losses[-1] - losses64[-1]) / losses64[-1] <= max(1e-3, 3 * drift)
-    np.testing.assert_allclose(losses, losses32, rtol=2e-2)  # the whole curve stays close
+    assert losses64[-1] < losses64[0]
+    np.testing.assert_allclose(losses, losses64, rtol=1e-3)
+    np.testing.assert_allclose(losses, losses32, rtol=1e-3)
     for k in w64:
         bound = max(1e-3, 3 * rel2(w32[k], w64[k]))
         assert rel2(p[k], w64[k]) <= bound, (k, rel2(p[k], w64[k]), bound)
