@@ -16,7 +16,7 @@ SYMBOLS = (
     "b200_batch_upload", "b200_step", "b200_backward", "b200_update", "b200_grad_buffer", "b200_loss",
     "b200_forward", "b200_sync", "b200_get_timings", "b200_net_get_activation", "b200_map_chess768",
     "b200_map_chess_buckets_mirrored", "b200_map_ataxx147", "b200_material_count", "b200_make_targets",
-    "b200_pack_indices_u16", "b200_unpack_indices_u16", "b200_net_get_stat", "b200_op_ft_forward",
+    "b200_pack_indices_u16", "b200_unpack_indices_u16", "b200_net_get_stat", "b200_op_ft_forward", "b200_op_ft_forward_noalloc",
 )
 
 
@@ -81,6 +81,7 @@ def load() -> ctypes.CDLL:
         "b200_net_get_activation": [vp, ctypes.c_int, vp, i64],
         "b200_net_get_stat": [vp, cp, ctypes.POINTER(i64)],
         "b200_op_ft_forward": [ctypes.c_int, vp, ctypes.POINTER(CFtOp)],
+        "b200_op_ft_forward_noalloc": [ctypes.c_int, vp, ctypes.POINTER(CFtOp)],
         "b200_map_chess768": [vp, i32, vp, vp, i32],
         "b200_map_chess_buckets_mirrored": [vp, i32, vp, vp, vp, i32],
         "b200_map_ataxx147": [vp, i32, vp, vp, i32],

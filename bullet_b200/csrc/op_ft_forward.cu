@@ -11,8 +11,11 @@
 // The tiled kernel visits (position, perspective) pairs grouped by the table row block their
 // features live in.  A b200_net gets that grouping from the host packer; here it is built on
 // the device into scratch memory: a block id per pair, a histogram, its scan and the grouped
-// pair order, taken from cudaMalloc for the duration of the call.
+// pair order.  b200_op_ft_forward takes that scratch from cudaMalloc for the duration of the
+// call; b200_op_ft_forward_noalloc keeps it in a fixed array that is part of the library image.
 #include <cuda_runtime.h>
+
+#include <mutex>
 
 #include "../../include/bullet_b200.h"
 #include "common.h"
@@ -34,6 +37,13 @@ constexpr int kMaxBlocks = 1024;  // table row blocks the grouping supports
 // cursors, [.. +kMaxBlocks+1] block_begin, then block id per pair [2n], then pair order [2n].
 constexpr size_t kScratchHeader = 1 + (kMaxBlocks + 1) + (kMaxBlocks + 1);
 size_t scratch_ints(int n) { return kScratchHeader + 4 * (size_t)n; }
+
+// Scratch of b200_op_ft_forward_noalloc: room for B200_OP_NOALLOC_MAX_POSITIONS positions
+// (about 270 KB).  It is a file-scope device array, so every GPU on which the library is
+// loaded carries it from load until the process exits, and every call on that GPU uses the
+// same bytes.
+constexpr size_t kStaticInts = kScratchHeader + 4 * (size_t)B200_OP_NOALLOC_MAX_POSITIONS;
+static __device__ __align__(256) int g_op_scratch[kStaticInts];
 
 __global__ void group_count_kernel(const uint16_t* stm, const uint16_t* nstm, int n, int nnz, int n_inputs,
                                    int block_rows, int* counts, int* blk) {
@@ -165,6 +175,48 @@ int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op) {
     const int rc = run_op(static_cast<cudaStream_t>(stream), op, scratch);
     cudaFree(scratch);
     return rc;
+}
+
+// Same result as b200_op_ft_forward without touching the allocator.  It is meant for code
+// that shares a GPU with a running training loop, or that runs after the process has handed
+// out all of its device memory: cudaMalloc and cudaFree synchronise the whole device and
+// serialise on a driver lock, so an evaluation thread that allocated per call would stall the
+// trainer's streams every time, and a caller with a fixed memory budget has nothing left to
+// allocate from.  Here the grouping scratch is the fixed array above and the call makes no
+// cudaMalloc, cudaFree or other allocating call.
+//
+// The first call on each device looks up the array's device address (one
+// cudaGetSymbolAddress, with that device current) and keeps it; make that first call before
+// starting any stream capture on the thread.  All calls on one device share the array and it
+// keeps the previous call's contents: the counters that must start at zero are cleared at
+// the start of every call, and two calls whose GPU work overlaps (different streams or
+// threads, same device) would overwrite each other's grouping — run them one after the other.
+int b200_op_ft_forward_noalloc(int device, void* stream, const b200_ft_op* op) {
+    if (int rc = check_op(op, "op_ft_forward_noalloc")) return rc;
+    if (op->n > B200_OP_NOALLOC_MAX_POSITIONS)
+        return b200::fail(B200_ERR_ARG,
+                          "op_ft_forward_noalloc: %d positions do not fit the fixed scratch, which holds at most %d; "
+                          "split the batch or call b200_op_ft_forward",
+                          op->n, B200_OP_NOALLOC_MAX_POSITIONS);
+    constexpr int kMaxDevices = 64;
+    if (device < 0 || device >= kMaxDevices)
+        return b200::fail(B200_ERR_ARG, "op_ft_forward_noalloc: device %d out of range", device);
+    CK(cudaSetDevice(device));
+    // In host code `g_op_scratch` is only a handle for the runtime, not an address a kernel
+    // could use: ask once per device, with that device current, where the array lives there.
+    static std::mutex lock;
+    static int* address[kMaxDevices] = {nullptr};
+    int* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if (!address[device]) {
+            void* p = nullptr;
+            CK(cudaGetSymbolAddress(&p, g_op_scratch));
+            address[device] = static_cast<int*>(p);
+        }
+        scratch = address[device];
+    }
+    return run_op(static_cast<cudaStream_t>(stream), op, scratch);
 }
 
 }  // extern "C"

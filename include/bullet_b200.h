@@ -165,6 +165,18 @@ typedef struct b200_ft_op {
 } b200_ft_op;
 int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op);
 
+/* The same operator for callers that must not allocate.  (No counterpart in the reference: its
+ * runtime allocates every buffer through its own Buffer type.)  Use it from code that runs
+ * beside a training loop on the same GPU, or after all device memory has been handed out:
+ * cudaMalloc/cudaFree stall every stream of the device, and a fixed memory budget leaves
+ * nothing to allocate.  The grouping scratch is a fixed array inside the library (about 270 KB
+ * on every GPU that loads it), so n is limited to B200_OP_NOALLOC_MAX_POSITIONS; larger n is
+ * refused with B200_ERR_ARG.  No cudaMalloc, cudaFree or other allocating call is made.
+ * The first call on a device looks up the array's address: make it before any stream capture.
+ * Calls on one device share the array, so calls whose GPU work overlaps race: serialise them. */
+#define B200_OP_NOALLOC_MAX_POSITIONS 16384
+int b200_op_ft_forward_noalloc(int device, void* stream, const b200_ft_op* op);
+
 /* ---- host featurisers (no device needed).  Records are the 32-byte layouts of
  * bulletformat's ChessBoard / AtaxxBoard as restated in examples/tests/test4.rs:8-36
  * and examples/ataxx.rs:8-31.  Outputs use the mapper's layout with -1 in every
