@@ -221,6 +221,8 @@ def run_ours(args, rank, world, local_rank):
         net.set_option("ft_fwd_mode", args.ft_fwd_mode)
     if args.ft_bwd_mode:
         net.set_option("ft_bwd_mode", args.ft_bwd_mode)
+    if args.ft_bwd_wide is not None:
+        net.set_option("ft_bwd_wide", args.ft_bwd_wide)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
     dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH)
     lr = cfg.lr
@@ -359,6 +361,7 @@ def main():
     ap.add_argument("--ft-mode", type=int, default=0, help="0 auto, 1 gather kernels, 2 tiled kernels")
     ap.add_argument("--ft-fwd-mode", type=int, default=0)
     ap.add_argument("--ft-bwd-mode", type=int, default=0)
+    ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads x 1 CTA/SM")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,

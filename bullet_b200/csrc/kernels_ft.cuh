@@ -48,6 +48,11 @@ struct TileArgs {
     const int* pair_order;   // [2n] pair ids (position*2 + perspective) grouped by block, or null = identity
     const int* block_begin;  // [nblocks+1] offsets into pair_order
     int* status;
+    // written by ft_prepare_kernel, read by the tiled kernels: for the i-th pair in visiting
+    // order its active rows as tile byte offsets, padded with the zero row to a multiple of four
+    int* lists;       // [2n][list_len]
+    int* list_count;  // [2n] padded length (multiple of 4)
+    int list_len;     // nnz rounded up to a multiple of 4
 };
 
 __device__ __forceinline__ float crelu_f(float v) { return fminf(fmaxf(v, 0.f), 1.f); }
@@ -255,14 +260,47 @@ __device__ __forceinline__ const uint16_t* pair_list(const FtArgs& a, int pair) 
     return ((pair & 1) ? a.idx_nstm : a.idx_stm) + (size_t)(pair >> 1) * a.nnz;
 }
 
+// Per batch, once: turns every (position, perspective) pair's slots into the list the tiled
+// kernels walk — rows local to the pair's block, as byte offsets into a tile (row * 256),
+// compacted in slot order and padded to a multiple of four with the offset of the all-zero
+// row.  A valid feature outside the block raises the status bit and is dropped.  One warp
+// per pair, in visiting order.  grid = ceil(2n / 8), block = 256.
+static __global__ void __launch_bounds__(256) ft_prepare_kernel(FtArgs a, TileArgs t) {
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= 2 * a.n) return;
+    const int pair = t.pair_order ? t.pair_order[i] : i;
+    uint32_t slot0, slot1;
+    load_slots(pair_list(a, pair), a.nnz, lane, slot0, slot1);
+    const bool v0 = slot0 < (uint32_t)a.n_inputs, v1 = slot1 < (uint32_t)a.n_inputs;
+    // the block of a pair is the block of its first valid feature (as the grouping defines it)
+    const unsigned mv0 = __ballot_sync(0xffffffffu, v0), mv1 = __ballot_sync(0xffffffffu, v1);
+    int block = 0;
+    if (mv0)
+        block = (int)__shfl_sync(0xffffffffu, slot0, __ffs(mv0) - 1) / t.block_rows;
+    else if (mv1)
+        block = (int)__shfl_sync(0xffffffffu, slot1, __ffs(mv1) - 1) / t.block_rows;
+    const int row0 = (int)slot0 - block * t.block_rows, row1 = (int)slot1 - block * t.block_rows;
+    const bool in0 = v0 && (unsigned)row0 < (unsigned)t.block_rows, in1 = v1 && (unsigned)row1 < (unsigned)t.block_rows;
+    if ((v0 && !in0) || (v1 && !in1)) atomicOr(t.status, kStatusOutsideBlock);
+    const unsigned m0 = __ballot_sync(0xffffffffu, in0), m1 = __ballot_sync(0xffffffffu, in1);
+    const unsigned lt = (1u << lane) - 1u;
+    const int cnt0 = __popc(m0), cnt = cnt0 + __popc(m1), cnt4 = (cnt + 3) & ~3;
+    int* list = t.lists + (size_t)i * t.list_len;
+    if (in0) list[__popc(m0 & lt)] = row0 * kTileRowBytes;
+    if (in1) list[cnt0 + __popc(m1 & lt)] = row1 * kTileRowBytes;
+    if (lane < cnt4 - cnt) list[cnt + lane] = t.block_rows * kTileRowBytes;
+    if (lane == 0) t.list_count[i] = cnt4;
+}
+
 // Forward.  grid = nblocks * nslabs * nsplit CTAs of 1024 threads (one per SM); dynamic
-// shared memory = (R+1) tile rows (the extra row is all zero) + 32 warps * 72 ints.
-// Each warp serves one (position, perspective) at a time: its lanes compact the position's
-// valid rows into the warp's list of tile byte offsets, padded to a multiple of four with
-// the zero row, then every lane adds its column pair over that list in slot order — the
-// same order and arithmetic as the interpreter (adding the zero row changes nothing).
-constexpr int kFwdThreads = 1024, kFwdListInts = 72;
-__host__ __device__ inline size_t ft_fwd_smem(int R) { return (size_t)(R + 1) * kTileRowBytes + 32 * kFwdListInts * 4; }
+// shared memory = (R+1) tile rows, the extra row all zero.  Each warp serves one
+// (position, perspective) at a time: it walks the pair's prepared list four offsets per
+// (warp-uniform) load, and every lane adds its column pair with one 64-bit shared-memory
+// load and one packed add per row, in slot order — the same order and arithmetic as the
+// interpreter (adding the zero row changes nothing).
+constexpr int kFwdThreads = 1024;
+__host__ __device__ inline size_t ft_fwd_smem(int R) { return (size_t)(R + 1) * kTileRowBytes; }
 
 template <bool PAIRWISE>
 __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs a, TileArgs t) {
@@ -272,7 +310,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
     const TileWork w = tile_work(t);
     const int R = t.block_rows;
     float* tile = reinterpret_cast<float*>(smem_raw);
-    int* offs = reinterpret_cast<int*>(smem_raw + (size_t)(R + 1) * kTileRowBytes) + warp * kFwdListInts;
     {   // fill the tile: 8 work items per row, each 8 floats of the row
         const float* src = a.table + (size_t)w.block * R * a.H;
         for (int i = threadIdx.x; i < R * 8; i += kFwdThreads) {
@@ -293,36 +330,28 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
     }
     const int col_a = tile_col_a<PAIRWISE>(w.slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, lane, a.H);
     const f32x2 bias = pack2(a.bias[col_a], a.bias[col_b]);
-    const int zero_row = R * kTileRowBytes;
     __syncthreads();
     const unsigned char* mine = smem_raw + lane * 8;
-    // the pair id is fetched two positions ahead and the slots one ahead, so their global
-    // latency overlaps the shared-memory work on the current position
-    auto pair_at = [&](int i) { return i < w.end ? (t.pair_order ? t.pair_order[i] : i) : 0; };
+    // outputs of pair p start at p * (row length): x is [n][2 persp][H or H/2], u is [n][2][H]
+    const int x_row = PAIRWISE ? a.H / 2 : a.H;
+    float* x_out = a.x + col_a;  // with pairwise col_a is also the product's column within the perspective
+    // pair id and list length are fetched one position ahead
     int i = w.begin + warp;
-    int pair = pair_at(i), pair_next = pair_at(i + NW);
-    uint32_t slot0 = kNoFeature, slot1 = kNoFeature;
-    if (i < w.end) load_slots(pair_list(a, pair), a.nnz, lane, slot0, slot1);
-    const unsigned lt = (1u << lane) - 1u;
+    int pair = 0, cnt4 = 0;
+    if (i < w.end) {
+        pair = t.pair_order ? t.pair_order[i] : i;
+        cnt4 = t.list_count[i];
+    }
     for (; i < w.end; i += NW) {
-        const int pair_next2 = pair_at(i + 2 * NW);
-        uint32_t next0 = kNoFeature, next1 = kNoFeature;
-        if (i + NW < w.end) load_slots(pair_list(a, pair_next), a.nnz, lane, next0, next1);
-        const int row0 = (int)slot0 - w.block * R, row1 = (int)slot1 - w.block * R;
-        const bool in0 = slot0 < (uint32_t)a.n_inputs && (unsigned)row0 < (unsigned)R;
-        const bool in1 = slot1 < (uint32_t)a.n_inputs && (unsigned)row1 < (unsigned)R;
-        if ((slot0 < (uint32_t)a.n_inputs && !in0) || (slot1 < (uint32_t)a.n_inputs && !in1))
-            atomicOr(t.status, kStatusOutsideBlock);  // dropped rather than read out of bounds
-        const unsigned m0 = __ballot_sync(0xffffffffu, in0), m1 = __ballot_sync(0xffffffffu, in1);
-        const int cnt0 = __popc(m0), cnt = cnt0 + __popc(m1), cnt4 = (cnt + 3) & ~3;
-        __syncwarp();  // the previous position's list has been read by every lane
-        if (in0) offs[__popc(m0 & lt)] = row0 * kTileRowBytes;
-        if (in1) offs[cnt0 + __popc(m1 & lt)] = row1 * kTileRowBytes;
-        if (lane < cnt4 - cnt) offs[cnt + lane] = zero_row;
-        __syncwarp();
+        int pair_next = 0, cnt4_next = 0;
+        if (i + NW < w.end) {
+            pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
+            cnt4_next = t.list_count[i + NW];
+        }
+        const int4* list = reinterpret_cast<const int4*>(t.lists + (size_t)i * t.list_len);
         f32x2 acc = 0;  // (+0.0f, +0.0f)
         for (int k = 0; k < cnt4; k += 4) {
-            const int4 o = *reinterpret_cast<const int4*>(offs + k);
+            const int4 o = __ldg(list + (k >> 2));
             const f32x2 v0 = *reinterpret_cast<const f32x2*>(mine + o.x);
             const f32x2 v1 = *reinterpret_cast<const f32x2*>(mine + o.y);
             const f32x2 v2 = *reinterpret_cast<const f32x2*>(mine + o.z);
@@ -330,86 +359,91 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
             acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
         }
         acc = add2(acc, bias);
-        const int b = pair >> 1, p = pair & 1;
         if (PAIRWISE) {
             const float ua = crelu_f(lo2(acc)), ub = crelu_f(hi2(acc));
             float* up = a.u + (size_t)pair * a.H;
             up[col_a] = ua;
             up[col_b] = ub;
-            a.x[(size_t)b * a.H + p * (a.H / 2) + col_a] = ua * ub;
+            x_out[(size_t)pair * x_row] = ua * ub;
         } else {
-            *reinterpret_cast<float2*>(a.x + (size_t)b * 2 * a.H + p * a.H + col_a) =
+            *reinterpret_cast<float2*>(x_out + (size_t)pair * x_row) =
                 make_float2(ft_act_fwd(a.act, lo2(acc)), ft_act_fwd(a.act, hi2(acc)));
         }
         pair = pair_next;
-        pair_next = pair_next2;
-        slot0 = next0;
-        slot1 = next1;
+        cnt4 = cnt4_next;
     }
 }
 
-// Backward.  Same grid and block size.  Positions are taken in chunks of CP; per chunk the CTA
+// Backward.  Same grid.  Positions are taken in chunks of CP; per chunk the CTA
 //   1. builds in shared memory a row-major list (CSR) of which positions of the chunk hold
-//      each table row: a count pass, a scan and a fill pass over the chunk's slots; every
-//      row's list is padded to a multiple of four entries that point at an all-zero line,
+//      each table row: a count pass, a scan and a fill pass over the chunk's prepared lists;
+//      every row's list is padded to a multiple of four entries that point at an all-zero line,
 //   2. stages the chunk's pre-activation gradients (from dx and the kept activations) as one
 //      64-float line per position, then
-//   3. every warp walks the lists of the rows it owns (row = warp, warp + 32, ...), sums the
+//   3. every warp walks the lists of the rows it owns (row = warp, warp + #warps, ...), sums the
 //      staged lines in registers and adds the row's total to the table gradient with one
 //      global reduction per lane.
 // Shared-memory accumulators need no atomics, and the table gradient sees one reduction per
 // (row, chunk) instead of one per (row, position).  The table gradient must be zero on entry.
-constexpr int kBwdThreads = 1024;
-
-__host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? 512 : 256; }
+// Two shapes: WIDE = one CTA of 1024 threads per SM with 512-position chunks, otherwise two
+// CTAs of 512 threads with 256-position chunks (chunks halve when nnz > 32).
+template <bool WIDE>
+struct BwdShape {
+    static constexpr int kThreads = WIDE ? 1024 : 512, kCtasPerSm = WIDE ? 1 : 2, kChunk = WIDE ? 512 : 256;
+};
+template <bool WIDE>
+__host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? BwdShape<WIDE>::kChunk : BwdShape<WIDE>::kChunk / 2; }
+template <bool WIDE>
 __host__ __device__ inline size_t ft_bwd_smem(int R, int nnz) {
-    const int cp = ft_bwd_chunk(nnz);
-    return (size_t)(cp + 1) * kTileRowBytes + ((size_t)cp * nnz + 4 * (size_t)R) * 2 + (size_t)(2 * R + 4 + 32 + cp) * 4;
+    const int cp = ft_bwd_chunk<WIDE>(nnz), len = (nnz + 3) & ~3;
+    return (size_t)(cp + 1) * kTileRowBytes + ((size_t)cp * len + 4 * (size_t)R) * 2 + (size_t)(2 * R + 4 + 32 + 2 * cp) * 4;
 }
 
-template <bool PAIRWISE>
-__global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
+template <bool PAIRWISE, bool WIDE>
+__global__ void __launch_bounds__(BwdShape<WIDE>::kThreads, BwdShape<WIDE>::kCtasPerSm)
+    ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kBwdThreads = BwdShape<WIDE>::kThreads;
     constexpr int NW = kBwdThreads / 32;
     const TileWork w = tile_work(t);
-    const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz);
+    const int R = t.block_rows, CP = ft_bwd_chunk<WIDE>(a.nnz), L = t.list_len;
     f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                              // [CP + 1][32] (A, B) pairs
     uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists
-    int* start = reinterpret_cast<int*>(ent + (size_t)CP * a.nnz + 4 * (size_t)R);  // [R + 1]
+    int* start = reinterpret_cast<int*>(ent + (size_t)CP * L + 4 * (size_t)R);    // [R + 1]
     int* cursor = start + R + 2;                                                  // [R]
     int* warp_tot = cursor + R + 2;                                               // [32]
     int* pairs_s = warp_tot + 32;                                                 // [CP] pair ids of the chunk
+    int* count_s = pairs_s + CP;                                                  // [CP] prepared list lengths
     const int col_a = tile_col_a<PAIRWISE>(w.slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, lane, a.H);
-    const int sp_shift = a.nnz <= 32 ? 5 : 6;  // slots per position padded to 32 or 64
+    const int zero_row = R * kTileRowBytes;
     float bsum_a = 0.f, bsum_b = 0.f;
     if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line
 
     for (int c0 = w.begin; c0 < w.end; c0 += CP) {
         const int cn = min(CP, w.end - c0);
         for (int r = threadIdx.x; r < R; r += kBwdThreads) cursor[r] = 0;
-        for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
-        __syncthreads();
-        // count how often each row occurs in the chunk; loads are issued four at a time
-        const int total = cn << sp_shift;
-        for (int e0 = threadIdx.x; e0 < total; e0 += 4 * kBwdThreads) {
-            uint32_t v[4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int e = e0 + k * kBwdThreads, sl = e & ((1 << sp_shift) - 1);
-                v[k] = (e < total && sl < a.nnz) ? __ldg(pair_list(a, pairs_s[e >> sp_shift]) + sl) : kNoFeature;
-            }
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int row = (int)v[k] - w.block * R;
-                if (v[k] < (uint32_t)a.n_inputs) {
-                    if ((unsigned)row < (unsigned)R)
-                        atomicAdd(&cursor[row], 1);
-                    else
-                        atomicOr(t.status, kStatusOutsideBlock);
-                }
-            }
+        for (int k = threadIdx.x; k < cn; k += kBwdThreads) {
+            pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
+            count_s[k] = t.list_count[c0 + k];
         }
+        __syncthreads();
+        // count how often each row occurs in the chunk: a warp per position, a lane per list
+        // entry, four positions in flight
+        const int* lists = t.lists + (size_t)c0 * L;
+        for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
+            for (int k0 = 0; k0 < L; k0 += 32) {
+                int o[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int pl = pl0 + k * NW;
+                    o[k] = zero_row;
+                    if (pl < cn && k0 + lane < count_s[pl]) o[k] = __ldg(lists + (size_t)pl * L + k0 + lane);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    if (o[k] != zero_row) atomicAdd(&cursor[o[k] / kTileRowBytes], 1);
+            }
         // stage this chunk's gradients at the feature-transformer pre-activation
         for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
             float q0[4], q1[4], q2[4];
@@ -418,13 +452,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
                 const int pl = pl0 + k * NW;
                 q0[k] = q1[k] = q2[k] = 0.f;
                 if (pl < cn) {
-                    const int pair = pairs_s[pl], b = pair >> 1, p = pair & 1;
+                    const int pair = pairs_s[pl];
                     if (PAIRWISE) {
                         q0[k] = a.u[(size_t)pair * a.H + col_a];
                         q1[k] = a.u[(size_t)pair * a.H + col_b];
-                        q2[k] = a.dx[(size_t)b * a.H + p * (a.H / 2) + col_a];
+                        q2[k] = a.dx[(size_t)pair * (a.H / 2) + col_a];
                     } else {
-                        const size_t at = (size_t)b * 2 * a.H + p * a.H + col_a;
+                        const size_t at = (size_t)pair * a.H + col_a;
                         const float2 d = *reinterpret_cast<const float2*>(a.dx + at);
                         const float2 y = *reinterpret_cast<const float2*>(a.x + at);
                         q0[k] = d.x * ft_act_bwd(a.act, y.x);
@@ -450,44 +484,51 @@ __global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArg
         __syncthreads();
         // exclusive scan of the row counts, each rounded up to a multiple of four
         {
-            const int r = threadIdx.x;
-            const int cnt = r < R ? cursor[r] : 0;
-            const int v = (cnt + 3) & ~3;
-            int incl = v;
+            int carry = 0;
+            for (int base = 0; base < R; base += kBwdThreads) {
+                const int r = base + threadIdx.x;
+                const int v = r < R ? (cursor[r] + 3) & ~3 : 0;
+                int incl = v;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int n = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += n;
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += n;
+                }
+                if (lane == 31) warp_tot[warp] = incl;
+                __syncthreads();
+                int before = carry, all = 0;
+                for (int k = 0; k < NW; k++) {
+                    if (k < warp) before += warp_tot[k];
+                    all += warp_tot[k];
+                }
+                if (r < R) {
+                    start[r] = before + incl - v;
+                    cursor[r] = before + incl - v;
+                }
+                carry += all;
+                __syncthreads();
             }
-            if (lane == 31) warp_tot[warp] = incl;
-            __syncthreads();
-            int before = 0;
-            for (int k = 0; k < warp; k++) before += warp_tot[k];
-            if (r < R) {
-                start[r] = before + incl - v;
-                cursor[r] = before + incl - v;
-                if (r == R - 1) start[R] = before + incl;
-            }
+            if (threadIdx.x == 0) start[R] = carry;
         }
         __syncthreads();
         // fill: entry = position of the chunk, grouped by row
-        for (int e0 = threadIdx.x; e0 < total; e0 += 4 * kBwdThreads) {
-            uint32_t v[4];
+        for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
+            for (int k0 = 0; k0 < L; k0 += 32) {
+                int o[4];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int e = e0 + k * kBwdThreads, sl = e & ((1 << sp_shift) - 1);
-                v[k] = (e < total && sl < a.nnz) ? __ldg(pair_list(a, pairs_s[e >> sp_shift]) + sl) : kNoFeature;
-            }
+                for (int k = 0; k < 4; k++) {
+                    const int pl = pl0 + k * NW;
+                    o[k] = zero_row;
+                    if (pl < cn && k0 + lane < count_s[pl]) o[k] = __ldg(lists + (size_t)pl * L + k0 + lane);
+                }
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int row = (int)v[k] - w.block * R;
-                if (v[k] < (uint32_t)a.n_inputs && (unsigned)row < (unsigned)R)
-                    ent[atomicAdd(&cursor[row], 1)] = (uint16_t)((e0 + k * kBwdThreads) >> sp_shift);
+                for (int k = 0; k < 4; k++)
+                    if (o[k] != zero_row) ent[atomicAdd(&cursor[o[k] / kTileRowBytes], 1)] = (uint16_t)(pl0 + k * NW);
             }
-        }
         __syncthreads();
-        if (threadIdx.x < R)  // pad every list to its rounded length with the all-zero line
-            for (int e = cursor[threadIdx.x]; e < start[threadIdx.x + 1]; e++) ent[e] = (uint16_t)CP;
+        // pad every list to its rounded length with the all-zero line
+        for (int r = threadIdx.x; r < R; r += kBwdThreads)
+            for (int e = cursor[r]; e < start[r + 1]; e++) ent[e] = (uint16_t)CP;
         __syncthreads();
         // accumulate: each warp walks the lists of the rows it owns
         const unsigned char* gl = smem_raw + lane * 8;

@@ -86,12 +86,14 @@ struct b200_net {
     float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr, *w1g = nullptr;
     float* dz[3] = {nullptr, nullptr, nullptr};
     int* status = nullptr;
+    int *ft_lists = nullptr, *ft_list_count = nullptr;  // prepared per-pair row lists of the tiled kernels
     int* h_status = nullptr;
     float* h_loss = nullptr;
     cudaEvent_t loss_ev = nullptr;
     bool loss_pending = false;
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
+    bool bwd_wide = true;  // shape of the tiled backward: one 1024-thread CTA per SM, or two of 512
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
     int last_n = 0;
@@ -195,8 +197,12 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
     if (tiled) {
-        b200::ft_backward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nsplit, b200::kBwdThreads,
-                                             b200::ft_bwd_smem(t.block_rows, a.nnz), net->stream>>>(a, t);
+        if (net->bwd_wide)
+            b200::ft_backward_tiled_kernel<PW, true><<<net->nblocks * t.nslabs * t.nsplit, b200::BwdShape<true>::kThreads,
+                                                       b200::ft_bwd_smem<true>(t.block_rows, a.nnz), net->stream>>>(a, t);
+        else
+            b200::ft_backward_tiled_kernel<PW, false><<<net->nblocks * t.nslabs * t.nsplit, b200::BwdShape<false>::kThreads,
+                                                        b200::ft_bwd_smem<false>(t.block_rows, a.nnz), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -265,6 +271,9 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, int nsplit) {
     t.pair_order = net->nblocks > 1 ? s.dev<int>(s.off_pairs) : nullptr;
     t.block_begin = s.dev<int>(s.off_blocks);
     t.status = net->status;
+    t.lists = net->ft_lists;
+    t.list_count = net->ft_list_count;
+    t.list_len = (net->d.nnz + 3) & ~3;
     return t;
 }
 
@@ -334,6 +343,10 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
     const bool tiled = net->fwd_tiled();
     b200::FtArgs fa = ft_args(net, s);
     b200::TileArgs ta = tile_args(net, s, tiled ? splits_for(net, s.n, 0.1) : 1);
+    if (tiled || (want_grad && net->bwd_tiled())) {
+        b200::ft_prepare_kernel<<<(2 * s.n + 7) / 8, 256, 0, net->stream>>>(fa, ta);
+        LAUNCHED(net);
+    }
     int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled) : launch_ft_forward<false>(net, fa, ta, tiled);
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
@@ -436,8 +449,8 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
 
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
-                    d.ft_block_rows <= b200::kBwdThreads && b200::ft_fwd_smem(d.ft_block_rows) <= kMaxSmem &&
-                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz) <= kMaxSmem;
+                    b200::ft_fwd_smem(d.ft_block_rows) <= kMaxSmem &&
+                    b200::ft_bwd_smem<true>(d.ft_block_rows, d.nnz) <= kMaxSmem;
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
 
@@ -457,6 +470,10 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     rc = rc ? rc : dev_alloc(net, &net->out, B);
     rc = rc ? rc : dev_alloc(net, &net->w1g, (size_t)d.n_out_buckets * d.dense_out[0] * net->D1());
     rc = rc ? rc : dev_alloc(net, &net->status, 1);
+    if (net->tiled_ok) {
+        rc = rc ? rc : dev_alloc(net, &net->ft_lists, 2 * B * ((d.nnz + 3) & ~3));
+        rc = rc ? rc : dev_alloc(net, &net->ft_list_count, 2 * B);
+    }
     if (rc) return bail(rc);
     if (!d.factoriser_rows) net->table = net->P + net->find("l0w")->off;
     cudaMemsetAsync(net->P, 0, net->n_flat * 4, net->stream);
@@ -487,11 +504,14 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         for (auto& e : ring) cudaEventCreate(&e);
 
     if (net->tiled_ok) {
-        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz);
+        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem<true>(d.ft_block_rows, d.nnz);
+        const int bn = (int)b200::ft_bwd_smem<false>(d.ft_block_rows, d.nnz);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
     }
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaGetLastError());
@@ -532,6 +552,10 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
                               "about 800 rows per block, and ft_out a multiple of 64");
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "ft_bwd_wide")) {
+        net->bwd_wide = value != 0;
         return 0;
     }
     return b200::fail(B200_ERR_ARG, "set_option: unknown key '%s'", key);

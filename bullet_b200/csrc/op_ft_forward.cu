@@ -34,15 +34,21 @@ namespace {
 constexpr int kMaxBlocks = 1024;  // table row blocks the grouping supports
 
 // Scratch layout, in ints: [0] status word, [1 .. 1+kMaxBlocks] histogram then running
-// cursors, [.. +kMaxBlocks+1] block_begin, then block id per pair [2n], then pair order [2n].
-constexpr size_t kScratchHeader = 1 + (kMaxBlocks + 1) + (kMaxBlocks + 1);
-size_t scratch_ints(int n) { return kScratchHeader + 4 * (size_t)n; }
+// cursors, [.. +kMaxBlocks+1] block_begin, then per pair: block id [2n], pair order [2n],
+// prepared list length [2n], and the prepared row lists [2n][nnz rounded up to 4].
+// Every section starts on a 256-byte boundary: the row lists are read with 16-byte loads.
+constexpr size_t kSectionAlign = 64;  // ints
+constexpr size_t align_ints(size_t v) { return (v + kSectionAlign - 1) / kSectionAlign * kSectionAlign; }
+constexpr size_t kScratchHeader = align_ints(1 + (kMaxBlocks + 1) + (kMaxBlocks + 1));
+int list_len(int nnz) { return (nnz + 3) & ~3; }
+size_t scratch_ints(int n, int nnz) { return kScratchHeader + 3 * align_ints((size_t)2 * n) + (size_t)2 * n * list_len(nnz); }
 
-// Scratch of b200_op_ft_forward_noalloc: room for B200_OP_NOALLOC_MAX_POSITIONS positions
-// (about 270 KB).  It is a file-scope device array, so every GPU on which the library is
-// loaded carries it from load until the process exits, and every call on that GPU uses the
-// same bytes.
-constexpr size_t kStaticInts = kScratchHeader + 4 * (size_t)B200_OP_NOALLOC_MAX_POSITIONS;
+// Scratch of b200_op_ft_forward_noalloc: room for B200_OP_NOALLOC_MAX_POSITIONS positions of
+// up to 32 index slots (about 4.6 MB).  It is a file-scope device array, so every GPU on
+// which the library is loaded carries it from load until the process exits, and every call
+// on that GPU uses the same bytes.
+constexpr size_t kStaticInts =
+    kScratchHeader + 3 * align_ints((size_t)2 * B200_OP_NOALLOC_MAX_POSITIONS) + (size_t)2 * B200_OP_NOALLOC_MAX_POSITIONS * 32;
 static __device__ __align__(256) int g_op_scratch[kStaticInts];
 
 __global__ void group_count_kernel(const uint16_t* stm, const uint16_t* nstm, int n, int nnz, int n_inputs,
@@ -117,7 +123,9 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     int* counts = scratch + 1;
     int* begin = counts + kMaxBlocks + 1;
     int* blk = scratch + kScratchHeader;
-    int* order = blk + 2 * (size_t)n;
+    int* order = blk + align_ints((size_t)2 * n);
+    int* counts_per_pair = order + align_ints((size_t)2 * n);
+    int* lists = counts_per_pair + align_ints((size_t)2 * n);
     // the scratch keeps whatever the previous call left: clear what must start at zero
     CK(cudaMemsetAsync(scratch, 0, (1 + kMaxBlocks + 1) * sizeof(int), stream));
     const int threads = 256, grid = (2 * n + threads - 1) / threads;
@@ -145,6 +153,11 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     t.pair_order = order;
     t.block_begin = begin;
     t.status = status;
+    t.lists = lists;
+    t.list_count = counts_per_pair;
+    t.list_len = list_len(op->nnz);
+    b200::ft_prepare_kernel<<<(2 * n + 7) / 8, 256, 0, stream>>>(a, t);
+    CK(cudaGetLastError());
     const size_t smem = b200::ft_fwd_smem(R);
     const int ctas = nblocks * t.nslabs;
     if (op->pairwise) {
@@ -171,7 +184,7 @@ int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op) {
     if (int rc = check_op(op, "op_ft_forward")) return rc;
     CK(cudaSetDevice(device));
     int* scratch = nullptr;
-    CK(cudaMalloc(&scratch, scratch_ints(op->n) * sizeof(int)));
+    CK(cudaMalloc(&scratch, scratch_ints(op->n, op->nnz) * sizeof(int)));
     const int rc = run_op(static_cast<cudaStream_t>(stream), op, scratch);
     cudaFree(scratch);
     return rc;
@@ -193,11 +206,12 @@ int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op) {
 // threads, same device) would overwrite each other's grouping — run them one after the other.
 int b200_op_ft_forward_noalloc(int device, void* stream, const b200_ft_op* op) {
     if (int rc = check_op(op, "op_ft_forward_noalloc")) return rc;
-    if (op->n > B200_OP_NOALLOC_MAX_POSITIONS)
+    const int most = op->nnz <= 32 ? B200_OP_NOALLOC_MAX_POSITIONS : B200_OP_NOALLOC_MAX_POSITIONS / 2;
+    if (op->n > most || scratch_ints(op->n, op->nnz) > kStaticInts)
         return b200::fail(B200_ERR_ARG,
-                          "op_ft_forward_noalloc: %d positions do not fit the fixed scratch, which holds at most %d; "
-                          "split the batch or call b200_op_ft_forward",
-                          op->n, B200_OP_NOALLOC_MAX_POSITIONS);
+                          "op_ft_forward_noalloc: %d positions do not fit the fixed scratch, which holds at most %d with "
+                          "nnz=%d; split the batch or call b200_op_ft_forward",
+                          op->n, most, op->nnz);
     constexpr int kMaxDevices = 64;
     if (device < 0 || device >= kMaxDevices)
         return b200::fail(B200_ERR_ARG, "op_ft_forward_noalloc: device %d out of range", device);

@@ -169,9 +169,9 @@ int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op);
  * runtime allocates every buffer through its own Buffer type.)  Use it from code that runs
  * beside a training loop on the same GPU, or after all device memory has been handed out:
  * cudaMalloc/cudaFree stall every stream of the device, and a fixed memory budget leaves
- * nothing to allocate.  The grouping scratch is a fixed array inside the library (about 270 KB
- * on every GPU that loads it), so n is limited to B200_OP_NOALLOC_MAX_POSITIONS; larger n is
- * refused with B200_ERR_ARG.  No cudaMalloc, cudaFree or other allocating call is made.
+ * nothing to allocate.  The grouping scratch is a fixed array inside the library (about 4.6 MB
+ * on every GPU that loads it), so n is limited to B200_OP_NOALLOC_MAX_POSITIONS (half of it
+ * when nnz > 32); larger n is refused with B200_ERR_ARG.  No cudaMalloc, cudaFree or other allocating call is made.
  * The first call on a device looks up the array's address: make it before any stream capture.
  * Calls on one device share the array, so calls whose GPU work overlaps race: serialise them. */
 #define B200_OP_NOALLOC_MAX_POSITIONS 16384
