@@ -224,7 +224,8 @@ def run_ours(args, rank, world, local_rank):
     if args.ft_bwd_wide is not None:
         net.set_option("ft_bwd_wide", args.ft_bwd_wide)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
-    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH)
+    parts = args.dp_parts if (world > 1 and net.stat("ft_tiled") & 2) else 1
+    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts)
     lr = cfg.lr
 
     def barrier():
@@ -234,7 +235,7 @@ def run_ours(args, rank, world, local_rank):
             torch.cuda.synchronize()
 
     def one_step(slot):
-        dp.step(slot, lr)  # backward, all-reduce of the flat gradient buffer when N > 1, AdamW
+        dp.step(slot, lr)  # backward, all-reduce of the flat gradient buffer when N > 1 (pipelined), AdamW
 
     def max_over_ranks(x: float) -> float:
         if world == 1:
@@ -334,7 +335,7 @@ def run_ours(args, rank, world, local_rank):
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
-                   "parallelism": f"dp{world}", "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
+                   "parallelism": f"dp{world}", "allreduce_parts": parts + 1 if parts > 1 else 1, "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
                                   "backward": "tiled" if net.stat("ft_tiled") & 2 else "gather"},
                    "l2": f"inputs larger than L2: {N_DISTINCT} distinct batches cycled, per-step activations "
                          f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
@@ -362,6 +363,8 @@ def main():
     ap.add_argument("--ft-fwd-mode", type=int, default=0)
     ap.add_argument("--ft-bwd-mode", type=int, default=0)
     ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads x 1 CTA/SM")
+    ap.add_argument("--dp-parts", type=int, default=4,
+                    help="N > 1: slices of the l0w gradient all-reduced while the backward still runs (1 = one all-reduce)")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,

@@ -17,6 +17,8 @@ SYMBOLS = (
     "b200_forward", "b200_sync", "b200_get_timings", "b200_net_get_activation", "b200_map_chess768",
     "b200_map_chess_buckets_mirrored", "b200_map_ataxx147", "b200_material_count", "b200_make_targets",
     "b200_pack_indices_u16", "b200_unpack_indices_u16", "b200_net_get_stat", "b200_op_ft_forward", "b200_op_ft_forward_noalloc",
+    "b200_backward_begin", "b200_backward_ft", "b200_backward_end", "b200_grad_part", "b200_update_range",
+    "b200_update_end",
 )
 
 
@@ -73,6 +75,12 @@ def load() -> ctypes.CDLL:
         "b200_step": [vp, ctypes.c_int, f32, f32],
         "b200_backward": [vp, ctypes.c_int],
         "b200_update": [vp, f32, f32],
+        "b200_backward_begin": [vp, ctypes.c_int],
+        "b200_backward_ft": [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int],
+        "b200_backward_end": [vp, ctypes.c_int],
+        "b200_grad_part": [vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(i64), ctypes.POINTER(i64)],
+        "b200_update_range": [vp, f32, f32, i64, i64],
+        "b200_update_end": [vp],
         "b200_grad_buffer": [vp, ctypes.POINTER(vp), ctypes.POINTER(i64)],
         "b200_loss": [vp, ctypes.POINTER(f32)],
         "b200_forward": [vp, ctypes.c_int, vp],

@@ -45,6 +45,7 @@ struct FtArgs {
 struct TileArgs {
     int block_rows;          // R
     int nslabs, nsplit;      // H/64 column slabs; position ranges (CTAs) per (block, slab)
+    int block0;              // first table row block this launch covers (grid spans a run of blocks)
     const int* pair_order;   // [2n] pair ids (position*2 + perspective) grouped by block, or null = identity
     const int* block_begin;  // [nblocks+1] offsets into pair_order
     int* status;
@@ -249,7 +250,7 @@ __device__ __forceinline__ TileWork tile_work(const TileArgs& t) {
     const int split = blockIdx.x % t.nsplit;
     const int rest = blockIdx.x / t.nsplit;
     w.slab = rest % t.nslabs;
-    w.block = rest / t.nslabs;
+    w.block = t.block0 + rest / t.nslabs;
     const int b0 = t.block_begin[w.block], cnt = t.block_begin[w.block + 1] - b0;
     w.begin = b0 + (int)(((long long)cnt * split) / t.nsplit);
     w.end = b0 + (int)(((long long)cnt * (split + 1)) / t.nsplit);
@@ -578,12 +579,14 @@ static __global__ void factoriser_merge_kernel(const float4* __restrict__ l0w, c
         table[i] = add4(l0w[i], l0f[i % block4]);
 }
 // g_l0f[i] = sum over the tiled copies of g_l0w, first copy first (reduce.rs:96-120)
+// `g_l0w` points at the first of `copies` consecutive copies; with `accumulate` the sum is added
+// to what g_l0f already holds (the copies are then visited in several launches).
 static __global__ void factoriser_grad_kernel(const float4* __restrict__ g_l0w, float4* __restrict__ g_l0f, size_t block4,
-                                       int copies) {
+                                       int copies, int accumulate) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < block4; i += (size_t)gridDim.x * blockDim.x) {
         float4 acc = g_l0w[i];
         for (int k = 1; k < copies; k++) acc = add4(acc, g_l0w[(size_t)k * block4 + i]);
-        g_l0f[i] = acc;
+        g_l0f[i] = accumulate ? add4(g_l0f[i], acc) : acc;
     }
 }
 

@@ -29,7 +29,7 @@ struct AdamArgs {
     float4* m;
     float4* v;
     const float4* g;
-    long long total4;
+    long long first4, total4;  // the launch covers float4 indices [first4, first4 + total4)
     int nseg;
     float rate, adj;
     AdamSegment seg[kMaxSegments];
@@ -45,8 +45,9 @@ __device__ __forceinline__ void adam_op(const AdamSegment& s, float rate, float 
 }
 
 __global__ void __launch_bounds__(256) adamw_flat_kernel(const __grid_constant__ AdamArgs a) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < a.total4;
-         i += (long long)gridDim.x * blockDim.x) {
+    for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < a.total4;
+         j += (long long)gridDim.x * blockDim.x) {
+        const long long i = a.first4 + j;
         int si = -1;
 #pragma unroll 1
         for (int k = 0; k < a.nseg; k++)

@@ -7,10 +7,12 @@
 // device memory is allocated once in b200_net_create; a step only enqueues kernels.
 //
 // HBM layout
-//   P, G, M, V   flat fp32 buffers holding every tensor in name order (l0b, l0f, l0w, l1b,
-//                l1w, ...), each tensor starting on a 256-byte boundary.  G carries one
-//                extra element at its end: the summed loss, so a data-parallel host moves
-//                gradients and loss with a single all-reduce.
+//   P, G, M, V   flat fp32 buffers: a 256-byte head whose first float (in G) is the summed
+//                loss, then every tensor in name order (l0b, l0f, l1b, l1w, ...) except l0w,
+//                which comes last; each tensor starts on a 256-byte boundary.  A
+//                data-parallel host moves gradients and loss with one all-reduce of G, or
+//                in parts: runs of l0w row blocks as the backward finishes them, then the
+//                head (loss and all other tensors) in one piece.
 //   table        l0w + tiled l0f (only with a factoriser; otherwise an alias of l0w in P)
 //   x, u, dx     activations kept between forward and backward, position-major
 //   slots        per staging slot one pinned host block and one device block holding the
@@ -93,12 +95,13 @@ struct b200_net {
     bool loss_pending = false;
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
+    int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
     bool bwd_wide = true;  // shape of the tiled backward: one 1024-thread CTA per SM, or two of 512
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
     int last_n = 0;
     // per-step CUDA events on the compute stream, kept for the last kTimingRing steps
-    static constexpr int kTimingRing = 256, kTimingEvents = 7;
+    static constexpr int kTimingRing = 256, kTimingEvents = 8;
     cudaEvent_t tev[kTimingRing][kTimingEvents] = {};
     int64_t steps_begun = 0, steps_done = 0, timing_origin = 0;
     bool step_open = false;
@@ -195,13 +198,13 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 }
 
 template <bool PW>
-int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
+int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int blocks) {
     if (tiled) {
         if (net->bwd_wide)
-            b200::ft_backward_tiled_kernel<PW, true><<<net->nblocks * t.nslabs * t.nsplit, b200::BwdShape<true>::kThreads,
+            b200::ft_backward_tiled_kernel<PW, true><<<blocks * t.nslabs * t.nsplit, b200::BwdShape<true>::kThreads,
                                                        b200::ft_bwd_smem<true>(t.block_rows, a.nnz), net->stream>>>(a, t);
         else
-            b200::ft_backward_tiled_kernel<PW, false><<<net->nblocks * t.nslabs * t.nsplit, b200::BwdShape<false>::kThreads,
+            b200::ft_backward_tiled_kernel<PW, false><<<blocks * t.nslabs * t.nsplit, b200::BwdShape<false>::kThreads,
                                                         b200::ft_bwd_smem<false>(t.block_rows, a.nnz), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
@@ -304,7 +307,7 @@ b200::DenseArgs dense_args(b200_net* net, const Slot& s, bool want_grad) {
     a.a1 = net->a1;
     a.a2 = net->a2;
     a.out = net->out;
-    a.loss = net->G + net->n_flat;
+    a.loss = net->G;
     a.want_grad = want_grad ? 1 : 0;
     return a;
 }
@@ -347,6 +350,7 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
         b200::ft_prepare_kernel<<<(2 * s.n + 7) / 8, 256, 0, net->stream>>>(fa, ta);
         LAUNCHED(net);
     }
+    if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][0], net->stream));
     int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled) : launch_ft_forward<false>(net, fa, ta, tiled);
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
@@ -431,7 +435,6 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     };
     add("l0b", d.ft_out);
     if (d.factoriser_rows) add("l0f", (int64_t)d.factoriser_rows * d.ft_out);
-    add("l0w", (int64_t)d.n_inputs * d.ft_out);
     for (int l = 0; l < d.n_dense; l++) {
         char name[8];
         const int64_t rows = (int64_t)d.n_out_buckets * d.dense_out[l];
@@ -440,7 +443,8 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         snprintf(name, sizeof name, "l%dw", l + 1);
         add(name, rows * net->dense_in(l));
     }
-    int64_t off = 0;
+    add("l0w", (int64_t)d.n_inputs * d.ft_out);  // last, so that everything else is one contiguous head
+    int64_t off = kAlignFloats;                  // float 0 of G is the loss
     for (auto& t : net->tensors) {
         t.off = off;
         off += (t.n + kAlignFloats - 1) / kAlignFloats * kAlignFloats;
@@ -457,7 +461,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     const size_t B = d.max_batch;
     int rc = 0;
     rc = rc ? rc : dev_alloc(net, &net->P, net->n_flat);
-    rc = rc ? rc : dev_alloc(net, &net->G, net->n_flat + kAlignFloats);
+    rc = rc ? rc : dev_alloc(net, &net->G, net->n_flat);
     rc = rc ? rc : dev_alloc(net, &net->M, net->n_flat);
     rc = rc ? rc : dev_alloc(net, &net->V, net->n_flat);
     if (d.factoriser_rows) rc = rc ? rc : dev_alloc(net, &net->table, (size_t)d.n_inputs * d.ft_out);
@@ -477,7 +481,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (rc) return bail(rc);
     if (!d.factoriser_rows) net->table = net->P + net->find("l0w")->off;
     cudaMemsetAsync(net->P, 0, net->n_flat * 4, net->stream);
-    cudaMemsetAsync(net->G, 0, (net->n_flat + kAlignFloats) * 4, net->stream);
+    cudaMemsetAsync(net->G, 0, net->n_flat * 4, net->stream);
     cudaMemsetAsync(net->M, 0, net->n_flat * 4, net->stream);
     cudaMemsetAsync(net->V, 0, net->n_flat * 4, net->stream);
     cudaMemsetAsync(net->status, 0, 4, net->stream);
@@ -711,67 +715,125 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
     return 0;
 }
 
-int b200_backward(b200_net* net, int slot) {
-    if (int rc = check_slot(net, slot, "backward")) return rc;
+// ---- the backward pass in three phases (b200_backward runs them back to back)
+
+int b200_backward_begin(b200_net* net, int slot) {
+    if (int rc = check_slot(net, slot, "backward_begin")) return rc;
     if (int rc = set_device(net)) return rc;
     Slot& s = net->slots[slot];
     const b200_net_desc& d = net->d;
     CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
     if (int rc = refresh_table(net)) return rc;
-    const bool tiled = net->bwd_tiled();
-    const int chunks = tiled ? splits_for(net, s.n, 0.3) : 1;
-    const Tensor* l0w = net->find("l0w");
-    const size_t total = (size_t)net->n_flat + kAlignFloats;
-    CK(cudaMemsetAsync(net->G, 0, total * 4, net->stream));  // every gradient is accumulated with reductions
-    cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
-    CK(cudaEventRecord(ev[0], net->stream));
+    CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->stream));  // every gradient is accumulated with reductions
     if (int rc = forward_part(net, s, true)) return rc;
+    cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[2], net->stream));
-    for (int l = d.n_dense - 1; l >= 0; l--)
-        if (int rc = launch_wgrad(net, s, l)) return rc;
     {
         b200::DenseArgs da = dense_args(net, s, true);
         DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<s.n_dtiles, 256, 0, net->stream>>>(da, net->dx));
         LAUNCHED(net);
     }
     CK(cudaEventRecord(ev[3], net->stream));
-    {
-        b200::FtArgs fa = ft_args(net, s);
-        b200::TileArgs ta = tile_args(net, s, chunks);
-        int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled) : launch_ft_backward<false>(net, fa, ta, tiled);
-        if (rc) return rc;
-    }
-    CK(cudaEventRecord(ev[4], net->stream));
-    if (d.factoriser_rows) {
-        const Tensor* f = net->find("l0f");
-        b200::factoriser_grad_kernel<<<kSmCount * 4, 256, 0, net->stream>>>(
-            reinterpret_cast<const float4*>(net->G + l0w->off), reinterpret_cast<float4*>(net->G + f->off),
-            (size_t)f->n / 4, (int)(l0w->n / f->n));
-        LAUNCHED(net);
-    }
-    CK(cudaEventRecord(ev[5], net->stream));
-    CK(cudaEventRecord(s.consumed, net->stream));
-    s.has_consumed = true;
-    net->have_backward = true;
-    net->step_open = true;
+    net->bwd_slot = slot;
+    net->bwd_parts_done = 0;
     net->last_n = s.n;
     return 0;
 }
 
-int b200_update(b200_net* net, float lr, float grad_factor) {
-    if (!net) return b200::fail(B200_ERR_ARG, "update: null net");
-    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update: no gradients yet, call b200_backward first");
+int b200_backward_ft(b200_net* net, int slot, int part, int n_parts) {
+    if (int rc = check_slot(net, slot, "backward_ft")) return rc;
+    if (net->bwd_slot != slot) return b200::fail(B200_ERR_STATE, "backward_ft: call b200_backward_begin on slot %d first", slot);
+    const bool tiled = net->bwd_tiled();
+    if (n_parts < 1 || part < 0 || part >= n_parts || part != net->bwd_parts_done)
+        return b200::fail(B200_ERR_ARG, "backward_ft: parts must be run in order 0..n_parts-1 (got %d of %d)", part, n_parts);
+    if (n_parts > 1 && (!tiled || net->nblocks % n_parts))
+        return b200::fail(B200_ERR_UNSUPPORTED, "backward_ft: %d parts need the tiled backward and must divide the %d row blocks",
+                          n_parts, net->nblocks);
     if (int rc = set_device(net)) return rc;
-    CK(cudaMemcpyAsync(net->h_loss, net->G + net->n_flat, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
-    CK(cudaMemcpyAsync(net->h_status, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
-    CK(cudaEventRecord(net->loss_ev, net->stream));
-    net->loss_pending = true;
+    Slot& s = net->slots[slot];
+    const b200_net_desc& d = net->d;
+    cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
+    const int per = net->nblocks / n_parts;
+    const Tensor* l0w = net->find("l0w");
+    {
+        b200::FtArgs fa = ft_args(net, s);
+        b200::TileArgs ta = tile_args(net, s, tiled ? splits_for(net, s.n, 0.3) : 1);
+        ta.block0 = part * per;
+        const int blocks = tiled ? per : 1;
+        int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled, blocks) : launch_ft_backward<false>(net, fa, ta, tiled, blocks);
+        if (rc) return rc;
+    }
+    if (part == n_parts - 1) CK(cudaEventRecord(ev[4], net->stream));
+    if (d.factoriser_rows) {
+        // sum of this part's copies of the factoriser rows; with one part: all copies, in order
+        const Tensor* f = net->find("l0f");
+        const int copies = (int)(l0w->n / f->n), per_part = copies / n_parts;
+        if (copies % n_parts) return b200::fail(B200_ERR_UNSUPPORTED, "backward_ft: %d parts do not divide %d factoriser copies", n_parts, copies);
+        b200::factoriser_grad_kernel<<<kSmCount * 4, 256, 0, net->stream>>>(
+            reinterpret_cast<const float4*>(net->G + l0w->off + (int64_t)part * per_part * f->n),
+            reinterpret_cast<float4*>(net->G + f->off), (size_t)f->n / 4, per_part, part > 0);
+        LAUNCHED(net);
+    }
+    if (part == n_parts - 1) CK(cudaEventRecord(ev[5], net->stream));
+    net->bwd_parts_done = part + 1;
+    net->bwd_parts = n_parts;
+    return 0;
+}
+
+int b200_backward_end(b200_net* net, int slot) {
+    if (int rc = check_slot(net, slot, "backward_end")) return rc;
+    if (net->bwd_slot != slot || net->bwd_parts_done < 1 || net->bwd_parts_done != net->bwd_parts)
+        return b200::fail(B200_ERR_STATE, "backward_end: run b200_backward_begin and every b200_backward_ft part first");
+    if (int rc = set_device(net)) return rc;
+    Slot& s = net->slots[slot];
+    for (int l = net->d.n_dense - 1; l >= 0; l--)
+        if (int rc = launch_wgrad(net, s, l)) return rc;
+    cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
+    CK(cudaEventRecord(ev[6], net->stream));
+    CK(cudaEventRecord(s.consumed, net->stream));
+    s.has_consumed = true;
+    net->have_backward = true;
+    net->step_open = true;
+    net->bwd_slot = -1;
+    return 0;
+}
+
+int b200_backward(b200_net* net, int slot) {
+    if (int rc = b200_backward_begin(net, slot)) return rc;
+    if (int rc = b200_backward_ft(net, slot, 0, 1)) return rc;
+    return b200_backward_end(net, slot);
+}
+
+int b200_grad_part(b200_net* net, int part, int n_parts, int64_t* first_float, int64_t* n_floats) {
+    if (!net || !first_float || !n_floats) return b200::fail(B200_ERR_ARG, "grad_part: null argument");
+    const Tensor* l0w = net->find("l0w");
+    if (n_parts < 1 || part < 0 || part > n_parts) return b200::fail(B200_ERR_ARG, "grad_part: part %d of %d", part, n_parts);
+    if (part == n_parts) {  // the head: loss and every tensor but l0w
+        *first_float = 0;
+        *n_floats = l0w->off;
+        return 0;
+    }
+    if (net->nblocks % n_parts) return b200::fail(B200_ERR_UNSUPPORTED, "grad_part: %d parts do not divide %d row blocks", n_parts, net->nblocks);
+    const int64_t per = l0w->n / n_parts;
+    *first_float = l0w->off + part * per;
+    *n_floats = part == n_parts - 1 ? net->n_flat - *first_float : per;  // the last part takes the alignment tail
+    return 0;
+}
+
+int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_float, int64_t n_floats) {
+    if (!net) return b200::fail(B200_ERR_ARG, "update_range: null net");
+    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_range: no gradients yet, call b200_backward first");
+    if (first_float < 0 || n_floats < 1 || first_float + n_floats > net->n_flat || first_float % 4 || n_floats % 4)
+        return b200::fail(B200_ERR_ARG, "update_range: [%lld, +%lld) is not a 4-float-aligned range of the flat buffer",
+                          (long long)first_float, (long long)n_floats);
+    if (int rc = set_device(net)) return rc;
     b200::AdamArgs a{};
     a.p = reinterpret_cast<float4*>(net->P);
     a.m = reinterpret_cast<float4*>(net->M);
     a.v = reinterpret_cast<float4*>(net->V);
     a.g = reinterpret_cast<const float4*>(net->G);
-    a.total4 = net->n_flat / 4;
+    a.first4 = first_float / 4;
+    a.total4 = n_floats / 4;
     a.rate = lr;
     a.adj = grad_factor;
     a.nseg = (int)net->tensors.size();
@@ -783,14 +845,31 @@ int b200_update(b200_net* net, float lr, float grad_factor) {
     b200::adamw_flat_kernel<<<(unsigned)blocks, 256, 0, net->stream>>>(a);
     LAUNCHED(net);
     net->table_dirty = true;
+    return 0;
+}
+
+int b200_update_end(b200_net* net) {
+    if (!net) return b200::fail(B200_ERR_ARG, "update_end: null net");
+    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_end: no gradients yet");
+    if (int rc = set_device(net)) return rc;
+    CK(cudaMemcpyAsync(net->h_loss, net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaMemcpyAsync(net->h_status, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaEventRecord(net->loss_ev, net->stream));
+    net->loss_pending = true;
     if (int rc = refresh_table(net)) return rc;
     if (net->step_open) {  // close the timed step begun by the matching backward
-        CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][6], net->stream));
+        CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][7], net->stream));
         net->steps_begun++;
         net->steps_done = net->steps_begun;
         net->step_open = false;
     }
     return 0;
+}
+
+int b200_update(b200_net* net, float lr, float grad_factor) {
+    if (!net) return b200::fail(B200_ERR_ARG, "update: null net");
+    if (int rc = b200_update_range(net, lr, grad_factor, 0, net->n_flat)) return rc;
+    return b200_update_end(net);
 }
 
 int b200_step(b200_net* net, int slot, float lr, float grad_factor) {
@@ -801,7 +880,7 @@ int b200_step(b200_net* net, int slot, float lr, float grad_factor) {
 int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats) {
     if (!net || !device_ptr || !n_floats) return b200::fail(B200_ERR_ARG, "grad_buffer: null argument");
     *device_ptr = net->G;
-    *n_floats = net->n_flat + 1;
+    *n_floats = net->n_flat;
     return 0;
 }
 
@@ -855,25 +934,27 @@ int b200_get_timings(b200_net* net, b200_timings* out) {
     net->timing_origin = net->steps_done;
     if (count < 1) return b200::fail(B200_ERR_STATE, "get_timings: no complete step since the last call");
     CK(cudaStreamSynchronize(net->stream));
-    double acc[7] = {0, 0, 0, 0, 0, 0, 0};
+    // events: 0 start, 1 FT forward, 2 dense forward, 3 dx, 4 FT backward, 5 factoriser sums,
+    // 6 dense weight gradients, 7 update
+    double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int64_t i = first; i < net->steps_done; i++) {
         cudaEvent_t* ev = net->tev[i % b200_net::kTimingRing];
         float ms = 0.f;
-        for (int k = 0; k < 6; k++) {
+        for (int k = 0; k < 7; k++) {
             CK(cudaEventElapsedTime(&ms, ev[k], ev[k + 1]));
             acc[k] += ms;
         }
-        CK(cudaEventElapsedTime(&ms, ev[0], ev[6]));
-        acc[6] += ms;
+        CK(cudaEventElapsedTime(&ms, ev[0], ev[7]));
+        acc[7] += ms;
     }
     const double inv = 1.0 / (double)count;
     out->ft_forward = (float)(acc[0] * inv);
     out->dense_forward = (float)(acc[1] * inv);
-    out->dense_backward = (float)(acc[2] * inv);
+    out->dense_backward = (float)((acc[2] + acc[5]) * inv);
     out->ft_backward = (float)(acc[3] * inv);
     out->factoriser_grad = (float)(acc[4] * inv);
-    out->optimiser = (float)(acc[5] * inv);
-    out->total = (float)(acc[6] * inv);
+    out->optimiser = (float)(acc[6] * inv);
+    out->total = (float)(acc[7] * inv);
     out->steps = (int32_t)count;
     return 0;
 }

@@ -2,9 +2,15 @@
 
 Positions are independent, so a global batch is cut into equal contiguous shards, one per
 rank; every rank holds a full replica of the weights and the optimiser state.  The only
-exchange is one sum all-reduce of the flat gradient buffer (whose last element carries the
+exchange is a sum all-reduce of the flat gradient buffer (whose first element carries the
 summed loss) between the backward pass and the AdamW update; the update then runs on every
 replica with grad_factor = 1 / global batch, which keeps the replicas bit-identical.
+
+With `parts > 1` the exchange is pipelined against the backward pass: the feature-transformer
+backward runs one run of table row blocks at a time, and the all-reduce of a finished slice of
+the l0w gradient (by far the largest tensor) travels while the next slice and the dense
+layers' weight gradients are still being computed; AdamW then runs slice by slice as the
+reduced slices arrive.  Every rank issues the same collectives in the same order.
 
 The reference has no multi-GPU path (one device chosen by ordinal,
 crates/bullet_lib/src/value/builder.rs:97-100); this module is new work on top of its step
@@ -32,14 +38,15 @@ def shard_batch(batch, rank: int, world: int):
 
 
 class DataParallelStep:
-    """Runs backward -> all-reduce -> update on an engine.
+    """Runs backward -> all-reduce -> update on an engine, in one piece or pipelined.
 
-    The engine is anything with the calls of `bullet_b200.net.Net` used here: `backward(slot)`,
-    `update(lr, grad_factor)` and a `grad` attribute holding a torch tensor that aliases the
-    flat gradient buffer (loss in its last element).
+    The engine is anything with the calls of `bullet_b200.net.Net` used here and a `grad`
+    attribute holding a torch tensor that aliases the flat gradient buffer.  For `parts == 1`
+    it needs `backward(slot)` and `update(lr, grad_factor)`; for `parts > 1` also
+    `backward_begin/backward_ft/backward_end`, `grad_part`, `update_range`, `update_end`.
     """
 
-    def __init__(self, engine, global_batch: int, process_group=None):
+    def __init__(self, engine, global_batch: int, parts: int = 1, process_group=None):
         import torch.distributed as dist
 
         self.engine = engine
@@ -47,12 +54,32 @@ class DataParallelStep:
         self.group = process_group
         self.dist = dist
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.parts = parts if self.world > 1 else 1
 
     def step(self, slot: int, lr: float) -> None:
-        self.engine.backward(slot)
-        if self.world > 1:
-            self.dist.all_reduce(self.engine.grad, group=self.group)
-        self.engine.update(lr, 1.0 / self.global_batch)
+        eng, gf = self.engine, 1.0 / self.global_batch
+        if self.parts == 1:
+            eng.backward(slot)
+            if self.world > 1:
+                self.dist.all_reduce(eng.grad, group=self.group)
+            eng.update(lr, gf)
+            return
+        eng.backward_begin(slot)
+        pending = []
+        for part in range(self.parts):
+            eng.backward_ft(slot, part, self.parts)
+            first, count = eng.grad_part(part, self.parts)
+            # the collective waits for the kernels enqueued so far and runs beside the next ones
+            work = self.dist.all_reduce(eng.grad[first:first + count], group=self.group, async_op=True)
+            pending.append((work, first, count))
+        eng.backward_end(slot)
+        first, count = eng.grad_part(self.parts, self.parts)
+        pending.append((self.dist.all_reduce(eng.grad[first:first + count], group=self.group, async_op=True),
+                        first, count))
+        for work, first, count in pending:
+            work.wait()  # orders the compute stream after the collective; the host does not block
+            eng.update_range(lr, gf, first, count)
+        eng.update_end()
 
 
 def wrap_device_buffer(ptr: int, count: int, device):
@@ -72,9 +99,6 @@ class NetEngine:
         self.net = net
         ptr, count = net.grad_buffer()
         self.grad = wrap_device_buffer(ptr, count, device)
-
-    def backward(self, slot: int) -> None:
-        self.net.backward(slot)
-
-    def update(self, lr: float, grad_factor: float) -> None:
-        self.net.update(lr, grad_factor)
+        for name in ("backward", "update", "backward_begin", "backward_ft", "backward_end", "grad_part",
+                     "update_range", "update_end"):
+            setattr(self, name, getattr(net, name))

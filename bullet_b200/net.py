@@ -93,6 +93,27 @@ class Net:
     def update(self, lr: float, grad_factor: float) -> None:
         _lib.check(self.lib.b200_update(self._h, lr, grad_factor))
 
+    # the same step in phases (see include/bullet_b200.h); used by the data-parallel host
+    def backward_begin(self, slot: int) -> None:
+        _lib.check(self.lib.b200_backward_begin(self._h, slot))
+
+    def backward_ft(self, slot: int, part: int, n_parts: int) -> None:
+        _lib.check(self.lib.b200_backward_ft(self._h, slot, part, n_parts))
+
+    def backward_end(self, slot: int) -> None:
+        _lib.check(self.lib.b200_backward_end(self._h, slot))
+
+    def grad_part(self, part: int, n_parts: int) -> tuple[int, int]:
+        first, count = ctypes.c_int64(), ctypes.c_int64()
+        _lib.check(self.lib.b200_grad_part(self._h, part, n_parts, ctypes.byref(first), ctypes.byref(count)))
+        return first.value, count.value
+
+    def update_range(self, lr: float, grad_factor: float, first: int, count: int) -> None:
+        _lib.check(self.lib.b200_update_range(self._h, lr, grad_factor, first, count))
+
+    def update_end(self) -> None:
+        _lib.check(self.lib.b200_update_end(self._h))
+
     def loss(self) -> float:
         v = ctypes.c_float()
         _lib.check(self.lib.b200_loss(self._h, ctypes.byref(v)))
@@ -122,7 +143,7 @@ class Net:
         return out
 
     def grad_buffer(self):
-        """(device address, number of floats) of the flat gradient buffer; the last float is the loss."""
+        """(device address, number of floats) of the flat gradient buffer; the first float is the loss."""
         ptr, n = ctypes.c_void_p(), ctypes.c_int64()
         _lib.check(self.lib.b200_grad_buffer(self._h, ctypes.byref(ptr), ctypes.byref(n)))
         return ptr.value, n.value

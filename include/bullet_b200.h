@@ -124,9 +124,30 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
 int b200_step(b200_net* net, int slot, float lr, float grad_factor);
 int b200_backward(b200_net* net, int slot);
 int b200_update(b200_net* net, float lr, float grad_factor);
-/* Device address and length (floats) of the flat gradient buffer; its last
+/* Device address and length (floats) of the flat gradient buffer; its FIRST
  * element is the summed loss, so one all-reduce carries both. */
 int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
+
+/* The same step in phases, for a host that overlaps the gradient exchange with the backward
+ * pass.  b200_backward = begin + ft(0, 1) + end; b200_update = update_range(whole buffer) + end.
+ *   b200_backward_begin  zeroes the gradients, runs the forward, the loss and the backward
+ *                        down to the gradient at the feature transformer's output;
+ *   b200_backward_ft     feature-transformer backward for the part-th of n_parts equal runs of
+ *                        table row blocks, in order (n_parts > 1 needs the tiled backward and
+ *                        must divide the number of row blocks); when it returns, part's slice
+ *                        of the l0w gradient is complete on the stream and may be all-reduced;
+ *   b200_backward_end    the dense layers' weight gradients; afterwards the head is complete;
+ *   b200_grad_part       flat range [first, first + count) of the gradient buffer that part
+ *                        covers; part == n_parts names the head: the loss and every tensor
+ *                        except l0w;
+ *   b200_update_range    AdamW+clip on a 4-float-aligned range of the flat buffer;
+ *   b200_update_end      after all ranges: rebuilds the derived tables, queues the loss read. */
+int b200_backward_begin(b200_net* net, int slot);
+int b200_backward_ft(b200_net* net, int slot, int part, int n_parts);
+int b200_backward_end(b200_net* net, int slot);
+int b200_grad_part(b200_net* net, int part, int n_parts, int64_t* first_float, int64_t* n_floats);
+int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_float, int64_t n_floats);
+int b200_update_end(b200_net* net);
 /* Summed loss of the most recent update/step (run.rs:212-221); waits for it. */
 int b200_loss(b200_net* net, float* loss_sum);
 /* Forward only: network output per position (ModelEvaluator, crates/trainer/src/model/evaluator.rs:22-81). */

@@ -17,7 +17,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 class OracleEngine:
-    """The engine interface of bullet_b200.dp implemented with the CPU oracle (test only)."""
+    """The engine interface of bullet_b200.dp implemented with the CPU oracle (test only).
+
+    Flat gradient layout as in the library: [loss, padding][all tensors but l0w][l0w]."""
+
+    HEAD = 64
 
     def __init__(self, desc, weights, hp):
         from oracle import Oracle
@@ -26,30 +30,65 @@ class OracleEngine:
         self.desc, self.hp = desc, hp
         self.w = self.orc.to_real(weights)
         self.m, self.v = self.orc.zeros_like(desc), self.orc.zeros_like(desc)
-        self.names = list(desc.tensor_shapes())
-        self.sizes = [self.w[k].size for k in self.names]
-        self.grad = torch.zeros(sum(self.sizes) + 1, dtype=torch.float32)
+        self.names = [k for k in desc.tensor_shapes() if k != "l0w"] + ["l0w"]
+        self.offsets, at = {}, self.HEAD
+        for k in self.names:
+            self.offsets[k] = at
+            at += self.w[k].size
+        self.grad = torch.zeros(at, dtype=torch.float32)
         self.slots = {}
 
     def upload(self, slot, *batch):
         self.slots[slot] = batch
 
+    # ---- one-piece form
     def backward(self, slot):
         loss, g, _ = self.orc.net_grad(self.desc, self.w, *self.slots[slot])
-        flat = np.concatenate([g[k] for k in self.names] + [np.array([loss], np.float32)])
-        self.grad.copy_(torch.from_numpy(flat))
+        flat = self.grad.numpy()
+        flat[:] = 0
+        flat[0] = loss
+        for k in self.names:
+            flat[self.offsets[k]:self.offsets[k] + g[k].size] = g[k]
 
     def update(self, lr, grad_factor):
+        self.update_range(lr, grad_factor, 0, self.grad.numel())
+        self.update_end()
+
+    # ---- phased form: the oracle computes everything at once, the phases only expose the ranges
+    def backward_begin(self, slot):
+        self.backward(slot)
+
+    def backward_ft(self, slot, part, n_parts):
+        pass
+
+    def backward_end(self, slot):
+        pass
+
+    def grad_part(self, part, n_parts):
+        lo = self.offsets["l0w"]
+        if part == n_parts:
+            return 0, lo
+        per = self.w["l0w"].size // n_parts
+        return lo + part * per, per
+
+    def update_range(self, lr, grad_factor, first, count):
         flat = self.grad.numpy()
-        g, at = {}, 0
-        for k, n in zip(self.names, self.sizes):
-            g[k] = np.ascontiguousarray(flat[at:at + n])
-            at += n
-        self.last_loss = float(flat[-1])
-        self.orc.net_update(self.desc, self.w, self.m, self.v, g, grad_factor, lr, self.hp)
+        self.last_loss = float(flat[0])
+        for k in self.names:
+            lo, n = self.offsets[k], self.w[k].size
+            a, b = max(lo, first), min(lo + n, first + count)
+            if a >= b:
+                continue
+            sl = slice(a - lo, b - lo)
+            p, m, v = (np.ascontiguousarray(t[k][sl]) for t in (self.w, self.m, self.v))
+            self.orc.adamw(p, m, v, np.ascontiguousarray(flat[a:b]), grad_factor, lr, self.hp)
+            self.w[k][sl], self.m[k][sl], self.v[k][sl] = p, m, v
+
+    def update_end(self):
+        pass
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, parts):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -63,7 +102,7 @@ def _worker(rank, world, port, out_dir):
     orc = Oracle("f32")
     weights = synth.init_weights(desc, seed=3)
     eng = OracleEngine(desc, weights, AdamWParams())
-    dp = DataParallelStep(eng, global_batch=256)
+    dp = DataParallelStep(eng, global_batch=256, parts=parts)
     losses = []
     for step in range(3):
         full = orc.map_batch(c.game, synth.records(c.game, 256, seed=50 + step), desc)
@@ -74,7 +113,8 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_rank_data_parallel_matches_single_rank(tmp_path):
+@pytest.mark.parametrize("parts", [1, 4])
+def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts):
     from bullet_b200 import config, synth
     from bullet_b200.configs import AdamWParams
     from bullet_b200.dp import shard_bounds
@@ -83,8 +123,8 @@ def test_two_rank_data_parallel_matches_single_rank(tmp_path):
     assert shard_bounds(8, 1, 2) == (4, 8)
     with pytest.raises(ValueError):
         shard_bounds(7, 0, 2)
-    port = 29500 + os.getpid() % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    port = 29500 + (os.getpid() + 7 * parts) % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path), parts), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     c = config(3)
     desc = dataclasses.replace(c.desc, ft_out=64, max_batch=256)

@@ -195,6 +195,49 @@ def test_per_tensor_adamw_params_and_clipping(oracle32):
     net.close()
 
 
+def test_phased_step_equals_one_piece_step(oracle32):
+    """begin / ft parts / end / update_range / update_end give what step() gives (the factoriser
+    gradient is summed per part, so it may differ in the last bits)."""
+    name, desc, game = NETS[4]
+    B = 700
+    desc = dataclasses.replace(desc, max_batch=B)
+    batch = oracle32.map_batch(game, synth.records(game, B, seed=25), desc)
+    w = rich_weights(desc)
+    ref = make_net(desc, FT_TILED, w)
+    ref.upload(0, *batch)
+    ref.step(0, 1e-3, 1.0 / B)
+    loss_ref, g_ref, p_ref = ref.loss(), ref.tensors(3), ref.tensors(0)
+    for parts in (1, 2, 16):
+        net = make_net(desc, FT_TILED, w)
+        net.upload(0, *batch)
+        net.backward_begin(0)
+        for part in range(parts):
+            net.backward_ft(0, part, parts)
+        net.backward_end(0)
+        ranges = [net.grad_part(part, parts) for part in range(parts + 1)]
+        assert ranges[parts][0] == 0 and ranges[0][0] == ranges[parts][1]          # head, then l0w slices
+        assert sum(c for _, c in ranges) == net.grad_buffer()[1]
+        for first, count in ranges:
+            net.update_range(1e-3, 1.0 / B, first, count)
+        net.update_end()
+        assert abs(net.loss() - loss_ref) <= 1e-6 * abs(loss_ref)
+        g, p = net.tensors(3), net.tensors(0)
+        for k in g_ref:
+            assert rel2(g[k], g_ref[k]) <= 1e-6 and rel2(p[k], p_ref[k]) <= 1e-6, (parts, k)
+        net.close()
+    ref.close()
+    from bullet_b200._lib import B200Error
+
+    net = make_net(desc, FT_TILED, w)
+    net.upload(0, *batch)
+    net.backward_begin(0)
+    with pytest.raises(B200Error):
+        net.backward_ft(0, 0, 3)        # 3 does not divide 16 row blocks
+    with pytest.raises(B200Error):
+        net.backward_end(0)             # no part has run
+    net.close()
+
+
 def test_edge_batches(oracle32):
     """One position, ragged sizes, empty feature lists, duplicate features, invalid slots."""
     name, desc, game = NETS[4]
