@@ -11,7 +11,7 @@ GLOBAL batch of 131072 seeded synthetic positions per step, sharded evenly over 
 Prints ONE JSON line on rank 0.  `value` times the step with batches already resident in
 HBM; `e2e` times the public call sequence (upload from host arrays through pinned staging,
 step, loss read-back) with the next batch's packing and copy overlapped with the current
-step.  `roofline` covers the dominant feature-transformer kernel, `cpu_baseline` is the CPU
+step and each step's loss read while the next step runs.  `roofline` covers the dominant feature-transformer kernel, `cpu_baseline` is the CPU
 oracle on this box's host cores.  `--impl reference` times that CPU oracle alone.
 """
 from __future__ import annotations
@@ -284,10 +284,12 @@ def run_ours(args, rank, world, local_rank):
         last_loss = None
         for i in range(args.steps):
             slot = (first + i) % N_DISTINCT
-            one_step(slot)                                              # enqueue only
             nxt = (slot + 1) % N_DISTINCT
+            one_step(slot)                                              # enqueue only
             net.upload(nxt, *batches[nxt])                               # pack + H2D of the next batch
-            last_loss = net.loss()                                       # D2H read of this step's loss
+            if i:
+                last_loss = net.loss(steps_back=1)                       # D2H read of the previous step's loss
+        last_loss = net.loss()                                           # ... and of the last step's
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         h2d_per_step = (net.stat("h2d_bytes") - h2d0) // max(args.steps, 1)

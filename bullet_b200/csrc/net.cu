@@ -89,10 +89,12 @@ struct b200_net {
     float* dz[3] = {nullptr, nullptr, nullptr};
     int* status = nullptr;
     int *ft_lists = nullptr, *ft_list_count = nullptr;  // prepared per-pair row lists of the tiled kernels
+    // pinned read-back ring: loss and status word of the last kLossRing updates
+    static constexpr int kLossRing = 4;
     int* h_status = nullptr;
     float* h_loss = nullptr;
-    cudaEvent_t loss_ev = nullptr;
-    bool loss_pending = false;
+    cudaEvent_t loss_ev[kLossRing] = {};
+    int64_t updates = 0;
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
@@ -503,7 +505,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (cudaHostAlloc(&raw, 64, cudaHostAllocDefault) != cudaSuccess) return bail(b200::fail(B200_ERR_CUDA, "net_create: pinned alloc failed"));
     net->h_loss = static_cast<float*>(raw);
     net->h_status = reinterpret_cast<int*>(net->h_loss + 8);
-    cudaEventCreateWithFlags(&net->loss_ev, cudaEventDisableTiming);
+    for (auto& e : net->loss_ev) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
     for (auto& ring : net->tev)
         for (auto& e : ring) cudaEventCreate(&e);
 
@@ -536,7 +538,8 @@ int b200_net_destroy(b200_net* net) {
         if (s.consumed) cudaEventDestroy(s.consumed);
     }
     if (net->h_loss) cudaFreeHost(net->h_loss);
-    if (net->loss_ev) cudaEventDestroy(net->loss_ev);
+    for (auto& e : net->loss_ev)
+        if (e) cudaEventDestroy(e);
     for (auto& ring : net->tev)
         for (auto& e : ring)
             if (e) cudaEventDestroy(e);
@@ -852,10 +855,11 @@ int b200_update_end(b200_net* net) {
     if (!net) return b200::fail(B200_ERR_ARG, "update_end: null net");
     if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_end: no gradients yet");
     if (int rc = set_device(net)) return rc;
-    CK(cudaMemcpyAsync(net->h_loss, net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
-    CK(cudaMemcpyAsync(net->h_status, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
-    CK(cudaEventRecord(net->loss_ev, net->stream));
-    net->loss_pending = true;
+    const int ring = (int)(net->updates % b200_net::kLossRing);
+    CK(cudaMemcpyAsync(net->h_loss + ring, net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaMemcpyAsync(net->h_status + ring, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaEventRecord(net->loss_ev[ring], net->stream));
+    net->updates++;
     if (int rc = refresh_table(net)) return rc;
     if (net->step_open) {  // close the timed step begun by the matching backward
         CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][7], net->stream));
@@ -884,14 +888,17 @@ int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats) {
     return 0;
 }
 
-int b200_loss(b200_net* net, float* loss_sum) {
+int b200_loss_of(b200_net* net, int steps_back, float* loss_sum) {
     if (!net || !loss_sum) return b200::fail(B200_ERR_ARG, "loss: null argument");
-    if (!net->loss_pending) return b200::fail(B200_ERR_STATE, "loss: no update has run yet");
+    if (steps_back < 0 || steps_back >= b200_net::kLossRing - 1)
+        return b200::fail(B200_ERR_ARG, "loss: only the last %d updates are kept", b200_net::kLossRing - 1);
+    if (net->updates <= steps_back) return b200::fail(B200_ERR_STATE, "loss: that update has not run yet");
     if (int rc = set_device(net)) return rc;
-    CK(cudaEventSynchronize(net->loss_ev));
-    *loss_sum = *net->h_loss;
-    if (*net->h_status & b200::kStatusOutsideBlock) {
-        *net->h_status = 0;
+    const int ring = (int)((net->updates - 1 - steps_back) % b200_net::kLossRing);
+    CK(cudaEventSynchronize(net->loss_ev[ring]));
+    *loss_sum = net->h_loss[ring];
+    if (net->h_status[ring] & b200::kStatusOutsideBlock) {
+        net->h_status[ring] = 0;
         cudaMemsetAsync(net->status, 0, sizeof(int), net->stream);
         return b200::fail(B200_ERR_DATA,
                           "a feature index fell outside the row block of its position (ft_block_rows=%d): those "
@@ -900,6 +907,8 @@ int b200_loss(b200_net* net, float* loss_sum) {
     }
     return 0;
 }
+
+int b200_loss(b200_net* net, float* loss_sum) { return b200_loss_of(net, 0, loss_sum); }
 
 int b200_forward(b200_net* net, int slot, float* out_host) {
     if (int rc = check_slot(net, slot, "forward")) return rc;

@@ -114,9 +114,10 @@ class Net:
     def update_end(self) -> None:
         _lib.check(self.lib.b200_update_end(self._h))
 
-    def loss(self) -> float:
+    def loss(self, steps_back: int = 0) -> float:
+        """Summed loss of the most recent update (or of the one `steps_back` before it); waits for it."""
         v = ctypes.c_float()
-        _lib.check(self.lib.b200_loss(self._h, ctypes.byref(v)))
+        _lib.check(self.lib.b200_loss_of(self._h, steps_back, ctypes.byref(v)))
         return v.value
 
     def forward(self, slot: int, n: int) -> np.ndarray:

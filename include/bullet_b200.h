@@ -150,6 +150,10 @@ int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_
 int b200_update_end(b200_net* net);
 /* Summed loss of the most recent update/step (run.rs:212-221); waits for it. */
 int b200_loss(b200_net* net, float* loss_sum);
+/* The same for an earlier update: steps_back = 1 is the update before the most recent one (at
+ * most 2).  Reading step n-1's loss right after enqueuing step n keeps the GPU busy while the
+ * host waits, where b200_loss would drain it every step. */
+int b200_loss_of(b200_net* net, int steps_back, float* loss_sum);
 /* Forward only: network output per position (ModelEvaluator, crates/trainer/src/model/evaluator.rs:22-81). */
 int b200_forward(b200_net* net, int slot, float* out_host);
 int b200_sync(b200_net* net);
