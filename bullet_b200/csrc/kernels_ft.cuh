@@ -54,6 +54,13 @@ struct TileArgs {
     int* lists;       // [2n][list_len]
     int* list_count;  // [2n] padded length (multiple of 4)
     int list_len;     // nnz rounded up to a multiple of 4
+    // backward only: the visiting order cut into chunks of at most ft_bwd_chunk pairs that never
+    // straddle a block, and per chunk the row-major lists built by ft_csr_kernel
+    const int4* chunks;            // [nchunks] (block, first index into pair_order, pairs, 0)
+    const int* block_chunk_begin;  // [nblocks + 1] first chunk of every block
+    uint16_t* csr_ent;             // [nchunks][ent_cap] positions of the chunk grouped by row, lists padded to x4
+    int* csr_start;                // [nchunks][start_cap] start of every row's list; start[R] = total
+    int ent_cap, start_cap;
 };
 
 __device__ __forceinline__ float crelu_f(float v) { return fminf(fmaxf(v, 0.f), 1.f); }
@@ -242,6 +249,12 @@ __device__ __forceinline__ int tile_col_b(int slab, int lane, int H) {
     return PAIRWISE ? H / 2 + slab * 32 + lane : slab * 64 + 2 * lane + 1;
 }
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
 struct TileWork {
     int block, slab, begin, end;  // pair_order range [begin, end) served by this CTA
 };
@@ -375,76 +388,153 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
     }
 }
 
-// Backward.  Same grid.  Positions are taken in chunks of CP; per chunk the CTA
-//   1. builds in shared memory a row-major list (CSR) of which positions of the chunk hold
-//      each table row: a count pass, a scan and a fill pass over the chunk's prepared lists;
-//      every row's list is padded to a multiple of four entries that point at an all-zero line,
-//   2. stages the chunk's pre-activation gradients (from dx and the kept activations) as one
-//      64-float line per position, then
-//   3. every warp walks the lists of the rows it owns (row = warp, warp + #warps, ...), sums the
-//      staged lines in registers and adds the row's total to the table gradient with one
-//      global reduction per lane.
-// Shared-memory accumulators need no atomics, and the table gradient sees one reduction per
-// (row, chunk) instead of one per (row, position).  The table gradient must be zero on entry.
-// Two shapes: WIDE = one CTA of 1024 threads per SM with 512-position chunks, otherwise two
-// CTAs of 512 threads with 256-position chunks (chunks halve when nnz > 32).
-template <bool WIDE>
-struct BwdShape {
-    static constexpr int kThreads = WIDE ? 1024 : 512, kCtasPerSm = WIDE ? 1 : 2, kChunk = WIDE ? 512 : 256;
-};
-template <bool WIDE>
-__host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? BwdShape<WIDE>::kChunk : BwdShape<WIDE>::kChunk / 2; }
-template <bool WIDE>
+// Backward.  Positions are visited in chunks of at most CP pairs of one row block.
+//   ft_csr_kernel (one CTA per chunk, once per batch) turns the chunk's prepared lists around:
+//     for every table row of the block, the list of the chunk's pairs that hold it (a count
+//     pass, a scan and a fill pass in shared memory), every list padded to a multiple of four
+//     entries that point at an all-zero line.  All column slabs share the result.
+//   ft_backward_tiled_kernel (same grid as the forward) then, per chunk, copies that list
+//     structure into shared memory, stages the chunk's pre-activation gradients (from dx and
+//     the kept activations) as one 64-float line per pair, and every warp walks the lists of
+//     the rows it owns (row = warp, warp + 32, ...), sums the staged lines in registers and
+//     adds the row's total to the table gradient with one global reduction per lane.
+// Accumulation needs no atomics, and the table gradient sees one reduction per (row, chunk)
+// instead of one per (row, position).  The table gradient must be zero on entry.
+constexpr int kBwdThreads = 1024, kCsrThreads = 512;
+
+__host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? 512 : 256; }
+// entries per chunk: every slot of every pair plus up to three padding entries per row, rounded to 16 bytes
+__host__ __device__ inline int ft_bwd_ent_cap(int R, int nnz) { return (ft_bwd_chunk(nnz) * ((nnz + 3) & ~3) + 4 * R + 7) & ~7; }
+__host__ __device__ inline int ft_bwd_start_cap(int R) { return (R + 1 + 3) & ~3; }
 __host__ __device__ inline size_t ft_bwd_smem(int R, int nnz) {
-    const int cp = ft_bwd_chunk<WIDE>(nnz), len = (nnz + 3) & ~3;
-    return (size_t)(cp + 1) * kTileRowBytes + ((size_t)cp * len + 4 * (size_t)R) * 2 + (size_t)(2 * R + 4 + 32 + 2 * cp) * 4;
+    return (size_t)(ft_bwd_chunk(nnz) + 1) * kTileRowBytes + (size_t)ft_bwd_ent_cap(R, nnz) * 2 +
+           (size_t)ft_bwd_start_cap(R) * 4 + (size_t)ft_bwd_chunk(nnz) * 4;
+}
+__host__ __device__ inline size_t ft_csr_smem(int R, int nnz) {
+    return (size_t)ft_bwd_ent_cap(R, nnz) * 2 + (size_t)(2 * (R + 2) + 32 + ft_bwd_chunk(nnz)) * 4;
 }
 
-template <bool PAIRWISE, bool WIDE>
-__global__ void __launch_bounds__(BwdShape<WIDE>::kThreads, BwdShape<WIDE>::kCtasPerSm)
-    ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
+// grid = number of chunks, block = kCsrThreads.
+static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    constexpr int kBwdThreads = BwdShape<WIDE>::kThreads;
-    constexpr int NW = kBwdThreads / 32;
-    const TileWork w = tile_work(t);
-    const int R = t.block_rows, CP = ft_bwd_chunk<WIDE>(a.nnz), L = t.list_len;
-    f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                              // [CP + 1][32] (A, B) pairs
-    uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists
-    int* start = reinterpret_cast<int*>(ent + (size_t)CP * L + 4 * (size_t)R);    // [R + 1]
-    int* cursor = start + R + 2;                                                  // [R]
-    int* warp_tot = cursor + R + 2;                                               // [32]
-    int* pairs_s = warp_tot + 32;                                                 // [CP] pair ids of the chunk
-    int* count_s = pairs_s + CP;                                                  // [CP] prepared list lengths
-    const int col_a = tile_col_a<PAIRWISE>(w.slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, lane, a.H);
+    constexpr int NW = kCsrThreads / 32;
+    const int4 chunk = t.chunks[blockIdx.x];
+    const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz), L = t.list_len, c0 = chunk.y, cn = chunk.z;
+    uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw);
+    int* start = reinterpret_cast<int*>(ent + ft_bwd_ent_cap(R, a.nnz));  // [R + 1]
+    int* cursor = start + R + 2;                                         // [R]
+    int* warp_tot = cursor + R + 2;                                      // [32]
+    int* count_s = warp_tot + 32;                                        // [CP] prepared list lengths
     const int zero_row = R * kTileRowBytes;
+    for (int r = threadIdx.x; r < R; r += kCsrThreads) cursor[r] = 0;
+    for (int k = threadIdx.x; k < cn; k += kCsrThreads) count_s[k] = t.list_count[c0 + k];
+    __syncthreads();
+    // count how often each row occurs in the chunk: a warp per pair, a lane per list entry,
+    // four pairs in flight
+    const int* lists = t.lists + (size_t)c0 * L;
+    for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
+        for (int k0 = 0; k0 < L; k0 += 32) {
+            int o[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int pl = pl0 + k * NW;
+                o[k] = zero_row;
+                if (pl < cn && k0 + lane < count_s[pl]) o[k] = __ldg(lists + (size_t)pl * L + k0 + lane);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (o[k] != zero_row) atomicAdd(&cursor[o[k] / kTileRowBytes], 1);
+        }
+    __syncthreads();
+    // exclusive scan of the row counts, each rounded up to a multiple of four
+    {
+        int carry = 0;
+        for (int base = 0; base < R; base += kCsrThreads) {
+            const int r = base + threadIdx.x;
+            const int v = r < R ? (cursor[r] + 3) & ~3 : 0;
+            int incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
+            }
+            if (lane == 31) warp_tot[warp] = incl;
+            __syncthreads();
+            int before = carry, all = 0;
+            for (int k = 0; k < NW; k++) {
+                if (k < warp) before += warp_tot[k];
+                all += warp_tot[k];
+            }
+            if (r < R) {
+                start[r] = before + incl - v;
+                cursor[r] = before + incl - v;
+            }
+            carry += all;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) start[R] = carry;
+    }
+    __syncthreads();
+    // fill: entry = index of the pair within the chunk, grouped by row
+    for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
+        for (int k0 = 0; k0 < L; k0 += 32) {
+            int o[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int pl = pl0 + k * NW;
+                o[k] = zero_row;
+                if (pl < cn && k0 + lane < count_s[pl]) o[k] = __ldg(lists + (size_t)pl * L + k0 + lane);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (o[k] != zero_row) ent[atomicAdd(&cursor[o[k] / kTileRowBytes], 1)] = (uint16_t)(pl0 + k * NW);
+        }
+    __syncthreads();
+    // pad every list to its rounded length with the all-zero line (index CP)
+    for (int r = threadIdx.x; r < R; r += kCsrThreads)
+        for (int e = cursor[r]; e < start[r + 1]; e++) ent[e] = (uint16_t)CP;
+    __syncthreads();
+    // publish (8-byte and 16-byte copies; both arrays are sized in multiples of four)
+    const int total = start[R];
+    uint2* ent_out = reinterpret_cast<uint2*>(t.csr_ent + (size_t)blockIdx.x * t.ent_cap);
+    for (int i = threadIdx.x; i < total / 4; i += kCsrThreads) ent_out[i] = reinterpret_cast<const uint2*>(ent)[i];
+    int* start_out = t.csr_start + (size_t)blockIdx.x * t.start_cap;
+    for (int i = threadIdx.x; i <= R; i += kCsrThreads) start_out[i] = start[i];
+}
+
+// grid = nblocks * nslabs * nsplit CTAs of 1024 threads, one per SM.
+template <bool PAIRWISE>
+__global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int NW = kBwdThreads / 32;
+    const int split = blockIdx.x % t.nsplit, rest = blockIdx.x / t.nsplit;
+    const int slab = rest % t.nslabs, block = t.block0 + rest / t.nslabs;
+    const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz);
+    f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                                          // [CP + 1][32] (A, B) pairs
+    uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists of the chunk
+    int* start = reinterpret_cast<int*>(ent + t.ent_cap);                                     // [R + 1]
+    int* pairs_s = start + t.start_cap;                                                       // [CP] pair ids of the chunk
+    const int col_a = tile_col_a<PAIRWISE>(slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(slab, lane, a.H);
     float bsum_a = 0.f, bsum_b = 0.f;
     if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line
 
-    for (int c0 = w.begin; c0 < w.end; c0 += CP) {
-        const int cn = min(CP, w.end - c0);
-        for (int r = threadIdx.x; r < R; r += kBwdThreads) cursor[r] = 0;
-        for (int k = threadIdx.x; k < cn; k += kBwdThreads) {
-            pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
-            count_s[k] = t.list_count[c0 + k];
+    const int cb = t.block_chunk_begin[block], nc = t.block_chunk_begin[block + 1] - cb;
+    const int ch_begin = cb + (int)(((long long)nc * split) / t.nsplit), ch_end = cb + (int)(((long long)nc * (split + 1)) / t.nsplit);
+    for (int ch = ch_begin; ch < ch_end; ch++) {
+        const int4 chunk = t.chunks[ch];
+        const int c0 = chunk.y, cn = chunk.z;
+        // the chunk's row lists: asynchronous copy into shared memory, overlapped with the staging below
+        {
+            const int* start_in = t.csr_start + (size_t)ch * t.start_cap;
+            for (int i = threadIdx.x; i < t.start_cap / 4; i += kBwdThreads) cp_async16(start + 4 * i, start_in + 4 * i);
+            const int total = __ldg(start_in + R);
+            const uint16_t* ent_in = t.csr_ent + (size_t)ch * t.ent_cap;
+            for (int i = threadIdx.x; i < (total + 7) / 8; i += kBwdThreads) cp_async16(ent + 8 * i, ent_in + 8 * i);
         }
+        for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
         __syncthreads();
-        // count how often each row occurs in the chunk: a warp per position, a lane per list
-        // entry, four positions in flight
-        const int* lists = t.lists + (size_t)c0 * L;
-        for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
-            for (int k0 = 0; k0 < L; k0 += 32) {
-                int o[4];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const int pl = pl0 + k * NW;
-                    o[k] = zero_row;
-                    if (pl < cn && k0 + lane < count_s[pl]) o[k] = __ldg(lists + (size_t)pl * L + k0 + lane);
-                }
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    if (o[k] != zero_row) atomicAdd(&cursor[o[k] / kTileRowBytes], 1);
-            }
         // stage this chunk's gradients at the feature-transformer pre-activation
         for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
             float q0[4], q1[4], q2[4];
@@ -482,54 +572,7 @@ __global__ void __launch_bounds__(BwdShape<WIDE>::kThreads, BwdShape<WIDE>::kCta
                 }
             }
         }
-        __syncthreads();
-        // exclusive scan of the row counts, each rounded up to a multiple of four
-        {
-            int carry = 0;
-            for (int base = 0; base < R; base += kBwdThreads) {
-                const int r = base + threadIdx.x;
-                const int v = r < R ? (cursor[r] + 3) & ~3 : 0;
-                int incl = v;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int n = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += n;
-                }
-                if (lane == 31) warp_tot[warp] = incl;
-                __syncthreads();
-                int before = carry, all = 0;
-                for (int k = 0; k < NW; k++) {
-                    if (k < warp) before += warp_tot[k];
-                    all += warp_tot[k];
-                }
-                if (r < R) {
-                    start[r] = before + incl - v;
-                    cursor[r] = before + incl - v;
-                }
-                carry += all;
-                __syncthreads();
-            }
-            if (threadIdx.x == 0) start[R] = carry;
-        }
-        __syncthreads();
-        // fill: entry = position of the chunk, grouped by row
-        for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
-            for (int k0 = 0; k0 < L; k0 += 32) {
-                int o[4];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const int pl = pl0 + k * NW;
-                    o[k] = zero_row;
-                    if (pl < cn && k0 + lane < count_s[pl]) o[k] = __ldg(lists + (size_t)pl * L + k0 + lane);
-                }
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    if (o[k] != zero_row) ent[atomicAdd(&cursor[o[k] / kTileRowBytes], 1)] = (uint16_t)(pl0 + k * NW);
-            }
-        __syncthreads();
-        // pad every list to its rounded length with the all-zero line
-        for (int r = threadIdx.x; r < R; r += kBwdThreads)
-            for (int e = cursor[r]; e < start[r + 1]; e++) ent[e] = (uint16_t)CP;
+        cp_async_wait_all();
         __syncthreads();
         // accumulate: each warp walks the lists of the rows it owns
         const unsigned char* gl = smem_raw + lane * 8;
@@ -544,7 +587,7 @@ __global__ void __launch_bounds__(BwdShape<WIDE>::kThreads, BwdShape<WIDE>::kCta
                 const f32x2 v3 = *reinterpret_cast<const f32x2*>(gl + (q.y >> 16) * kTileRowBytes);
                 acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
             }
-            float* dst = a.g_table + (size_t)(w.block * R + row) * a.H;
+            float* dst = a.g_table + (size_t)(block * R + row) * a.H;
             const float ga = lo2(acc), gb = hi2(acc);
             if (PAIRWISE) {
                 if (ga != 0.f) atomicAdd(dst + col_a, ga);
@@ -555,7 +598,7 @@ __global__ void __launch_bounds__(BwdShape<WIDE>::kThreads, BwdShape<WIDE>::kCta
         }
         __syncthreads();
     }
-    // bias gradient: every position's gradient once, summed over the warps
+    // bias gradient: every pair's gradient once, summed over the warps
     float* red = reinterpret_cast<float*>(smem_raw);
     red[warp * kTileCols + lane] = bsum_a;
     red[warp * kTileCols + 32 + lane] = bsum_b;

@@ -63,8 +63,9 @@ struct Slot {
     size_t capacity = 0;
     int n = 0;
     int n_dtiles = 0;  // CTA tiles of the dense kernels held in off_dtiles
+    int n_chunks = 0;  // chunks of the tiled FT backward held in off_chunks
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
-           off_dtiles = 0, bytes = 0;
+           off_dtiles = 0, off_chunks = 0, off_bcb = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
     bool has_ready = false, has_consumed = false;
     template <class T>
@@ -89,6 +90,8 @@ struct b200_net {
     float* dz[3] = {nullptr, nullptr, nullptr};
     int* status = nullptr;
     int *ft_lists = nullptr, *ft_list_count = nullptr;  // prepared per-pair row lists of the tiled kernels
+    uint16_t* csr_ent = nullptr;                        // per-chunk row-major lists of the tiled backward
+    int* csr_start = nullptr;
     // pinned read-back ring: loss and status word of the last kLossRing updates
     static constexpr int kLossRing = 4;
     int* h_status = nullptr;
@@ -98,7 +101,6 @@ struct b200_net {
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
-    bool bwd_wide = true;  // shape of the tiled backward: one 1024-thread CTA per SM, or two of 512
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
     int last_n = 0;
@@ -182,6 +184,8 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.off_pairs = take((size_t)n * 8);
     s.off_blocks = take((size_t)(net->nblocks + 1) * 4);
     s.off_dtiles = take(((size_t)n / b200::kDenseTile + d.n_out_buckets + 1) * 8);
+    s.off_chunks = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz) + net->nblocks + 1) * 16);
+    s.off_bcb = take((size_t)(net->nblocks + 1) * 4);
     s.bytes = off;
 }
 
@@ -202,12 +206,8 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int blocks) {
     if (tiled) {
-        if (net->bwd_wide)
-            b200::ft_backward_tiled_kernel<PW, true><<<blocks * t.nslabs * t.nsplit, b200::BwdShape<true>::kThreads,
-                                                       b200::ft_bwd_smem<true>(t.block_rows, a.nnz), net->stream>>>(a, t);
-        else
-            b200::ft_backward_tiled_kernel<PW, false><<<blocks * t.nslabs * t.nsplit, b200::BwdShape<false>::kThreads,
-                                                        b200::ft_bwd_smem<false>(t.block_rows, a.nnz), net->stream>>>(a, t);
+        b200::ft_backward_tiled_kernel<PW><<<blocks * t.nslabs * t.nsplit, b200::kBwdThreads,
+                                             b200::ft_bwd_smem(t.block_rows, a.nnz), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -279,6 +279,12 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, int nsplit) {
     t.lists = net->ft_lists;
     t.list_count = net->ft_list_count;
     t.list_len = (net->d.nnz + 3) & ~3;
+    t.chunks = s.dev<int4>(s.off_chunks);
+    t.block_chunk_begin = s.dev<int>(s.off_bcb);
+    t.csr_ent = net->csr_ent;
+    t.csr_start = net->csr_start;
+    t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz);
+    t.start_cap = b200::ft_bwd_start_cap(net->d.ft_block_rows);
     return t;
 }
 
@@ -456,7 +462,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
                     b200::ft_fwd_smem(d.ft_block_rows) <= kMaxSmem &&
-                    b200::ft_bwd_smem<true>(d.ft_block_rows, d.nnz) <= kMaxSmem;
+                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz) <= kMaxSmem;
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
 
@@ -479,6 +485,9 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (net->tiled_ok) {
         rc = rc ? rc : dev_alloc(net, &net->ft_lists, 2 * B * ((d.nnz + 3) & ~3));
         rc = rc ? rc : dev_alloc(net, &net->ft_list_count, 2 * B);
+        const size_t max_chunks = 2 * B / b200::ft_bwd_chunk(d.nnz) + net->nblocks + 1;
+        rc = rc ? rc : dev_alloc(net, &net->csr_ent, max_chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz));
+        rc = rc ? rc : dev_alloc(net, &net->csr_start, max_chunks * b200::ft_bwd_start_cap(d.ft_block_rows));
     }
     if (rc) return bail(rc);
     if (!d.factoriser_rows) net->table = net->P + net->find("l0w")->off;
@@ -510,14 +519,13 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         for (auto& e : ring) cudaEventCreate(&e);
 
     if (net->tiled_ok) {
-        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem<true>(d.ft_block_rows, d.nnz);
-        const int bn = (int)b200::ft_bwd_smem<false>(d.ft_block_rows, d.nnz);
+        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_csr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)b200::ft_csr_smem(d.ft_block_rows, d.nnz));
     }
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaGetLastError());
@@ -559,10 +567,6 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
                               "about 800 rows per block, and ft_out a multiple of 64");
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
-        return 0;
-    }
-    if (!strcmp(key, "ft_bwd_wide")) {
-        net->bwd_wide = value != 0;
         return 0;
     }
     return b200::fail(B200_ERR_ARG, "set_option: unknown key '%s'", key);
@@ -709,6 +713,18 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         h_blocks[0] = 0;
         h_blocks[1] = 2 * n;
     }
+    {   // chunks of the tiled backward: runs of at most ft_bwd_chunk pairs that stay inside one block
+        int4* h_chunks = s.host<int4>(s.off_chunks);
+        int* h_bcb = s.host<int>(s.off_bcb);
+        const int cp = b200::ft_bwd_chunk(d.nnz);
+        int nc = 0;
+        for (int b = 0; b < nb; b++) {
+            h_bcb[b] = nc;
+            for (int at = h_blocks[b]; at < h_blocks[b + 1]; at += cp) h_chunks[nc++] = make_int4(b, at, std::min(cp, h_blocks[b + 1] - at), 0);
+        }
+        h_bcb[nb] = nc;
+        s.n_chunks = nc;
+    }
     CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
     net->h2d_bytes += (int64_t)s.bytes;
     CK(cudaEventRecord(s.ready, net->copy_stream));
@@ -731,6 +747,12 @@ int b200_backward_begin(b200_net* net, int slot) {
     if (int rc = forward_part(net, s, true)) return rc;
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[2], net->stream));
+    if (net->bwd_tiled() && s.n_chunks > 0) {  // row-major lists of every chunk, shared by all column slabs
+        b200::FtArgs fa = ft_args(net, s);
+        b200::TileArgs ta = tile_args(net, s, 1);
+        b200::ft_csr_kernel<<<s.n_chunks, b200::kCsrThreads, b200::ft_csr_smem(d.ft_block_rows, d.nnz), net->stream>>>(fa, ta);
+        LAUNCHED(net);
+    }
     {
         b200::DenseArgs da = dense_args(net, s, true);
         DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<s.n_dtiles, 256, 0, net->stream>>>(da, net->dx));
