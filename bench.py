@@ -221,6 +221,8 @@ def run_ours(args, rank, world, local_rank):
         net.set_option("ft_fwd_mode", args.ft_fwd_mode)
     if args.ft_bwd_mode:
         net.set_option("ft_bwd_mode", args.ft_bwd_mode)
+    if args.ft_bwd_wide is not None:
+        net.set_option("ft_bwd_wide", args.ft_bwd_wide)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
     parts = args.dp_parts if (world > 1 and net.stat("ft_tiled") & 2) else 1
     dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts)
@@ -362,6 +364,7 @@ def main():
     ap.add_argument("--ft-mode", type=int, default=0, help="0 auto, 1 gather kernels, 2 tiled kernels")
     ap.add_argument("--ft-fwd-mode", type=int, default=0)
     ap.add_argument("--ft-bwd-mode", type=int, default=0)
+    ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads, one CTA per SM")
     ap.add_argument("--dp-parts", type=int, default=4,
                     help="N > 1: slices of the l0w gradient all-reduced while the backward still runs (1 = one all-reduce)")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")

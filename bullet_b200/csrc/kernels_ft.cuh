@@ -50,8 +50,9 @@ struct TileArgs {
     const int* block_begin;  // [nblocks+1] offsets into pair_order
     int* status;
     // written by ft_prepare_kernel, read by the tiled kernels: for the i-th pair in visiting
-    // order its active rows as tile byte offsets, padded with the zero row to a multiple of four
-    int* lists;       // [2n][list_len]
+    // order its active rows (local to the pair's block), padded to a multiple of four with the
+    // index of the all-zero row (= block_rows)
+    uint16_t* lists;  // [2n][list_len]
     int* list_count;  // [2n] padded length (multiple of 4)
     int list_len;     // nnz rounded up to a multiple of 4
     // backward only: the visiting order cut into chunks of at most ft_bwd_chunk pairs that never
@@ -61,6 +62,7 @@ struct TileArgs {
     uint16_t* csr_ent;             // [nchunks][ent_cap] positions of the chunk grouped by row, lists padded to x4
     int* csr_start;                // [nchunks][start_cap] start of every row's list; start[R] = total
     int ent_cap, start_cap;
+    int chunk_len;  // CP: most pairs per chunk
 };
 
 __device__ __forceinline__ float crelu_f(float v) { return fminf(fmaxf(v, 0.f), 1.f); }
@@ -275,9 +277,8 @@ __device__ __forceinline__ const uint16_t* pair_list(const FtArgs& a, int pair) 
 }
 
 // Per batch, once: turns every (position, perspective) pair's slots into the list the tiled
-// kernels walk — rows local to the pair's block, as byte offsets into a tile (row * 256),
-// compacted in slot order and padded to a multiple of four with the offset of the all-zero
-// row.  A valid feature outside the block raises the status bit and is dropped.  One warp
+// kernels walk — rows local to the pair's block, compacted in slot order and padded to a
+// multiple of four with the index of the all-zero row.  A valid feature outside the block raises the status bit and is dropped.  One warp
 // per pair, in visiting order.  grid = ceil(2n / 8), block = 256.
 static __global__ void __launch_bounds__(256) ft_prepare_kernel(FtArgs a, TileArgs t) {
     const int lane = threadIdx.x & 31;
@@ -300,10 +301,10 @@ static __global__ void __launch_bounds__(256) ft_prepare_kernel(FtArgs a, TileAr
     const unsigned m0 = __ballot_sync(0xffffffffu, in0), m1 = __ballot_sync(0xffffffffu, in1);
     const unsigned lt = (1u << lane) - 1u;
     const int cnt0 = __popc(m0), cnt = cnt0 + __popc(m1), cnt4 = (cnt + 3) & ~3;
-    int* list = t.lists + (size_t)i * t.list_len;
-    if (in0) list[__popc(m0 & lt)] = row0 * kTileRowBytes;
-    if (in1) list[cnt0 + __popc(m1 & lt)] = row1 * kTileRowBytes;
-    if (lane < cnt4 - cnt) list[cnt + lane] = t.block_rows * kTileRowBytes;
+    uint16_t* list = t.lists + (size_t)i * t.list_len;
+    if (in0) list[__popc(m0 & lt)] = (uint16_t)row0;
+    if (in1) list[cnt0 + __popc(m1 & lt)] = (uint16_t)row1;
+    if (lane < cnt4 - cnt) list[cnt + lane] = (uint16_t)t.block_rows;
     if (lane == 0) t.list_count[i] = cnt4;
 }
 
@@ -362,14 +363,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
             pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
             cnt4_next = t.list_count[i + NW];
         }
-        const int4* list = reinterpret_cast<const int4*>(t.lists + (size_t)i * t.list_len);
+        const uint2* list = reinterpret_cast<const uint2*>(t.lists + (size_t)i * t.list_len);
         f32x2 acc = 0;  // (+0.0f, +0.0f)
         for (int k = 0; k < cnt4; k += 4) {
-            const int4 o = __ldg(list + (k >> 2));
-            const f32x2 v0 = *reinterpret_cast<const f32x2*>(mine + o.x);
-            const f32x2 v1 = *reinterpret_cast<const f32x2*>(mine + o.y);
-            const f32x2 v2 = *reinterpret_cast<const f32x2*>(mine + o.z);
-            const f32x2 v3 = *reinterpret_cast<const f32x2*>(mine + o.w);
+            const uint2 q = __ldg(list + (k >> 2));  // four row indices, the same for every lane
+            const f32x2 v0 = *reinterpret_cast<const f32x2*>(mine + (q.x & 0xffffu) * kTileRowBytes);
+            const f32x2 v1 = *reinterpret_cast<const f32x2*>(mine + (q.x >> 16) * kTileRowBytes);
+            const f32x2 v2 = *reinterpret_cast<const f32x2*>(mine + (q.y & 0xffffu) * kTileRowBytes);
+            const f32x2 v3 = *reinterpret_cast<const f32x2*>(mine + (q.y >> 16) * kTileRowBytes);
             acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
         }
         acc = add2(acc, bias);
@@ -400,18 +401,20 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
 //     adds the row's total to the table gradient with one global reduction per lane.
 // Accumulation needs no atomics, and the table gradient sees one reduction per (row, chunk)
 // instead of one per (row, position).  The table gradient must be zero on entry.
-constexpr int kBwdThreads = 1024, kCsrThreads = 512;
+constexpr int kCsrThreads = 512;
 
-__host__ __device__ inline int ft_bwd_chunk(int nnz) { return nnz <= 32 ? 512 : 256; }
+// Two shapes of the backward: "wide" = one CTA of 1024 threads per SM working on chunks of 512
+// pairs, otherwise two CTAs of 512 threads on chunks of 256, so that one CTA's global loads
+// overlap the other's shared-memory work.  Chunks halve when nnz > 32.
+__host__ __device__ inline int ft_bwd_chunk(int nnz, bool wide) { return (wide ? 512 : 256) / (nnz <= 32 ? 1 : 2); }
 // entries per chunk: every slot of every pair plus up to three padding entries per row, rounded to 16 bytes
-__host__ __device__ inline int ft_bwd_ent_cap(int R, int nnz) { return (ft_bwd_chunk(nnz) * ((nnz + 3) & ~3) + 4 * R + 7) & ~7; }
+__host__ __device__ inline int ft_bwd_ent_cap(int R, int nnz, int cp) { return (cp * ((nnz + 3) & ~3) + 4 * R + 7) & ~7; }
 __host__ __device__ inline int ft_bwd_start_cap(int R) { return (R + 1 + 3) & ~3; }
-__host__ __device__ inline size_t ft_bwd_smem(int R, int nnz) {
-    return (size_t)(ft_bwd_chunk(nnz) + 1) * kTileRowBytes + (size_t)ft_bwd_ent_cap(R, nnz) * 2 +
-           (size_t)ft_bwd_start_cap(R) * 4 + (size_t)ft_bwd_chunk(nnz) * 4;
+__host__ __device__ inline size_t ft_bwd_smem(int R, int nnz, int cp) {
+    return (size_t)(cp + 1) * kTileRowBytes + (size_t)ft_bwd_ent_cap(R, nnz, cp) * 2 + (size_t)ft_bwd_start_cap(R) * 4 + (size_t)cp * 4;
 }
-__host__ __device__ inline size_t ft_csr_smem(int R, int nnz) {
-    return (size_t)ft_bwd_ent_cap(R, nnz) * 2 + (size_t)(2 * (R + 2) + 32 + ft_bwd_chunk(nnz)) * 4;
+__host__ __device__ inline size_t ft_csr_smem(int R, int nnz, int cp) {
+    return (size_t)ft_bwd_ent_cap(R, nnz, cp) * 2 + (size_t)(2 * (R + 2) + 32 + cp) * 4;
 }
 
 // grid = number of chunks, block = kCsrThreads.
@@ -420,19 +423,19 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int NW = kCsrThreads / 32;
     const int4 chunk = t.chunks[blockIdx.x];
-    const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz), L = t.list_len, c0 = chunk.y, cn = chunk.z;
+    const int R = t.block_rows, CP = t.chunk_len, L = t.list_len, c0 = chunk.y, cn = chunk.z;
     uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw);
-    int* start = reinterpret_cast<int*>(ent + ft_bwd_ent_cap(R, a.nnz));  // [R + 1]
+    int* start = reinterpret_cast<int*>(ent + t.ent_cap);  // [R + 1]
     int* cursor = start + R + 2;                                         // [R]
     int* warp_tot = cursor + R + 2;                                      // [32]
     int* count_s = warp_tot + 32;                                        // [CP] prepared list lengths
-    const int zero_row = R * kTileRowBytes;
+    const int zero_row = R;
     for (int r = threadIdx.x; r < R; r += kCsrThreads) cursor[r] = 0;
     for (int k = threadIdx.x; k < cn; k += kCsrThreads) count_s[k] = t.list_count[c0 + k];
     __syncthreads();
     // count how often each row occurs in the chunk: a warp per pair, a lane per list entry,
     // four pairs in flight
-    const int* lists = t.lists + (size_t)c0 * L;
+    const uint16_t* lists = t.lists + (size_t)c0 * L;
     for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW)
         for (int k0 = 0; k0 < L; k0 += 32) {
             int o[4];
@@ -444,7 +447,7 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
             }
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                if (o[k] != zero_row) atomicAdd(&cursor[o[k] / kTileRowBytes], 1);
+                if (o[k] != zero_row) atomicAdd(&cursor[o[k]], 1);
         }
     __syncthreads();
     // exclusive scan of the row counts, each rounded up to a multiple of four
@@ -488,7 +491,7 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
             }
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                if (o[k] != zero_row) ent[atomicAdd(&cursor[o[k] / kTileRowBytes], 1)] = (uint16_t)(pl0 + k * NW);
+                if (o[k] != zero_row) ent[atomicAdd(&cursor[o[k]], 1)] = (uint16_t)(pl0 + k * NW);
         }
     __syncthreads();
     // pad every list to its rounded length with the all-zero line (index CP)
@@ -503,15 +506,16 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
     for (int i = threadIdx.x; i <= R; i += kCsrThreads) start_out[i] = start[i];
 }
 
-// grid = nblocks * nslabs * nsplit CTAs of 1024 threads, one per SM.
-template <bool PAIRWISE>
-__global__ void __launch_bounds__(kBwdThreads, 1) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
+// grid = nblocks * nslabs * nsplit CTAs of THREADS threads (1024: one per SM; 512: two per SM).
+template <bool PAIRWISE, int THREADS>
+__global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kBwdThreads = THREADS;
     constexpr int NW = kBwdThreads / 32;
     const int split = blockIdx.x % t.nsplit, rest = blockIdx.x / t.nsplit;
     const int slab = rest % t.nslabs, block = t.block0 + rest / t.nslabs;
-    const int R = t.block_rows, CP = ft_bwd_chunk(a.nnz);
+    const int R = t.block_rows, CP = t.chunk_len;
     f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                                          // [CP + 1][32] (A, B) pairs
     uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists of the chunk
     int* start = reinterpret_cast<int*>(ent + t.ent_cap);                                     // [R + 1]

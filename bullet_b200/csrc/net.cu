@@ -63,7 +63,7 @@ struct Slot {
     size_t capacity = 0;
     int n = 0;
     int n_dtiles = 0;  // CTA tiles of the dense kernels held in off_dtiles
-    int n_chunks = 0;  // chunks of the tiled FT backward held in off_chunks
+    int n_chunks = 0, chunk_len = 0;  // chunks of the tiled FT backward held in off_chunks, and their size
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
            off_dtiles = 0, off_chunks = 0, off_bcb = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
@@ -89,7 +89,8 @@ struct b200_net {
     float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr, *w1g = nullptr;
     float* dz[3] = {nullptr, nullptr, nullptr};
     int* status = nullptr;
-    int *ft_lists = nullptr, *ft_list_count = nullptr;  // prepared per-pair row lists of the tiled kernels
+    uint16_t* ft_lists = nullptr;  // prepared per-pair row lists of the tiled kernels
+    int* ft_list_count = nullptr;
     uint16_t* csr_ent = nullptr;                        // per-chunk row-major lists of the tiled backward
     int* csr_start = nullptr;
     // pinned read-back ring: loss and status word of the last kLossRing updates
@@ -100,6 +101,8 @@ struct b200_net {
     int64_t updates = 0;
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
+    bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
+    int bwd_chunk() const { return b200::ft_bwd_chunk(d.nnz, bwd_wide); }
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
@@ -184,7 +187,7 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.off_pairs = take((size_t)n * 8);
     s.off_blocks = take((size_t)(net->nblocks + 1) * 4);
     s.off_dtiles = take(((size_t)n / b200::kDenseTile + d.n_out_buckets + 1) * 8);
-    s.off_chunks = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz) + net->nblocks + 1) * 16);
+    s.off_chunks = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
     s.off_bcb = take((size_t)(net->nblocks + 1) * 4);
     s.bytes = off;
 }
@@ -206,8 +209,11 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int blocks) {
     if (tiled) {
-        b200::ft_backward_tiled_kernel<PW><<<blocks * t.nslabs * t.nsplit, b200::kBwdThreads,
-                                             b200::ft_bwd_smem(t.block_rows, a.nnz), net->stream>>>(a, t);
+        const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len);
+        if (t.chunk_len == b200::ft_bwd_chunk(a.nnz, true))
+            b200::ft_backward_tiled_kernel<PW, 1024><<<blocks * t.nslabs * t.nsplit, 1024, smem, net->stream>>>(a, t);
+        else
+            b200::ft_backward_tiled_kernel<PW, 512><<<blocks * t.nslabs * t.nsplit, 512, smem, net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -283,7 +289,8 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, int nsplit) {
     t.block_chunk_begin = s.dev<int>(s.off_bcb);
     t.csr_ent = net->csr_ent;
     t.csr_start = net->csr_start;
-    t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz);
+    t.chunk_len = s.chunk_len;
+    t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz, s.chunk_len);
     t.start_cap = b200::ft_bwd_start_cap(net->d.ft_block_rows);
     return t;
 }
@@ -462,7 +469,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
                     b200::ft_fwd_smem(d.ft_block_rows) <= kMaxSmem &&
-                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz) <= kMaxSmem;
+                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz, b200::ft_bwd_chunk(d.nnz, true)) <= kMaxSmem;
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
 
@@ -485,8 +492,15 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (net->tiled_ok) {
         rc = rc ? rc : dev_alloc(net, &net->ft_lists, 2 * B * ((d.nnz + 3) & ~3));
         rc = rc ? rc : dev_alloc(net, &net->ft_list_count, 2 * B);
-        const size_t max_chunks = 2 * B / b200::ft_bwd_chunk(d.nnz) + net->nblocks + 1;
-        rc = rc ? rc : dev_alloc(net, &net->csr_ent, max_chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz));
+        // sized for whichever backward shape needs more: every block may end in a partly filled chunk
+        size_t ent_total = 0, max_chunks = 0;
+        for (int wide = 0; wide < 2; wide++) {
+            const int cp = b200::ft_bwd_chunk(d.nnz, wide != 0);
+            const size_t chunks = 2 * B / cp + net->nblocks + 1;
+            max_chunks = std::max(max_chunks, chunks);
+            ent_total = std::max(ent_total, chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz, cp));
+        }
+        rc = rc ? rc : dev_alloc(net, &net->csr_ent, ent_total);
         rc = rc ? rc : dev_alloc(net, &net->csr_start, max_chunks * b200::ft_bwd_start_cap(d.ft_block_rows));
     }
     if (rc) return bail(rc);
@@ -519,13 +533,17 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         for (auto& e : ring) cudaEventCreate(&e);
 
     if (net->tiled_ok) {
-        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows), bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz);
+        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows);
+        const int wide = b200::ft_bwd_chunk(d.nnz, true), narrow = b200::ft_bwd_chunk(d.nnz, false);
+        const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
         cudaFuncSetAttribute(b200::ft_csr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)b200::ft_csr_smem(d.ft_block_rows, d.nnz));
+                             (int)b200::ft_csr_smem(d.ft_block_rows, d.nnz, wide));
     }
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaGetLastError());
@@ -567,6 +585,10 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
                               "about 800 rows per block, and ft_out a multiple of 64");
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "ft_bwd_wide")) {  // takes effect for batches uploaded afterwards
+        net->bwd_wide = value != 0;
         return 0;
     }
     return b200::fail(B200_ERR_ARG, "set_option: unknown key '%s'", key);
@@ -716,7 +738,8 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
     {   // chunks of the tiled backward: runs of at most ft_bwd_chunk pairs that stay inside one block
         int4* h_chunks = s.host<int4>(s.off_chunks);
         int* h_bcb = s.host<int>(s.off_bcb);
-        const int cp = b200::ft_bwd_chunk(d.nnz);
+        const int cp = net->bwd_chunk();
+        s.chunk_len = cp;
         int nc = 0;
         for (int b = 0; b < nb; b++) {
             h_bcb[b] = nc;
@@ -750,7 +773,7 @@ int b200_backward_begin(b200_net* net, int slot) {
     if (net->bwd_tiled() && s.n_chunks > 0) {  // row-major lists of every chunk, shared by all column slabs
         b200::FtArgs fa = ft_args(net, s);
         b200::TileArgs ta = tile_args(net, s, 1);
-        b200::ft_csr_kernel<<<s.n_chunks, b200::kCsrThreads, b200::ft_csr_smem(d.ft_block_rows, d.nnz), net->stream>>>(fa, ta);
+        b200::ft_csr_kernel<<<s.n_chunks, b200::kCsrThreads, b200::ft_csr_smem(d.ft_block_rows, d.nnz, s.chunk_len), net->stream>>>(fa, ta);
         LAUNCHED(net);
     }
     {

@@ -153,7 +153,7 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     t.pair_order = order;
     t.block_begin = begin;
     t.status = status;
-    t.lists = lists;
+    t.lists = reinterpret_cast<uint16_t*>(lists);
     t.list_count = counts_per_pair;
     t.list_len = list_len(op->nnz);
     b200::ft_prepare_kernel<<<(2 * n + 7) / 8, 256, 0, stream>>>(a, t);
