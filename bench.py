@@ -39,6 +39,14 @@ METRIC = "train positions/sec (fwd+bwd+AdamW)"
 UNIT = "positions/s"
 GLOBAL_BATCH = 131072  # --global-batch overrides it for profiling runs on a smaller case
 WORKLOAD = "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), global batch {}"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two feature-transformer kernels, by
+# positions per GPU.  16384 is measured (ncu, profiles/step_kernels_c3_16384.txt); the larger sizes are
+# scaled from it: per-position terms linearly, the one table-sized term (100.7 MB read in the forward,
+# 63 MB of gradient write-back in the backward) kept fixed.
+FT_DRAM_BYTES = {
+    "ft_forward": {16384: 447804416, 32768: 794945536, 65536: 1489227776, 131072: 2877792256},
+    "ft_backward": {16384: 556155136, 32768: 1049104640, 65536: 2035003648, 131072: 4006801664},
+}
 N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)
 
 
@@ -307,12 +315,7 @@ def run_ours(args, rank, world, local_rank):
         k["achieved_gbs"] = k["algorithmic_bytes"] / (k["ms"] * 1e-3) / 1e9 if k["ms"] > 0 else None
         k["frac_of_hbm_peak"] = k["achieved_gbs"] / peak if k["achieved_gbs"] else None
     dom = max(kernels, key=lambda n: kernels[n]["ms"])
-    traffic = None
-    try:  # per-launch DRAM bytes of the dominant kernel from the committed ncu summary, if present
-        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
-            traffic = json.load(f).get(dom, {}).get(f"n{n_local}")
-    except Exception:
-        pass
+    traffic = FT_DRAM_BYTES.get(dom, {}).get(n_local)
     roofline = {
         "bound": "hbm", "kernel": dom, "achieved": kernels[dom]["achieved_gbs"], "peak": peak, "unit": "GB/s",
         "frac": kernels[dom]["frac_of_hbm_peak"], "traffic": traffic, "peak_kind": f"of {peak_kind}",
