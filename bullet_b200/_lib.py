@@ -18,7 +18,7 @@ SYMBOLS = (
     "b200_map_chess_buckets_mirrored", "b200_map_ataxx147", "b200_material_count", "b200_make_targets",
     "b200_pack_indices_u16", "b200_unpack_indices_u16", "b200_net_get_stat", "b200_op_ft_forward", "b200_op_ft_forward_noalloc",
     "b200_backward_begin", "b200_backward_ft", "b200_backward_end", "b200_grad_part", "b200_update_range",
-    "b200_update_end", "b200_loss_of",
+    "b200_update_end", "b200_loss_of", "b200_checkpoint_save", "b200_checkpoint_load",
 )
 
 
@@ -86,6 +86,8 @@ def load() -> ctypes.CDLL:
         "b200_loss_of": [vp, ctypes.c_int, ctypes.POINTER(f32)],
         "b200_forward": [vp, ctypes.c_int, vp],
         "b200_sync": [vp],
+        "b200_checkpoint_save": [vp, cp],
+        "b200_checkpoint_load": [vp, cp],
         "b200_get_timings": [vp, ctypes.POINTER(CTimings)],
         "b200_net_get_activation": [vp, ctypes.c_int, vp, i64],
         "b200_net_get_stat": [vp, cp, ctypes.POINTER(i64)],

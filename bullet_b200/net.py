@@ -125,6 +125,13 @@ class Net:
         _lib.check(self.lib.b200_forward(self._h, slot, _p(out)))
         return out
 
+    def save_checkpoint(self, directory: str) -> None:
+        """weights.bin / momentum.bin / velocity.bin in the reference's record format."""
+        _lib.check(self.lib.b200_checkpoint_save(self._h, directory.encode()))
+
+    def load_checkpoint(self, directory: str) -> None:
+        _lib.check(self.lib.b200_checkpoint_load(self._h, directory.encode()))
+
     def sync(self) -> None:
         _lib.check(self.lib.b200_sync(self._h))
 

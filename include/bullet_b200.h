@@ -170,6 +170,14 @@ int b200_net_get_stat(b200_net* net, const char* key, int64_t* value);
  *        2 = gradient at x [n][D1], 3 = network outputs [n]. */
 int b200_net_get_activation(b200_net* net, int which, float* host, int64_t n);
 
+/* ---- checkpoints in the reference's on-disk format: `dir`/weights.bin, momentum.bin and
+ * velocity.bin, each a sequence of records (ASCII id, '\n', u64 LE count, f32 LE values) in name
+ * order, as Optimiser::write_to_checkpoint / load_from_checkpoint read and write them
+ * (crates/trainer/src/optimiser.rs:218-236, crates/trainer/src/model/weights.rs:404-467).
+ * The directory must exist; in the reference it is `<checkpoint>/optimiser_state`. */
+int b200_checkpoint_save(b200_net* net, const char* dir);
+int b200_checkpoint_load(b200_net* net, const char* dir);
+
 /* ---- operator level: the feature-transformer forward on caller-owned DEVICE memory, without a
  * b200_net.  For both perspectives of n positions: the sparse affine of SparseMatmul::evaluate
  * (crates/compiler/src/tensor/operation/linear/sparse.rs:86-119), the bias

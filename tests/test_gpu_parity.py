@@ -238,6 +238,53 @@ def test_phased_step_equals_one_piece_step(oracle32):
     net.close()
 
 
+def test_checkpoint_round_trip_in_reference_format(oracle32, tmp_path):
+    """save -> files in the reference's record layout -> load into a fresh net -> identical training."""
+    import struct
+
+    name, desc, game = NETS[4]
+    B = 300
+    desc = dataclasses.replace(desc, max_batch=B)
+    batch = oracle32.map_batch(game, synth.records(game, B, seed=26), desc)
+    net = make_net(desc, 0, rich_weights(desc))
+    net.upload(0, *batch)
+    net.step(0, 1e-3, 1.0 / B)
+    net.loss()
+    net.save_checkpoint(str(tmp_path))
+    # parse weights.bin by hand: id, newline, u64 LE count, f32 LE values, tensors in name order
+    raw = (tmp_path / "weights.bin").read_bytes()
+    at, ids = 0, []
+    while at < len(raw):
+        end = raw.index(b"\n", at)
+        tid = raw[at:end].decode("ascii")
+        (count,) = struct.unpack_from("<Q", raw, end + 1)
+        vals = np.frombuffer(raw, dtype="<f4", count=count, offset=end + 9)
+        assert np.array_equal(vals, net.get_tensor(tid))
+        ids.append(tid)
+        at = end + 9 + 4 * count
+    assert ids == sorted(desc.tensor_shapes()) and at == len(raw)
+    for fname, kind in (("momentum.bin", 1), ("velocity.bin", 2)):
+        assert (tmp_path / fname).stat().st_size == len(raw)
+    twin = make_net(desc, 0, synth.init_weights(desc, seed=99))
+    twin.load_checkpoint(str(tmp_path))
+    for kind in (0, 1, 2):
+        a, b = net.tensors(kind), twin.tensors(kind)
+        assert all(np.array_equal(a[k], b[k]) for k in a)
+    for n in (net, twin):
+        n.upload(1, *batch)
+        n.step(1, 1e-3, 1.0 / B)
+    assert abs(net.loss() - twin.loss()) <= 1e-6 * abs(net.loss())
+    # a file from a different network is refused
+    from bullet_b200._lib import B200Error
+
+    other = make_net(dataclasses.replace(NETS[1][1], max_batch=8))
+    with pytest.raises(B200Error) as e:
+        other.load_checkpoint(str(tmp_path))
+    assert e.value.code == -4
+    for n in (net, twin, other):
+        n.close()
+
+
 def test_edge_batches(oracle32):
     """One position, ragged sizes, empty feature lists, duplicate features, invalid slots."""
     name, desc, game = NETS[4]

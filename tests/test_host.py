@@ -13,6 +13,16 @@ from bullet_b200.net import featurise, pack_indices, unpack_indices
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def test_rust_declarations_cover_the_header():
+    header = open(os.path.join(ROOT, "include", "bullet_b200.h")).read()
+    rust = open(os.path.join(ROOT, "bindings", "rust", "b200-sys", "src", "lib.rs")).read()
+    declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
+    bound = set(re.findall(r"pub fn (b200_[a-z0-9_]+)\s*\(", rust))
+    assert declared == bound
+    for struct in ("b200_net_desc", "b200_adamw_params", "b200_timings", "b200_ft_op"):
+        assert f"pub struct {struct}" in rust
+
+
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "bullet_b200.h")).read()
     declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
