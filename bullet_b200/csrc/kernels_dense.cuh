@@ -365,63 +365,51 @@ __global__ void __launch_bounds__(256) dense_wgrad_kernel(WgradArgs a) {
     flush();
 }
 
-// The same gradients for the narrow layers after the first (K <= 64 inputs): too few columns
-// to give every thread one, so a thread owns up to kSmallOutputs (row, column) entries of
-// the current bucket's gradient block instead.  grid = chunks, block = 256.
-constexpr int kSmallOutputs = 9;  // ceil(32 * 65 / 256)
+// Weight and bias gradients of the narrow layers after the first, all in one launch: one CTA
+// per tile of up to 32 positions of one output bucket (the tiles of the forward).  For layer
+// l >= 1 with input X = the activated output of layer l-1 (K values per position) and dY = the
+// gradient at its selected pre-activation (M values): a thread owns entries (row r, column c)
+// of the bucket's M x (K+1) block (column K is the bias), sums dY[p][r] * X[p][c] over the
+// tile's positions from shared memory and adds the result with one atomic per entry.
+// grid = ntiles, block = 256.
+struct SmallGradArgs {
+    const int* order;
+    const int2* tiles;
+    const int* buckets;
+    int O, n_layers;     // layers handled here: dense layers 1 .. n_dense-1
+    int K[2], M[2];
+    const float* X[2];   // [n][K]
+    const float* dY[2];  // [n][M]
+    float* gW[2];
+    float* gB[2];
+};
 
-__global__ void __launch_bounds__(256) dense_wgrad_small_kernel(WgradArgs a, int M) {
-    constexpr int S = 32;
-    __shared__ int s_bucket[S];
-    __shared__ float s_x[S][65], s_dy[S][32];
-    const int K = a.K, OM = a.O * M, outputs = M * (K + 1);
-    const int begin = blockIdx.x * a.chunk_len, end = min(a.n, begin + a.chunk_len);
-    float acc[kSmallOutputs];
-    int row[kSmallOutputs], col[kSmallOutputs];
-#pragma unroll
-    for (int q = 0; q < kSmallOutputs; q++) {
-        const int o = threadIdx.x + 256 * q;
-        acc[q] = 0.f;
-        row[q] = o % M;
-        col[q] = o < outputs ? o / M : -1;
-    }
-    int cur = -1;
-    auto flush = [&]() {
-        if (cur < 0) return;
-#pragma unroll
-        for (int q = 0; q < kSmallOutputs; q++) {
-            if (col[q] >= 0 && acc[q] != 0.f)
-                atomicAdd(col[q] < K ? a.gW + (size_t)col[q] * OM + cur * M + row[q] : a.gB + cur * M + row[q], acc[q]);
-            acc[q] = 0.f;
-        }
-    };
-    for (int base = begin; base < end; base += S) {
-        const int cnt = min(S, end - base);
+static __global__ void __launch_bounds__(256) dense_small_grads_kernel(SmallGradArgs a) {
+    __shared__ float s_x[32][33], s_dy[32][33];
+    __shared__ int s_pos[32];
+    const int2 t = a.tiles[blockIdx.x];
+    if (threadIdx.x < t.y) s_pos[threadIdx.x] = a.order[t.x + threadIdx.x];
+    __syncthreads();
+    const int k = a.buckets[s_pos[0]];
+    for (int l = 0; l < a.n_layers; l++) {
+        const int K = a.K[l], M = a.M[l], OM = a.O * M;
         __syncthreads();
-        for (int i = threadIdx.x; i < cnt * (K + 1); i += blockDim.x) {
-            const int j = i / (K + 1), c = i % (K + 1);
-            const int pos = a.order ? a.order[base + j] : base + j;
-            s_x[j][c] = c < K ? a.X[(size_t)pos * K + c] : 1.f;
-            if (c == 0) s_bucket[j] = a.buckets[pos];
+        for (int i = threadIdx.x; i < t.y * (K + 1); i += blockDim.x) {
+            const int p = i / (K + 1), c = i % (K + 1);
+            s_x[p][c] = c < K ? a.X[l][(size_t)s_pos[p] * K + c] : 1.f;
         }
-        for (int i = threadIdx.x; i < cnt * M; i += blockDim.x) {
-            const int j = i / M, r = i % M;
-            const int pos = a.order ? a.order[base + j] : base + j;
-            s_dy[j][r] = a.dY[(size_t)pos * M + r];
+        for (int i = threadIdx.x; i < t.y * M; i += blockDim.x) {
+            const int p = i / M, r = i % M;
+            s_dy[p][r] = a.dY[l][(size_t)s_pos[p] * M + r];
         }
         __syncthreads();
-        for (int j = 0; j < cnt; j++) {
-            const int k = s_bucket[j];
-            if (k != cur) {
-                flush();
-                cur = k;
-            }
-#pragma unroll
-            for (int q = 0; q < kSmallOutputs; q++)
-                if (col[q] >= 0) acc[q] += s_dy[j][row[q]] * s_x[j][col[q]];
+        for (int o = threadIdx.x; o < M * (K + 1); o += blockDim.x) {
+            const int r = o % M, c = o / M;
+            float sum = 0.f;
+            for (int p = 0; p < t.y; p++) sum += s_dy[p][r] * s_x[p][c];
+            if (sum != 0.f) atomicAdd(c < K ? a.gW[l] + (size_t)c * OM + k * M + r : a.gB[l] + k * M + r, sum);
         }
     }
-    flush();
 }
 
 }  // namespace b200

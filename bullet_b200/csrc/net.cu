@@ -390,13 +390,6 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
     w.gW = net->G + net->find(name)->off;
     snprintf(name, sizeof name, "l%db", layer + 1);
     w.gB = net->G + net->find(name)->off;
-    if (layer > 0) {  // narrow layers: one CTA per chunk of positions, threads over (row, column)
-        const int chunks = std::max(1, std::min((s.n + 63) / 64, 2 * kSmCount));
-        w.chunk_len = ((s.n + chunks - 1) / chunks + 31) / 32 * 32;
-        b200::dense_wgrad_small_kernel<<<(s.n + w.chunk_len - 1) / w.chunk_len, 256, 0, net->stream>>>(w, d.dense_out[layer]);
-        LAUNCHED(net);
-        return 0;
-    }
     const int threads = w.K + 1 >= 256 ? 256 : ((w.K + 1 + 31) / 32) * 32;
     const int gx = (w.K + 1 + threads - 1) / threads;
     int chunks = std::max(1, std::min((s.n + 63) / 64, kTargetCtas / gx));
@@ -834,8 +827,29 @@ int b200_backward_end(b200_net* net, int slot) {
         return b200::fail(B200_ERR_STATE, "backward_end: run b200_backward_begin and every b200_backward_ft part first");
     if (int rc = set_device(net)) return rc;
     Slot& s = net->slots[slot];
-    for (int l = net->d.n_dense - 1; l >= 0; l--)
-        if (int rc = launch_wgrad(net, s, l)) return rc;
+    if (net->d.n_dense > 1) {  // the narrow layers' weight and bias gradients, one launch
+        const b200_net_desc& d = net->d;
+        b200::SmallGradArgs g{};
+        g.order = s.dev<int>(s.off_order);
+        g.tiles = s.dev<int2>(s.off_dtiles);
+        g.buckets = s.dev<int>(s.off_buckets);
+        g.O = d.n_out_buckets;
+        g.n_layers = d.n_dense - 1;
+        for (int l = 1; l < d.n_dense; l++) {
+            char name[8];
+            g.K[l - 1] = d.dense_out[l - 1];
+            g.M[l - 1] = d.dense_out[l];
+            g.X[l - 1] = l == 1 ? net->a1 : net->a2;
+            g.dY[l - 1] = net->dz[l];
+            snprintf(name, sizeof name, "l%dw", l + 1);
+            g.gW[l - 1] = net->G + net->find(name)->off;
+            snprintf(name, sizeof name, "l%db", l + 1);
+            g.gB[l - 1] = net->G + net->find(name)->off;
+        }
+        b200::dense_small_grads_kernel<<<s.n_dtiles, 256, 0, net->stream>>>(g);
+        LAUNCHED(net);
+    }
+    if (int rc = launch_wgrad(net, s, 0)) return rc;
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[6], net->stream));
     CK(cudaEventRecord(s.consumed, net->stream));
