@@ -295,7 +295,8 @@ __global__ void __launch_bounds__(256, (M1 > 16 ? 1 : 2)) dense_dx_kernel(DenseA
 // reduce over the batch for the bias: model/builder.rs:263-267).
 // Positions are visited in bucket-sorted order (`order`), so a thread keeps M running sums
 // for the current bucket and flushes them with atomics only when the bucket changes.
-// Thread c < K owns column c; thread c == K owns the bias.  grid = (ceil((K+1)/T), chunks).
+// A thread owns four neighbouring columns (one 16-byte load of x per position); the thread
+// after the last column owns the bias.  grid = (ceil((K/4 + 1) / 128), chunks), block = 128.
 struct WgradArgs {
     const float* X;      // [n][K]
     const float* dY;     // [n][M]
@@ -307,25 +308,38 @@ struct WgradArgs {
 };
 
 template <int M>
-__global__ void __launch_bounds__(256) dense_wgrad_kernel(WgradArgs a) {
+__global__ void __launch_bounds__(128) dense_wgrad_kernel(WgradArgs a) {
     constexpr int S = 64;  // positions staged per round
     __shared__ int s_pos[S], s_bucket[S];
-    __shared__ float s_dy[S][M];
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const bool is_col = c < a.K, is_bias = c == a.K;
+    __shared__ __align__(16) float s_dy[S][M];
+    const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);  // this thread's four columns c .. c+3
+    const bool is_col = c < a.K, is_bias = c == a.K;             // K is a multiple of four
     const int OM = a.O * M;
     const int begin = blockIdx.y * a.chunk_len, end = min(a.n, begin + a.chunk_len);
-    float acc[M];
+    float acc[4][M];
 #pragma unroll
-    for (int r = 0; r < M; r++) acc[r] = 0.f;
+    for (int q = 0; q < 4; q++)
+#pragma unroll
+        for (int r = 0; r < M; r++) acc[q][r] = 0.f;
     int cur = -1;
-    auto flush = [&]() {
+    auto flush = [&]() {  // one column's M rows are contiguous: 128-bit reductions when M allows
         if (cur >= 0 && (is_col || is_bias)) {
-            float* dst = is_col ? a.gW + (size_t)c * OM + cur * M : a.gB + cur * M;
 #pragma unroll
-            for (int r = 0; r < M; r++) {
-                if (acc[r] != 0.f) atomicAdd(dst + r, acc[r]);
-                acc[r] = 0.f;
+            for (int q = 0; q < 4; q++) {
+                float* dst = is_col ? a.gW + (size_t)(c + q) * OM + cur * M : a.gB + cur * M;
+                if (is_col || q == 0) {
+                    if (M % 4 == 0) {
+#pragma unroll
+                        for (int r = 0; r < M; r += 4)
+                            atomicAdd(reinterpret_cast<float4*>(dst + r), make_float4(acc[q][r], acc[q][r + 1], acc[q][r + 2], acc[q][r + 3]));
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < M; r++)
+                            if (acc[q][r] != 0.f) atomicAdd(dst + r, acc[q][r]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < M; r++) acc[q][r] = 0.f;
             }
         }
     };
@@ -340,12 +354,13 @@ __global__ void __launch_bounds__(256) dense_wgrad_kernel(WgradArgs a) {
         __syncthreads();
         for (int i = threadIdx.x; i < cnt * M; i += blockDim.x) s_dy[i / M][i % M] = a.dY[(size_t)s_pos[i / M] * M + i % M];
         __syncthreads();
-        for (int j0 = 0; j0 < cnt; j0 += 4) {
-            float xv[4];
+        for (int j0 = 0; j0 < cnt; j0 += 4) {  // four positions' loads in flight per thread
+            float4 xv[4];
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const int j = j0 + u;
-                xv[u] = j < cnt ? (is_col ? a.X[(size_t)s_pos[j] * a.K + c] : 1.f) : 0.f;
+                xv[u] = make_float4(is_bias ? 1.f : 0.f, 0.f, 0.f, 0.f);  // the bias "column" sees x = 1
+                if (j < cnt && is_col) xv[u] = __ldg(reinterpret_cast<const float4*>(a.X + (size_t)s_pos[j] * a.K + c));
             }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
@@ -356,8 +371,13 @@ __global__ void __launch_bounds__(256) dense_wgrad_kernel(WgradArgs a) {
                         flush();
                         cur = k;
                     }
+                    const float xs[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
 #pragma unroll
-                    for (int r = 0; r < M; r++) acc[r] += s_dy[j][r] * xv[u];
+                    for (int r = 0; r < M; r++) {
+                        const float dy = s_dy[j][r];
+#pragma unroll
+                        for (int q = 0; q < 4; q++) acc[q][r] += dy * xs[q];
+                    }
                 }
             }
         }

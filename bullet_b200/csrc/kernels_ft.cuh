@@ -30,8 +30,10 @@ constexpr uint32_t kNoFeature = 0xFFFFu;
 constexpr int kStatusOutsideBlock = 1;  // a feature fell outside its position's declared row block
 
 struct FtArgs {
-    const float* table;  // [n_inputs][H] effective weights (l0w, or l0w + tiled l0f)
-    const float* bias;   // [H]
+    const float* table;   // [n_inputs][H] effective weights: l0w, or l0w + tiled l0f already merged
+    const float* factor;  // tiled forward only: [factor_rows][H] l0f to be added to `table` (= l0w) on the fly, or null
+    int factor_rows;
+    const float* bias;    // [H]
     const uint16_t* idx_stm;
     const uint16_t* idx_nstm;  // [n][nnz] each, 0xFFFF = empty slot
     int n, nnz, H, n_inputs, act;
@@ -326,19 +328,33 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
     const int R = t.block_rows;
     float* tile = reinterpret_cast<float*>(smem_raw);
     {   // fill the tile: 8 work items per row, each 8 floats of the row
+        // with a factoriser the table row is l0w[row] + l0f[row mod factor_rows], one fp32 add per
+        // element exactly as the reference forms `l0w + l0f.repeat(n)` (model/builder.rs:421-424)
         const float* src = a.table + (size_t)w.block * R * a.H;
         for (int i = threadIdx.x; i < R * 8; i += kFwdThreads) {
             const int row = i >> 3, q = i & 7;
             float4* dst = reinterpret_cast<float4*>(tile + row * kTileCols + q * 8);
+            const float* frow = a.factor ? a.factor + (size_t)((w.block * R + row) % a.factor_rows) * a.H : nullptr;
             if (PAIRWISE) {
-                const float4 lo = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + w.slab * 32 + q * 4));
-                const float4 hi = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + a.H / 2 + w.slab * 32 + q * 4));
+                const int c_lo = w.slab * 32 + q * 4, c_hi = a.H / 2 + c_lo;
+                float4 lo = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_lo));
+                float4 hi = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_hi));
+                if (frow) {
+                    lo = add4(lo, __ldg(reinterpret_cast<const float4*>(frow + c_lo)));
+                    hi = add4(hi, __ldg(reinterpret_cast<const float4*>(frow + c_hi)));
+                }
                 dst[0] = make_float4(lo.x, hi.x, lo.y, hi.y);
                 dst[1] = make_float4(lo.z, hi.z, lo.w, hi.w);
             } else {
-                const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + w.slab * 64 + q * 8);
-                dst[0] = __ldg(g);
-                dst[1] = __ldg(g + 1);
+                const int c0 = w.slab * 64 + q * 8;
+                const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c0);
+                float4 v0 = __ldg(g), v1 = __ldg(g + 1);
+                if (frow) {
+                    v0 = add4(v0, __ldg(reinterpret_cast<const float4*>(frow + c0)));
+                    v1 = add4(v1, __ldg(reinterpret_cast<const float4*>(frow + c0 + 4)));
+                }
+                dst[0] = v0;
+                dst[1] = v1;
             }
         }
         if (threadIdx.x < kTileCols) tile[R * kTileCols + threadIdx.x] = 0.f;

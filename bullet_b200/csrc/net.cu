@@ -257,7 +257,12 @@ int splits_for(const b200_net* net, int n, double overhead) {
 b200::FtArgs ft_args(b200_net* net, const Slot& s) {
     b200::FtArgs a{};
     const b200_net_desc& d = net->d;
-    a.table = net->table;
+    // the tiled forward adds the factoriser while it fills its tile; only the gather forward
+    // needs the merged table
+    const bool merged = net->d.factoriser_rows && !net->fwd_tiled();
+    a.table = merged ? net->table : net->P + net->find("l0w")->off;
+    a.factor = (net->d.factoriser_rows && !merged) ? net->P + net->find("l0f")->off : nullptr;
+    a.factor_rows = net->d.factoriser_rows;
     a.bias = net->P + net->find("l0b")->off;
     a.idx_stm = s.dev<uint16_t>(s.off_stm);
     a.idx_nstm = s.dev<uint16_t>(s.off_nstm);
@@ -329,7 +334,7 @@ b200::DenseArgs dense_args(b200_net* net, const Slot& s, bool want_grad) {
 
 int refresh_table(b200_net* net) {
     if (!net->table_dirty) return 0;
-    if (net->d.factoriser_rows) {
+    if (net->d.factoriser_rows && !net->fwd_tiled()) {
         const Tensor* w = net->find("l0w");
         const Tensor* f = net->find("l0f");
         const size_t n4 = (size_t)w->n / 4, block4 = (size_t)f->n / 4;
@@ -390,9 +395,10 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
     w.gW = net->G + net->find(name)->off;
     snprintf(name, sizeof name, "l%db", layer + 1);
     w.gB = net->G + net->find(name)->off;
-    const int threads = w.K + 1 >= 256 ? 256 : ((w.K + 1 + 31) / 32) * 32;
-    const int gx = (w.K + 1 + threads - 1) / threads;
-    int chunks = std::max(1, std::min((s.n + 63) / 64, kTargetCtas / gx));
+    const int groups = w.K / 4 + 1;  // four columns per thread, plus the bias
+    const int threads = groups >= 128 ? 128 : ((groups + 31) / 32) * 32;
+    const int gx = (groups + threads - 1) / threads;
+    int chunks = std::max(1, std::min((s.n + 63) / 64, 8 * kSmCount / gx));  // 128-thread CTAs, several per SM
     w.chunk_len = ((s.n + chunks - 1) / chunks + 63) / 64 * 64;
     chunks = (s.n + w.chunk_len - 1) / w.chunk_len;
     dim3 grid(gx, chunks);
@@ -577,6 +583,7 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
                               "tiled feature-transformer kernels need ft_block_rows > 0 dividing n_inputs, at most "
                               "about 800 rows per block, and ft_out a multiple of 64");
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
+        net->table_dirty = true;  // the gather forward reads the merged table, the tiled one does not keep it fresh
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
         return 0;
     }
