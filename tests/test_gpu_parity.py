@@ -285,6 +285,34 @@ def test_checkpoint_round_trip_in_reference_format(oracle32, tmp_path):
         n.close()
 
 
+def test_real_positions_from_the_reference_fixture(oracle32):
+    """1024 real positions (first records of the reference's examples/tests/batch.bf): kings sit on a few
+    squares, so the king buckets are very unevenly filled — the tiled kernels must not care."""
+    import os
+
+    rec = np.fromfile(os.path.join(os.path.dirname(__file__), "golden", "batch_head.bf"), dtype=synth.CHESS_DTYPE)
+    B = len(rec)
+    for name, desc, game in (NETS[3], NETS[4], NETS[1]):
+        desc = dataclasses.replace(desc, max_batch=B)
+        batch = oracle32.map_batch(game, rec, desc)
+        if game == "chess_buckets":
+            counts = np.bincount(batch[0][:, 0] // 768, minlength=16)
+            assert counts.max() > 4 * max(1, counts[counts > 0].min())     # skewed indeed
+        w = rich_weights(desc)
+        loss_ref, g_ref, _ = oracle32.net_grad(desc, w, *batch)
+        w_ref, _, _, _ = oracle32.train(desc, w, [batch], 1e-3, AdamWParams())
+        for mode in modes_for(desc):
+            net = make_net(desc, mode, w)
+            net.upload(0, *batch)
+            net.step(0, 1e-3, 1.0 / B)
+            assert abs(net.loss() - loss_ref) <= 1e-4 * abs(loss_ref)
+            g, p = net.tensors(3), net.tensors(0)
+            for k in g_ref:
+                assert np.abs(g[k] - g_ref[k]).max() <= 3e-5 * max(np.abs(g_ref[k]).max(), 1e-20), (name, mode, k)
+                assert rel2(p[k], w_ref[k]) <= 1e-4, (name, mode, k)
+            net.close()
+
+
 def test_edge_batches(oracle32):
     """One position, ragged sizes, empty feature lists, duplicate features, invalid slots."""
     name, desc, game = NETS[4]
