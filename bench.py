@@ -229,6 +229,10 @@ def run_ours(args, rank, world, local_rank):
         net.set_option("ft_fwd_mode", args.ft_fwd_mode)
     if args.ft_bwd_mode:
         net.set_option("ft_bwd_mode", args.ft_bwd_mode)
+    if args.opt:
+        for kv in args.opt:
+            k, v = kv.split("=")
+            net.set_option(k, int(v))
     if args.ft_bwd_wide is not None:
         net.set_option("ft_bwd_wide", args.ft_bwd_wide)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
@@ -367,6 +371,7 @@ def main():
     ap.add_argument("--ft-mode", type=int, default=0, help="0 auto, 1 gather kernels, 2 tiled kernels")
     ap.add_argument("--ft-fwd-mode", type=int, default=0)
     ap.add_argument("--ft-bwd-mode", type=int, default=0)
+    ap.add_argument("--opt", action="append", help="library option key=value (b200_net_set_option), repeatable")
     ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads, one CTA per SM")
     ap.add_argument("--dp-parts", type=int, default=4,
                     help="N > 1: slices of the l0w gradient all-reduced while the backward still runs (1 = one all-reduce)")

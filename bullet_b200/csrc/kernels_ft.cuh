@@ -46,8 +46,11 @@ struct FtArgs {
 
 struct TileArgs {
     int block_rows;          // R
-    int nslabs, nsplit;      // H/64 column slabs; position ranges (CTAs) per (block, slab)
-    int block0;              // first table row block this launch covers (grid spans a run of blocks)
+    int nslabs;              // H/64 column slabs
+    // Work items: a launch runs one CTA per (item, slab); consecutive CTAs share an item.
+    // forward: (block, first, last+1 index into pair_order, 0); backward: (block, first chunk,
+    // last+1 chunk, 0).  Items of one block are near-equal in size however full the block is.
+    const int4* items;
     const int* pair_order;   // [2n] pair ids (position*2 + perspective) grouped by block, or null = identity
     const int* block_begin;  // [nblocks+1] offsets into pair_order
     int* status;
@@ -60,7 +63,6 @@ struct TileArgs {
     // backward only: the visiting order cut into chunks of at most ft_bwd_chunk pairs that never
     // straddle a block, and per chunk the row-major lists built by ft_csr_kernel
     const int4* chunks;            // [nchunks] (block, first index into pair_order, pairs, 0)
-    const int* block_chunk_begin;  // [nblocks + 1] first chunk of every block
     uint16_t* csr_ent;             // [nchunks][ent_cap] positions of the chunk grouped by row, lists padded to x4
     int* csr_start;                // [nchunks][start_cap] start of every row's list; start[R] = total
     int ent_cap, start_cap;
@@ -260,17 +262,15 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 struct TileWork {
-    int block, slab, begin, end;  // pair_order range [begin, end) served by this CTA
+    int block, slab, begin, end;  // forward: pair_order range [begin, end); backward: chunk range
 };
 __device__ __forceinline__ TileWork tile_work(const TileArgs& t) {
+    const int4 item = t.items[blockIdx.x / t.nslabs];
     TileWork w;
-    const int split = blockIdx.x % t.nsplit;
-    const int rest = blockIdx.x / t.nsplit;
-    w.slab = rest % t.nslabs;
-    w.block = t.block0 + rest / t.nslabs;
-    const int b0 = t.block_begin[w.block], cnt = t.block_begin[w.block + 1] - b0;
-    w.begin = b0 + (int)(((long long)cnt * split) / t.nsplit);
-    w.end = b0 + (int)(((long long)cnt * (split + 1)) / t.nsplit);
+    w.slab = blockIdx.x % t.nslabs;
+    w.block = item.x;
+    w.begin = item.y;
+    w.end = item.z;
     return w;
 }
 
@@ -310,7 +310,7 @@ static __global__ void __launch_bounds__(256) ft_prepare_kernel(FtArgs a, TileAr
     if (lane == 0) t.list_count[i] = cnt4;
 }
 
-// Forward.  grid = nblocks * nslabs * nsplit CTAs of 1024 threads (one per SM); dynamic
+// Forward.  grid = items * nslabs CTAs of 1024 threads (one per SM); dynamic
 // shared memory = (R+1) tile rows, the extra row all zero.  Each warp serves one
 // (position, perspective) at a time: it walks the pair's prepared list four offsets per
 // (warp-uniform) load, and every lane adds its column pair with one 64-bit shared-memory
@@ -522,15 +522,15 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
     for (int i = threadIdx.x; i <= R; i += kCsrThreads) start_out[i] = start[i];
 }
 
-// grid = nblocks * nslabs * nsplit CTAs of THREADS threads (1024: one per SM; 512: two per SM).
+// grid = items * nslabs CTAs of THREADS threads (1024: one per SM; 512: two per SM).
 template <bool PAIRWISE, int THREADS>
 __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int kBwdThreads = THREADS;
     constexpr int NW = kBwdThreads / 32;
-    const int split = blockIdx.x % t.nsplit, rest = blockIdx.x / t.nsplit;
-    const int slab = rest % t.nslabs, block = t.block0 + rest / t.nslabs;
+    const TileWork w = tile_work(t);
+    const int slab = w.slab, block = w.block;
     const int R = t.block_rows, CP = t.chunk_len;
     f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                                          // [CP + 1][32] (A, B) pairs
     uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists of the chunk
@@ -540,9 +540,7 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
     float bsum_a = 0.f, bsum_b = 0.f;
     if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line
 
-    const int cb = t.block_chunk_begin[block], nc = t.block_chunk_begin[block + 1] - cb;
-    const int ch_begin = cb + (int)(((long long)nc * split) / t.nsplit), ch_end = cb + (int)(((long long)nc * (split + 1)) / t.nsplit);
-    for (int ch = ch_begin; ch < ch_end; ch++) {
+    for (int ch = w.begin; ch < w.end; ch++) {
         const int4 chunk = t.chunks[ch];
         const int c0 = chunk.y, cn = chunk.z;
         // the chunk's row lists: asynchronous copy into shared memory, overlapped with the staging below

@@ -50,6 +50,7 @@ namespace {
 constexpr int kSmCount = 148;
 constexpr int kTargetCtas = 4 * kSmCount;  // two resident CTAs per SM, two waves
 constexpr int64_t kAlignFloats = 64;       // 256-byte tensor alignment in the flat buffers
+constexpr int kMinItemPairs = 128;         // a forward work item serves at least this many pairs per tile load
 
 struct Tensor {
     std::string name;
@@ -64,8 +65,10 @@ struct Slot {
     int n = 0;
     int n_dtiles = 0;  // CTA tiles of the dense kernels held in off_dtiles
     int n_chunks = 0, chunk_len = 0;  // chunks of the tiled FT backward held in off_chunks, and their size
+    int n_fitems = 0;                 // work items of the tiled forward / backward (see TileArgs::items)
+    std::vector<int> bitem_begin;     // [nblocks + 1] first backward item of every block
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
-           off_dtiles = 0, off_chunks = 0, off_bcb = 0, bytes = 0;
+           off_dtiles = 0, off_chunks = 0, off_fitems = 0, off_bitems = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
     bool has_ready = false, has_consumed = false;
     template <class T>
@@ -188,15 +191,15 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.off_blocks = take((size_t)(net->nblocks + 1) * 4);
     s.off_dtiles = take(((size_t)n / b200::kDenseTile + d.n_out_buckets + 1) * 8);
     s.off_chunks = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
-    s.off_bcb = take((size_t)(net->nblocks + 1) * 4);
+    s.off_fitems = take(((size_t)2 * n / kMinItemPairs + net->nblocks + 1) * 16);
+    s.off_bitems = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
     s.bytes = off;
 }
 
 template <bool PW>
-int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled) {
+int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int items) {
     if (tiled) {
-        b200::ft_forward_tiled_kernel<PW><<<net->nblocks * t.nslabs * t.nsplit, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows),
-                                            net->stream>>>(a, t);
+        b200::ft_forward_tiled_kernel<PW><<<items * t.nslabs, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -207,13 +210,13 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 }
 
 template <bool PW>
-int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int blocks) {
+int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int items) {
     if (tiled) {
         const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len);
         if (t.chunk_len == b200::ft_bwd_chunk(a.nnz, true))
-            b200::ft_backward_tiled_kernel<PW, 1024><<<blocks * t.nslabs * t.nsplit, 1024, smem, net->stream>>>(a, t);
+            b200::ft_backward_tiled_kernel<PW, 1024><<<items * t.nslabs, 1024, smem, net->stream>>>(a, t);
         else
-            b200::ft_backward_tiled_kernel<PW, 512><<<blocks * t.nslabs * t.nsplit, 512, smem, net->stream>>>(a, t);
+            b200::ft_backward_tiled_kernel<PW, 512><<<items * t.nslabs, 512, smem, net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -234,16 +237,15 @@ int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArg
         default: return b200::fail(B200_ERR_UNSUPPORTED, "rows per bucket %d", m); \
     }
 
-// Position ranges (CTAs) per (block, slab) tile.  One CTA is resident per SM, so the grid
-// runs in waves of kSmCount; splitting a tile's positions over more CTAs evens out the last
-// wave but repeats the tile's fixed cost (`overhead`, as a fraction of a whole tile's work:
-// the tile load in the forward, the atomic flush in the backward).
-int splits_for(const b200_net* net, int n, double overhead) {
+// How many near-equal work items an average block is cut into.  One CTA is resident per SM,
+// so the grid runs in waves of kSmCount; more items even out the last wave but repeat the
+// tile's fixed cost (`overhead`, as a fraction of a whole tile's work: the tile load in the
+// forward, the gradient flush in the backward).  `most` bounds the count from above.
+int splits_for(const b200_net* net, int most, double overhead) {
     const int tiles = net->nblocks * net->nslabs;
-    const int most = std::max(1, std::min(512, (2 * n) / (128 * net->nblocks)));
     int best = 1;
     double best_cost = 1e30;
-    for (int sp = 1; sp <= most; sp++) {
+    for (int sp = 1; sp <= std::max(1, std::min(512, most)); sp++) {
         const double waves = (double)((tiles * sp + kSmCount - 1) / kSmCount);
         const double cost = waves * (1.0 / sp + overhead);
         if (cost < best_cost * 0.98) {
@@ -279,11 +281,11 @@ b200::FtArgs ft_args(b200_net* net, const Slot& s) {
     return a;
 }
 
-b200::TileArgs tile_args(b200_net* net, const Slot& s, int nsplit) {
+b200::TileArgs tile_args(b200_net* net, const Slot& s, bool backward) {
     b200::TileArgs t{};
     t.block_rows = net->d.ft_block_rows;
     t.nslabs = net->nslabs;
-    t.nsplit = nsplit;
+    t.items = s.dev<int4>(backward ? s.off_bitems : s.off_fitems);
     t.pair_order = net->nblocks > 1 ? s.dev<int>(s.off_pairs) : nullptr;
     t.block_begin = s.dev<int>(s.off_blocks);
     t.status = net->status;
@@ -291,7 +293,6 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, int nsplit) {
     t.list_count = net->ft_list_count;
     t.list_len = (net->d.nnz + 3) & ~3;
     t.chunks = s.dev<int4>(s.off_chunks);
-    t.block_chunk_begin = s.dev<int>(s.off_bcb);
     t.csr_ent = net->csr_ent;
     t.csr_start = net->csr_start;
     t.chunk_len = s.chunk_len;
@@ -365,13 +366,13 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
     const b200_net_desc& d = net->d;
     const bool tiled = net->fwd_tiled();
     b200::FtArgs fa = ft_args(net, s);
-    b200::TileArgs ta = tile_args(net, s, tiled ? splits_for(net, s.n, 0.1) : 1);
+    b200::TileArgs ta = tile_args(net, s, false);
     if (tiled || (want_grad && net->bwd_tiled())) {
         b200::ft_prepare_kernel<<<(2 * s.n + 7) / 8, 256, 0, net->stream>>>(fa, ta);
         LAUNCHED(net);
     }
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][0], net->stream));
-    int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled) : launch_ft_forward<false>(net, fa, ta, tiled);
+    int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled, s.n_fitems) : launch_ft_forward<false>(net, fa, ta, tiled, s.n_fitems);
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
     b200::DenseArgs da = dense_args(net, s, want_grad);
@@ -735,18 +736,41 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         h_blocks[0] = 0;
         h_blocks[1] = 2 * n;
     }
-    {   // chunks of the tiled backward: runs of at most ft_bwd_chunk pairs that stay inside one block
+    if (net->tiled_ok) {
+        // chunks of the tiled backward: runs of at most ft_bwd_chunk pairs that stay inside one
+        // block; and the work items of both passes: every block cut into near-equal pieces whose
+        // size is set by the AVERAGE block, so a crowded block simply yields more items
         int4* h_chunks = s.host<int4>(s.off_chunks);
-        int* h_bcb = s.host<int>(s.off_bcb);
+        int4* h_fitems = s.host<int4>(s.off_fitems);
+        int4* h_bitems = s.host<int4>(s.off_bitems);
         const int cp = net->bwd_chunk();
         s.chunk_len = cp;
-        int nc = 0;
+        const int avg_pairs = std::max(1, 2 * n / nb);
+        const int f_target = std::max(kMinItemPairs, (avg_pairs + splits_for(net, avg_pairs / kMinItemPairs, 0.1) - 1) /
+                                                         splits_for(net, avg_pairs / kMinItemPairs, 0.1));
+        const int avg_chunks = std::max(1, (avg_pairs + cp - 1) / cp);
+        const int b_split = splits_for(net, avg_chunks, 0.3);
+        const int b_target = std::max(1, (avg_chunks + b_split - 1) / b_split);  // chunks per item
+        int nc = 0, nf = 0, nbi = 0;
+        s.bitem_begin.assign(nb + 1, 0);
         for (int b = 0; b < nb; b++) {
-            h_bcb[b] = nc;
-            for (int at = h_blocks[b]; at < h_blocks[b + 1]; at += cp) h_chunks[nc++] = make_int4(b, at, std::min(cp, h_blocks[b + 1] - at), 0);
+            const int lo = h_blocks[b], hi = h_blocks[b + 1], cnt = hi - lo;
+            const int first_chunk = nc;
+            for (int at = lo; at < hi; at += cp) h_chunks[nc++] = make_int4(b, at, std::min(cp, hi - at), 0);
+            // forward: at least one item per block (an empty block still has nothing to write, so none is needed)
+            const int fpieces = cnt > 0 ? (cnt + f_target - 1) / f_target : 0;
+            for (int k = 0; k < fpieces; k++)
+                h_fitems[nf++] = make_int4(b, lo + (int)((long long)cnt * k / fpieces), lo + (int)((long long)cnt * (k + 1) / fpieces), 0);
+            s.bitem_begin[b] = nbi;
+            const int chunks_here = nc - first_chunk;
+            const int bpieces = (chunks_here + b_target - 1) / b_target;
+            for (int k = 0; k < bpieces; k++)
+                h_bitems[nbi++] = make_int4(b, first_chunk + (int)((long long)chunks_here * k / bpieces),
+                                            first_chunk + (int)((long long)chunks_here * (k + 1) / bpieces), 0);
         }
-        h_bcb[nb] = nc;
+        s.bitem_begin[nb] = nbi;
         s.n_chunks = nc;
+        s.n_fitems = nf;
     }
     CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
     net->h2d_bytes += (int64_t)s.bytes;
@@ -772,7 +796,7 @@ int b200_backward_begin(b200_net* net, int slot) {
     CK(cudaEventRecord(ev[2], net->stream));
     if (net->bwd_tiled() && s.n_chunks > 0) {  // row-major lists of every chunk, shared by all column slabs
         b200::FtArgs fa = ft_args(net, s);
-        b200::TileArgs ta = tile_args(net, s, 1);
+        b200::TileArgs ta = tile_args(net, s, true);
         b200::ft_csr_kernel<<<s.n_chunks, b200::kCsrThreads, b200::ft_csr_smem(d.ft_block_rows, d.nnz, s.chunk_len), net->stream>>>(fa, ta);
         LAUNCHED(net);
     }
@@ -805,11 +829,17 @@ int b200_backward_ft(b200_net* net, int slot, int part, int n_parts) {
     const Tensor* l0w = net->find("l0w");
     {
         b200::FtArgs fa = ft_args(net, s);
-        b200::TileArgs ta = tile_args(net, s, tiled ? splits_for(net, s.n, 0.3) : 1);
-        ta.block0 = part * per;
-        const int blocks = tiled ? per : 1;
-        int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled, blocks) : launch_ft_backward<false>(net, fa, ta, tiled, blocks);
-        if (rc) return rc;
+        b200::TileArgs ta = tile_args(net, s, true);
+        int items = 0;
+        if (tiled) {  // the items of this part's run of blocks
+            const int first = s.bitem_begin[part * per], last = s.bitem_begin[(part + 1) * per];
+            ta.items += first;
+            items = last - first;
+        }
+        if (!tiled || items > 0) {
+            int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled, items) : launch_ft_backward<false>(net, fa, ta, tiled, items);
+            if (rc) return rc;
+        }
     }
     if (part == n_parts - 1) CK(cudaEventRecord(ev[4], net->stream));
     if (d.factoriser_rows) {

@@ -34,12 +34,14 @@ namespace {
 constexpr int kMaxBlocks = 1024;  // table row blocks the grouping supports
 
 // Scratch layout, in ints: [0] status word, [1 .. 1+kMaxBlocks] histogram then running
-// cursors, [.. +kMaxBlocks+1] block_begin, then per pair: block id [2n], pair order [2n],
-// prepared list length [2n], and the prepared row lists [2n][nnz rounded up to 4].
+// cursors, [.. +kMaxBlocks+1] block_begin, one work item (int4) per block, then per pair:
+// block id [2n], pair order [2n], prepared list length [2n], and the prepared row lists
+// [2n][nnz rounded up to 4] as u16.
 // Every section starts on a 256-byte boundary: the row lists are read with 16-byte loads.
 constexpr size_t kSectionAlign = 64;  // ints
 constexpr size_t align_ints(size_t v) { return (v + kSectionAlign - 1) / kSectionAlign * kSectionAlign; }
-constexpr size_t kScratchHeader = align_ints(1 + (kMaxBlocks + 1) + (kMaxBlocks + 1));
+constexpr size_t kItemsAt = align_ints(1 + (kMaxBlocks + 1) + (kMaxBlocks + 1));
+constexpr size_t kScratchHeader = kItemsAt + 4 * kMaxBlocks;
 int list_len(int nnz) { return (nnz + 3) & ~3; }
 size_t scratch_ints(int n, int nnz) { return kScratchHeader + 3 * align_ints((size_t)2 * n) + (size_t)2 * n * list_len(nnz); }
 
@@ -89,6 +91,12 @@ __global__ void group_scan_kernel(int* counts, int* begin, int nblocks) {
     }
 }
 
+// the forward's work items: one per block, all of the block's pairs
+__global__ void group_items_kernel(const int* begin, int nblocks, int4* items) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < nblocks) items[b] = make_int4(b, begin[b], begin[b + 1], 0);
+}
+
 __global__ void group_fill_kernel(const int* blk, int n, int* cursors, int* order) {
     const int pair = blockIdx.x * blockDim.x + threadIdx.x;
     if (pair >= 2 * n) return;
@@ -132,6 +140,8 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     group_count_kernel<<<grid, threads, 0, stream>>>(op->idx_stm, op->idx_nstm, n, op->nnz, op->n_inputs, R, counts, blk);
     group_scan_kernel<<<1, 256, 0, stream>>>(counts, begin, nblocks);
     group_fill_kernel<<<grid, threads, 0, stream>>>(blk, n, counts, order);
+    int4* items = reinterpret_cast<int4*>(scratch + kItemsAt);
+    group_items_kernel<<<(nblocks + 255) / 256, 256, 0, stream>>>(begin, nblocks, items);
     CK(cudaGetLastError());
 
     b200::FtArgs a{};
@@ -149,7 +159,7 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     b200::TileArgs t{};
     t.block_rows = R;
     t.nslabs = op->ft_out / b200::kTileCols;
-    t.nsplit = 1;
+    t.items = items;
     t.pair_order = order;
     t.block_begin = begin;
     t.status = status;
