@@ -237,7 +237,8 @@ def run_ours(args, rank, world, local_rank):
         net.set_option("ft_bwd_wide", args.ft_bwd_wide)
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
     parts = args.dp_parts if (world > 1 and net.stat("ft_tiled") & 2) else 1
-    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts)
+    shard = bool(args.dp_shard) and world > 1
+    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts, shard_optimiser=shard)
     lr = cfg.lr
 
     def barrier():
@@ -344,7 +345,8 @@ def run_ours(args, rank, world, local_rank):
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
-                   "parallelism": f"dp{world}", "allreduce_parts": parts + 1 if parts > 1 else 1, "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
+                   "parallelism": f"dp{world}", "exchange": ("reduce-scatter + sharded AdamW + all-gather" if shard else
+                                                         f"all-reduce in {parts + 1} pipelined parts" if parts > 1 else "one all-reduce"), "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
                                   "backward": "tiled" if net.stat("ft_tiled") & 2 else "gather"},
                    "l2": f"inputs larger than L2: {N_DISTINCT} distinct batches cycled, per-step activations "
                          f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
@@ -373,7 +375,9 @@ def main():
     ap.add_argument("--ft-bwd-mode", type=int, default=0)
     ap.add_argument("--opt", action="append", help="library option key=value (b200_net_set_option), repeatable")
     ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads, one CTA per SM")
-    ap.add_argument("--dp-parts", type=int, default=4,
+    ap.add_argument("--dp-shard", type=int, default=1,
+                    help="N > 1: 1 = reduce-scatter, AdamW on 1/N of the parameters per rank, all-gather; 0 = all-reduce")
+    ap.add_argument("--dp-parts", type=int, default=1,
                     help="N > 1: slices of the l0w gradient all-reduced while the backward still runs (1 = one all-reduce)")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -118,6 +118,7 @@ extern "C" {
     pub fn b200_grad_part(net: *mut b200_net, part: c_int, n_parts: c_int, first_float: *mut i64, n_floats: *mut i64) -> c_int;
     pub fn b200_update_range(net: *mut b200_net, lr: f32, grad_factor: f32, first_float: i64, n_floats: i64) -> c_int;
     pub fn b200_update_end(net: *mut b200_net) -> c_int;
+    pub fn b200_flat_buffer(net: *mut b200_net, kind: c_int, device_ptr: *mut *mut c_void, n_floats: *mut i64) -> c_int;
     pub fn b200_loss(net: *mut b200_net, loss_sum: *mut f32) -> c_int;
     pub fn b200_loss_of(net: *mut b200_net, steps_back: c_int, loss_sum: *mut f32) -> c_int;
     pub fn b200_forward(net: *mut b200_net, slot: c_int, out_host: *mut f32) -> c_int;

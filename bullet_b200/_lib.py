@@ -18,7 +18,7 @@ SYMBOLS = (
     "b200_map_chess_buckets_mirrored", "b200_map_ataxx147", "b200_material_count", "b200_make_targets",
     "b200_pack_indices_u16", "b200_unpack_indices_u16", "b200_net_get_stat", "b200_op_ft_forward", "b200_op_ft_forward_noalloc",
     "b200_backward_begin", "b200_backward_ft", "b200_backward_end", "b200_grad_part", "b200_update_range",
-    "b200_update_end", "b200_loss_of", "b200_checkpoint_save", "b200_checkpoint_load",
+    "b200_update_end", "b200_loss_of", "b200_checkpoint_save", "b200_checkpoint_load", "b200_flat_buffer",
 )
 
 
@@ -82,6 +82,7 @@ def load() -> ctypes.CDLL:
         "b200_update_range": [vp, f32, f32, i64, i64],
         "b200_update_end": [vp],
         "b200_grad_buffer": [vp, ctypes.POINTER(vp), ctypes.POINTER(i64)],
+        "b200_flat_buffer": [vp, ctypes.c_int, ctypes.POINTER(vp), ctypes.POINTER(i64)],
         "b200_loss": [vp, ctypes.POINTER(f32)],
         "b200_loss_of": [vp, ctypes.c_int, ctypes.POINTER(f32)],
         "b200_forward": [vp, ctypes.c_int, vp],

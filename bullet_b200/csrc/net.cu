@@ -464,7 +464,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         t.off = off;
         off += (t.n + kAlignFloats - 1) / kAlignFloats * kAlignFloats;
     }
-    net->n_flat = off;
+    net->n_flat = (off + 1023) / 1024 * 1024;  // a multiple of 4 floats x 256: splits evenly over up to 256 ranks
 
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
@@ -980,6 +980,15 @@ int b200_step(b200_net* net, int slot, float lr, float grad_factor) {
 int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats) {
     if (!net || !device_ptr || !n_floats) return b200::fail(B200_ERR_ARG, "grad_buffer: null argument");
     *device_ptr = net->G;
+    *n_floats = net->n_flat;
+    return 0;
+}
+
+int b200_flat_buffer(b200_net* net, int kind, void** device_ptr, int64_t* n_floats) {
+    if (!net || !device_ptr || !n_floats) return b200::fail(B200_ERR_ARG, "flat_buffer: null argument");
+    float* base = kind_base(net, kind);
+    if (!base) return b200::fail(B200_ERR_ARG, "flat_buffer: unknown kind %d", kind);
+    *device_ptr = base;
     *n_floats = net->n_flat;
     return 0;
 }

@@ -46,7 +46,7 @@ class DataParallelStep:
     `backward_begin/backward_ft/backward_end`, `grad_part`, `update_range`, `update_end`.
     """
 
-    def __init__(self, engine, global_batch: int, parts: int = 1, process_group=None):
+    def __init__(self, engine, global_batch: int, parts: int = 1, shard_optimiser: bool = False, process_group=None):
         import torch.distributed as dist
 
         self.engine = engine
@@ -54,10 +54,48 @@ class DataParallelStep:
         self.group = process_group
         self.dist = dist
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.parts = parts if self.world > 1 else 1
+        self.shard = shard_optimiser and self.world > 1
+        if self.shard and engine.grad.numel() % self.world:
+            raise ValueError("the flat buffer does not split evenly over the ranks")
+
+    def _sharded_step(self, slot: int, lr: float) -> None:
+        """reduce-scatter the gradients, AdamW on this rank's 1/world of the flat buffer only,
+        all-gather the weights.  Same bytes on the wire as one all-reduce, 1/world of the
+        optimiser traffic per GPU.  Momentum and velocity then live sharded: each rank holds the
+        true values for its own range only (`gather_state` collects them, e.g. for a checkpoint).
+        The summed loss rides in float 0: reduced onto rank 0, copied into the weight buffer's
+        unused first float, gathered with the weights, and copied back on every rank."""
+        eng, dist = self.engine, self.dist
+        per = eng.grad.numel() // self.world
+        mine = slice(self.rank * per, (self.rank + 1) * per)
+        eng.backward(slot)
+        if dist.get_backend(self.group) == "nccl":
+            dist.reduce_scatter_tensor(eng.grad[mine], eng.grad, group=self.group)
+        else:  # gloo has no reduce-scatter: reduce everything, use this rank's part
+            dist.all_reduce(eng.grad, group=self.group)
+        if self.rank == 0:
+            eng.param[0:1].copy_(eng.grad[0:1])
+        eng.update_range(lr, 1.0 / self.global_batch, self.rank * per, per)
+        dist.all_gather_into_tensor(eng.param, eng.param[mine], group=self.group)
+        eng.grad[0:1].copy_(eng.param[0:1])
+        eng.update_end()
+
+    def gather_state(self) -> None:
+        """After sharded steps: make momentum and velocity complete on every rank."""
+        if not self.shard:
+            return
+        per = self.engine.grad.numel() // self.world
+        mine = slice(self.rank * per, (self.rank + 1) * per)
+        for buf in self.engine.state_buffers():
+            self.dist.all_gather_into_tensor(buf, buf[mine].clone(), group=self.group)
 
     def step(self, slot: int, lr: float) -> None:
         eng, gf = self.engine, 1.0 / self.global_batch
+        if self.shard:
+            self._sharded_step(slot, lr)
+            return
         if self.parts == 1:
             eng.backward(slot)
             if self.world > 1:
@@ -99,6 +137,8 @@ class NetEngine:
         self.net = net
         ptr, count = net.grad_buffer()
         self.grad = wrap_device_buffer(ptr, count, device)
+        self.param, self._m, self._v = (wrap_device_buffer(*net.flat_buffer(kind), device) for kind in (0, 1, 2))
+        self.state_buffers = lambda: [self._m, self._v]
         for name in ("backward", "update", "backward_begin", "backward_ft", "backward_end", "grad_part",
                      "update_range", "update_end"):
             setattr(self, name, getattr(net, name))

@@ -150,6 +150,12 @@ class Net:
         _lib.check(self.lib.b200_net_get_activation(self._h, which, _p(out), out.size))
         return out
 
+    def flat_buffer(self, kind: int):
+        """(device address, number of floats) of a flat buffer: weights, momentum, velocity or gradients."""
+        ptr, n = ctypes.c_void_p(), ctypes.c_int64()
+        _lib.check(self.lib.b200_flat_buffer(self._h, kind, ctypes.byref(ptr), ctypes.byref(n)))
+        return ptr.value, n.value
+
     def grad_buffer(self):
         """(device address, number of floats) of the flat gradient buffer; the first float is the loss."""
         ptr, n = ctypes.c_void_p(), ctypes.c_int64()

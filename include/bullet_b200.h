@@ -148,6 +148,12 @@ int b200_backward_end(b200_net* net, int slot);
 int b200_grad_part(b200_net* net, int part, int n_parts, int64_t* first_float, int64_t* n_floats);
 int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_float, int64_t n_floats);
 int b200_update_end(b200_net* net);
+/* Device address and length of one of the four flat buffers (B200_KIND_*), all of the same
+ * layout and length (a multiple of 1024 floats); float 0 is used only in the gradient buffer.
+ * A data-parallel host that shards the optimiser reduce-scatters the gradients, runs
+ * b200_update_range on its own shard only, and all-gathers the weight buffer before
+ * b200_update_end; momentum and velocity then stay sharded until it gathers them too. */
+int b200_flat_buffer(b200_net* net, int kind, void** device_ptr, int64_t* n_floats);
 /* Summed loss of the most recent update/step (run.rs:212-221); waits for it. */
 int b200_loss(b200_net* net, float* loss_sum);
 /* The same for an earlier update: steps_back = 1 is the update before the most recent one (at

@@ -28,15 +28,23 @@ class OracleEngine:
 
         self.orc = Oracle("f32")
         self.desc, self.hp = desc, hp
-        self.w = self.orc.to_real(weights)
-        self.m, self.v = self.orc.zeros_like(desc), self.orc.zeros_like(desc)
         self.names = [k for k in desc.tensor_shapes() if k != "l0w"] + ["l0w"]
         self.offsets, at = {}, self.HEAD
         for k in self.names:
             self.offsets[k] = at
-            at += self.w[k].size
-        self.grad = torch.zeros(at, dtype=torch.float32)
+            at += weights[k].size
+        total = (at + 1023) // 1024 * 1024
+        self.flat = {kind: np.zeros(total, np.float32) for kind in ("w", "m", "v")}
+        view = lambda kind: {k: self.flat[kind][self.offsets[k]:self.offsets[k] + weights[k].size] for k in self.names}  # noqa: E731
+        self.w, self.m, self.v = view("w"), view("m"), view("v")
+        for k in self.names:
+            self.w[k][:] = weights[k]
+        self.grad = torch.zeros(total, dtype=torch.float32)
+        self.param = torch.from_numpy(self.flat["w"])
         self.slots = {}
+
+    def state_buffers(self):
+        return [torch.from_numpy(self.flat["m"]), torch.from_numpy(self.flat["v"])]
 
     def upload(self, slot, *batch):
         self.slots[slot] = batch
@@ -88,7 +96,7 @@ class OracleEngine:
         pass
 
 
-def _worker(rank, world, port, out_dir, parts):
+def _worker(rank, world, port, out_dir, parts, shard):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -102,19 +110,20 @@ def _worker(rank, world, port, out_dir, parts):
     orc = Oracle("f32")
     weights = synth.init_weights(desc, seed=3)
     eng = OracleEngine(desc, weights, AdamWParams())
-    dp = DataParallelStep(eng, global_batch=256, parts=parts)
+    dp = DataParallelStep(eng, global_batch=256, parts=parts, shard_optimiser=shard)
     losses = []
     for step in range(3):
         full = orc.map_batch(c.game, synth.records(c.game, 256, seed=50 + step), desc)
         eng.upload(0, *shard_batch(full, rank, world))
         dp.step(0, 1e-3)
         losses.append(eng.last_loss)
-    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), losses=np.array(losses), **eng.w)
+    dp.gather_state()
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), losses=np.array(losses), m_l0w=eng.m["l0w"], **eng.w)
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("parts", [1, 4])
-def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts):
+@pytest.mark.parametrize("parts,shard", [(1, False), (4, False), (1, True)])
+def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard):
     from bullet_b200 import config, synth
     from bullet_b200.configs import AdamWParams
     from bullet_b200.dp import shard_bounds
@@ -123,16 +132,19 @@ def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts):
     assert shard_bounds(8, 1, 2) == (4, 8)
     with pytest.raises(ValueError):
         shard_bounds(7, 0, 2)
-    port = 29500 + (os.getpid() + 7 * parts) % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path), parts), nprocs=2, join=True)
+    port = 29500 + (os.getpid() + 7 * parts + 3 * shard) % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path), parts, shard), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     c = config(3)
     desc = dataclasses.replace(c.desc, ft_out=64, max_batch=256)
     orc = Oracle("f32")
     batches = [orc.map_batch(c.game, synth.records(c.game, 256, seed=50 + s), desc) for s in range(3)]
-    w_ref, _, _, losses_ref = orc.train(desc, synth.init_weights(desc, seed=3), batches, 1e-3, AdamWParams())
+    w_ref, m_ref, _, losses_ref = orc.train(desc, synth.init_weights(desc, seed=3), batches, 1e-3, AdamWParams())
     np.testing.assert_allclose(r0["losses"], losses_ref, rtol=1e-5)
     for k in w_ref:
         assert np.array_equal(r0[k], r1[k]), f"replicas differ in {k}"
         err = np.linalg.norm(r0[k].astype(np.float64) - w_ref[k]) / max(np.linalg.norm(w_ref[k]), 1e-30)
         assert err <= 1e-4, (k, err)
+    # after gather_state both ranks hold the complete momentum, sharded optimiser or not
+    assert np.array_equal(r0["m_l0w"], r1["m_l0w"])
+    assert np.linalg.norm(r0["m_l0w"] - m_ref["l0w"]) <= 1e-4 * np.linalg.norm(m_ref["l0w"])
