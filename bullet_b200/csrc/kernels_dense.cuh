@@ -76,7 +76,7 @@ __device__ __forceinline__ void dense_cp_wait() { asm volatile("cp.async.wait_gr
 // Stages columns [chunk*128, chunk*128+128) of bucket k's first-layer weights; columns past
 // K1 are zero-filled.  All 256 threads take part.
 template <int M1>
-__device__ __forceinline__ void dense_stage_chunk(const DenseArgs& a, int k, int chunk, float* buf) {
+__device__ __forceinline__ void dense_stage_chunk(const DenseArgs& a, int k, int chunk, float* buf, bool commit = true) {
     constexpr int MP = dense_col_stride<M1>();
     const int c_begin = chunk * kDenseChunk;
     const float* src = a.W1g + ((size_t)k * a.K1 + c_begin) * M1;
@@ -94,7 +94,7 @@ __device__ __forceinline__ void dense_stage_chunk(const DenseArgs& a, int k, int
         for (int i = threadIdx.x; i < kDenseChunk * M1; i += blockDim.x)
             buf[i] = c_begin + i / M1 < a.K1 ? __ldg(src + i) : 0.f;
     }
-    dense_cp_commit();
+    if (commit) dense_cp_commit();
 }
 
 template <int M1>
@@ -113,58 +113,80 @@ __device__ __forceinline__ void dense_read_weights(const float* buf, int c, floa
 }
 
 // One CTA per tile of up to 32 positions of the same output bucket, four per warp.  The
-// bucket's first-layer weights stream through shared memory in 128-column chunks (double
-// buffered with cp.async) and are shared by all 32 positions; lane l takes columns l, l+32,
-// l+64, l+96 of a chunk, so x is read coalesced.  After the K1-long dot products the tiny
-// remaining layers, the loss and the backward pass down to the first layer's pre-activation
-// gradient follow per position.  grid = ntiles, block = 256.
+// bucket's first-layer weights AND the tile's rows of x stream through shared memory in
+// 128-column chunks, three chunks in flight (cp.async), so no global latency sits between
+// the chunks; lane l takes columns l, l+32, l+64, l+96 of a chunk.  After the K1-long dot
+// products the tiny remaining layers, the loss and the backward pass down to the first
+// layer's pre-activation gradient follow per position.  grid = ntiles, block = 256, dynamic
+// shared memory = dense_fwd_smem<M1>().
+constexpr int kDenseStages = 3;
+template <int M1>
+__host__ __device__ constexpr size_t dense_fwd_smem() {
+    return (size_t)kDenseStages * (kDenseChunk * dense_col_stride<M1>() + kDenseTile * kDenseChunk) * sizeof(float);
+}
+
 template <int M1>
 __global__ void __launch_bounds__(256, (M1 > 16 ? 1 : 2)) dense_forward_kernel(DenseArgs a) {
     constexpr int P = kDenseWarpPos, MP = dense_col_stride<M1>();
-    __shared__ __align__(16) float wbuf[2][kDenseChunk * MP];
+    constexpr int kStageFloats = kDenseChunk * MP + kDenseTile * kDenseChunk;
+    extern __shared__ __align__(16) float dense_smem[];
     __shared__ float loss_part[8];
+    __shared__ int s_pos[kDenseTile];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int2 t = a.tiles[blockIdx.x];
-    const int k = a.buckets[a.order[t.x]];
+    if (threadIdx.x < kDenseTile) s_pos[threadIdx.x] = a.order[t.x + min((int)threadIdx.x, t.y - 1)];
+    __syncthreads();
+    const int k = a.buckets[s_pos[0]];
     const int npos = max(0, min(P, t.y - warp * P));
     int pos[P];
 #pragma unroll
-    for (int j = 0; j < P; j++) pos[j] = a.order[npos ? t.x + warp * P + min(j, npos - 1) : t.x];
+    for (int j = 0; j < P; j++) pos[j] = s_pos[min(warp * P + j, t.y - 1)];
     float acc[P][M1];
 #pragma unroll
     for (int j = 0; j < P; j++)
 #pragma unroll
         for (int r = 0; r < M1; r++) acc[j][r] = 0.f;
     const int nchunks = (a.K1 + kDenseChunk - 1) / kDenseChunk;
-    dense_stage_chunk<M1>(a, k, 0, wbuf[0]);
-    for (int ch = 0; ch < nchunks; ch++) {
-        if (ch + 1 < nchunks) dense_stage_chunk<M1>(a, k, ch + 1, wbuf[(ch + 1) & 1]);
-        float xs[P][4];
-#pragma unroll
-        for (int j = 0; j < P; j++)
-#pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
-                const int c = ch * kDenseChunk + jj * 32 + lane;
-                xs[j][jj] = (npos && c < a.K1) ? a.x[(size_t)pos[j] * a.K1 + c] : 0.f;
+    // one cp.async group per chunk: the bucket's weights and the tile's x for 128 columns
+    auto stage = [&](int ch) {
+        if (ch < nchunks) {
+            float* wb = dense_smem + (ch % kDenseStages) * kStageFloats;
+            float* xb = wb + kDenseChunk * MP;
+            dense_stage_chunk<M1>(a, k, ch, wb, false);
+            for (int i = threadIdx.x; i < kDenseTile * (kDenseChunk / 4); i += blockDim.x) {
+                const int p = i / (kDenseChunk / 4), q = i % (kDenseChunk / 4);
+                const int c = ch * kDenseChunk + q * 4;  // K1 is a multiple of four: a quad is inside or outside
+                float* dst = xb + p * kDenseChunk + q * 4;
+                if (c < a.K1)
+                    dense_cp_async16(dst, a.x + (size_t)s_pos[p] * a.K1 + c);
+                else
+                    *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
             }
-        if (ch + 1 < nchunks)
-            dense_cp_wait<1>();
-        else
-            dense_cp_wait<0>();
+        }
+        dense_cp_commit();  // an empty group past the end keeps the group count in step with `ch`
+    };
+    stage(0);
+    stage(1);
+    for (int ch = 0; ch < nchunks; ch++) {
+        stage(ch + 2);
+        dense_cp_wait<kDenseStages - 1>();  // chunk ch has landed
         __syncthreads();
         if (npos) {
-            const float* buf = wbuf[ch & 1];
+            const float* wb = dense_smem + (ch % kDenseStages) * kStageFloats;
+            const float* xb = wb + kDenseChunk * MP + (warp * P) * kDenseChunk;
 #pragma unroll
             for (int jj = 0; jj < 4; jj++) {
                 float w[M1];
-                dense_read_weights<M1>(buf, jj * 32 + lane, w);
+                dense_read_weights<M1>(wb, jj * 32 + lane, w);
 #pragma unroll
-                for (int j = 0; j < P; j++)
+                for (int j = 0; j < P; j++) {
+                    const float xv = xb[j * kDenseChunk + jj * 32 + lane];
 #pragma unroll
-                    for (int r = 0; r < M1; r++) acc[j][r] += w[r] * xs[j][jj];
+                    for (int r = 0; r < M1; r++) acc[j][r] += w[r] * xv;
+                }
             }
         }
-        __syncthreads();
+        __syncthreads();  // the stage read here is refilled by the next iteration
     }
     float my_loss = 0.f;
 #pragma unroll

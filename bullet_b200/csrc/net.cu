@@ -376,7 +376,7 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
     b200::DenseArgs da = dense_args(net, s, want_grad);
-    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<s.n_dtiles, 256, 0, net->stream>>>(da));
+    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<s.n_dtiles, 256, b200::dense_fwd_smem<MM>(), net->stream>>>(da));
     LAUNCHED(net);
     return 0;
 }
@@ -532,6 +532,16 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     for (auto& ring : net->tev)
         for (auto& e : ring) cudaEventCreate(&e);
 
+    {
+        constexpr int MM_unused = 0;
+        (void)MM_unused;
+        auto set_dense = [&](int m) -> int {
+            DISPATCH_M(m, cudaFuncSetAttribute(b200::dense_forward_kernel<MM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)b200::dense_fwd_smem<MM>()));
+            return 0;
+        };
+        if (int rc2 = set_dense(d.dense_out[0])) return bail(rc2);
+    }
     if (net->tiled_ok) {
         const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows);
         const int wide = b200::ft_bwd_chunk(d.nnz, true), narrow = b200::ft_bwd_chunk(d.nnz, false);
