@@ -429,3 +429,38 @@ def test_full_size_configs_one_step(oracle32, ci):
             used[idx[idx >= 0]] = True
         assert not g["l0w"].reshape(c.desc.n_inputs, -1)[~used].any()
         net.close()
+
+
+def test_full_size_properties_without_the_oracle():
+    """Properties that need no CPU reference, at the benchmark's network and 2 x 16384 positions:
+    batch-summed gradients and loss are additive over a split of the batch, and repeating a
+    pass from the same state gives the same result (up to the order of floating-point sums)."""
+    from bullet_b200.net import featurise
+
+    c = config(3)
+    n = c.batch
+    desc = dataclasses.replace(c.desc, max_batch=2 * n)
+    rec = synth.records(c.game, 2 * n, seed=91)
+    full = featurise(c.game, rec, desc)
+    halves = [tuple(a[i * n:(i + 1) * n] for a in full) for i in (0, 1)]
+    w = synth.init_weights(desc, seed=91)
+    w["l0f"] = np.random.default_rng(2).normal(0, 0.02, w["l0f"].size).astype(np.float32)
+    net = make_net(desc, 0, w)
+
+    def grads_of(batch):
+        net.upload(0, *batch)
+        net.backward(0)
+        net.update(0.0, 0.0)          # lr = 0: weights untouched, loss read back
+        return net.loss(), net.tensors(3)
+
+    loss_full, g_full = grads_of(full)
+    loss_again, g_again = grads_of(full)
+    (loss_a, g_a), (loss_b, g_b) = grads_of(halves[0]), grads_of(halves[1])
+    assert abs(loss_full - (loss_a + loss_b)) <= 1e-5 * loss_full
+    assert abs(loss_full - loss_again) <= 1e-6 * loss_full
+    for k in g_full:
+        assert rel2(g_a[k] + g_b[k], g_full[k]) <= 1e-5, k
+        assert rel2(g_again[k], g_full[k]) <= 1e-6, k
+    # the weights did not move
+    assert all(np.array_equal(v, w[k]) for k, v in net.tensors(0).items())
+    net.close()
