@@ -264,6 +264,184 @@ __global__ void __launch_bounds__(256, (M1 > 16 ? 1 : 2)) dense_forward_kernel(D
     }
 }
 
+// Register-tiled forward for M1 a multiple of four and two or three dense layers.  Same
+// tiles, staging pipeline and results as dense_forward_kernel, different work split: the M1 x 32
+// block of first-layer outputs of a tile is cut into (four rows) x (M1/4 positions) pieces, one
+// per lane, and the eight warps split each 128-column chunk into 16-column slices.  A lane
+// then reads, per four columns, four 16-byte weight pieces (M1/4 distinct addresses in the
+// warp: a broadcast) and M1/4 16-byte pieces of x (32/(M1/4) distinct addresses, rows padded
+// by four floats so they fall into different banks): one shared-memory wavefront per load
+// instead of four, and no shuffles.  The warps' partial sums meet in shared memory; the small
+// layers, the loss and the way back to the first layer's pre-activation gradient run from
+// shared memory with one warp per position.
+// grid = ntiles, block = 256, dynamic shared memory = dense_fwd_tile_smem<M1>().
+constexpr int kDenseXStride = kDenseChunk + 4;
+template <int M1>
+__host__ __device__ constexpr size_t dense_fwd_tile_smem() {
+    return (size_t)kDenseStages * (kDenseChunk * M1 + kDenseTile * kDenseXStride) * sizeof(float);
+}
+
+template <int M1>
+__global__ void __launch_bounds__(256, 2) dense_forward_tile_kernel(DenseArgs a) {
+    static_assert(M1 % 4 == 0 && M1 <= 32, "four-row pieces");
+    constexpr int RG = M1 / 4;           // row groups = positions per lane
+    constexpr int PG = 32 / RG;          // position groups in a warp
+    constexpr int XS = kDenseXStride;
+    constexpr int kStageFloats = kDenseChunk * M1 + kDenseTile * XS;
+    static_assert(8 * kDenseTile * M1 <= kDenseStages * kStageFloats, "partial sums reuse the stage buffers");
+    extern __shared__ __align__(16) float dense_smem[];
+    __shared__ float s_w2[M1][33], s_b2[32], s_w3[32], s_a1[kDenseTile][M1], s_dz2[8][32], loss_part[8];
+    __shared__ int s_pos[kDenseTile];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rg = lane % RG, pg = lane / RG;
+    const int2 t = a.tiles[blockIdx.x];
+    if (threadIdx.x < kDenseTile) s_pos[threadIdx.x] = a.order[t.x + min((int)threadIdx.x, t.y - 1)];
+    __syncthreads();
+    const int k = a.buckets[s_pos[0]];
+    const int M2 = a.M[1], OM2 = a.O * M2;
+    // the bucket's small-layer weights: needed only after the long loop
+    for (int i = threadIdx.x; i < M1 * M2; i += blockDim.x) s_w2[i / M2][i % M2] = a.W[1][(i / M2) * OM2 + k * M2 + i % M2];
+    if (threadIdx.x < 32) {
+        const bool on = (int)threadIdx.x < M2;
+        s_b2[threadIdx.x] = on ? a.B[1][k * M2 + threadIdx.x] : 0.f;
+        s_w3[threadIdx.x] = on && a.n_dense == 3 ? a.W[2][threadIdx.x * a.O + k] : 0.f;
+    }
+
+    float acc[RG][4];
+#pragma unroll
+    for (int i = 0; i < RG; i++)
+#pragma unroll
+        for (int r = 0; r < 4; r++) acc[i][r] = 0.f;
+    const int nchunks = (a.K1 + kDenseChunk - 1) / kDenseChunk;
+    auto stage = [&](int ch) {
+        if (ch < nchunks) {
+            float* wb = dense_smem + (ch % kDenseStages) * kStageFloats;
+            float* xb = wb + kDenseChunk * M1;
+            const int c_begin = ch * kDenseChunk;
+            const float* src = a.W1g + ((size_t)k * a.K1 + c_begin) * M1;  // 128 columns x M1 rows, contiguous
+            const int wq = min(kDenseChunk, a.K1 - c_begin) * RG;          // 16-byte pieces inside K1
+            for (int i = threadIdx.x; i < kDenseChunk * RG; i += blockDim.x) {
+                if (i < wq)
+                    dense_cp_async16(wb + i * 4, src + i * 4);
+                else
+                    *reinterpret_cast<float4*>(wb + i * 4) = make_float4(0, 0, 0, 0);
+            }
+            for (int i = threadIdx.x; i < kDenseTile * (kDenseChunk / 4); i += blockDim.x) {
+                const int p = i / (kDenseChunk / 4), q = i % (kDenseChunk / 4);
+                const int c = c_begin + q * 4;  // K1 is a multiple of four: a quad is inside or outside
+                float* dst = xb + p * XS + q * 4;
+                if (c < a.K1)
+                    dense_cp_async16(dst, a.x + (size_t)s_pos[p] * a.K1 + c);
+                else
+                    *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
+            }
+        }
+        dense_cp_commit();
+    };
+    stage(0);
+    stage(1);
+    for (int ch = 0; ch < nchunks; ch++) {
+        stage(ch + 2);
+        dense_cp_wait<kDenseStages - 1>();
+        __syncthreads();
+        const float* wb = dense_smem + (ch % kDenseStages) * kStageFloats;
+        const float* xb = wb + kDenseChunk * M1;
+#pragma unroll
+        for (int kq = 0; kq < 4; kq++) {
+            const int c0 = warp * 16 + kq * 4;
+            float4 xv[RG];
+#pragma unroll
+            for (int i = 0; i < RG; i++) xv[i] = *reinterpret_cast<const float4*>(xb + (i * PG + pg) * XS + c0);
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                const float4 wv = *reinterpret_cast<const float4*>(wb + (c0 + kk) * M1 + rg * 4);
+#pragma unroll
+                for (int i = 0; i < RG; i++) {
+                    const float xs = kk == 0 ? xv[i].x : kk == 1 ? xv[i].y : kk == 2 ? xv[i].z : xv[i].w;
+                    acc[i][0] += wv.x * xs;
+                    acc[i][1] += wv.y * xs;
+                    acc[i][2] += wv.z * xs;
+                    acc[i][3] += wv.w * xs;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // partial sums of the eight column slices -> shared memory -> first-layer activations
+    float* red = dense_smem;  // [8][32][M1]; every real cp.async group has been waited for
+#pragma unroll
+    for (int i = 0; i < RG; i++)
+        *reinterpret_cast<float4*>(red + ((warp * kDenseTile) + i * PG + pg) * M1 + rg * 4) =
+            make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    __syncthreads();
+    for (int o = threadIdx.x; o < kDenseTile * M1; o += blockDim.x) {
+        float z = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) z += red[w * kDenseTile * M1 + o];
+        const int p = o / M1, r = o % M1;
+        const float v = act_fwd(a.act[0], z + a.B[0][k * M1 + r]);
+        s_a1[p][r] = v;
+        if (a.want_grad && p < t.y) a.a1[(size_t)s_pos[p] * M1 + r] = v;
+    }
+    __syncthreads();
+
+    float my_loss = 0.f;
+    for (int p = warp; p < t.y; p += 8) {  // warp-uniform
+        const int b = s_pos[p];
+        float z2 = 0.f;
+        if (lane < M2) {
+#pragma unroll
+            for (int c = 0; c < M1; c++) z2 += s_w2[c][lane] * s_a1[p][c];
+            z2 += s_b2[lane];
+        }
+        float o, a2v = 0.f;
+        if (a.n_dense == 2) {
+            o = __shfl_sync(0xffffffffu, z2, 0);
+        } else {
+            a2v = lane < M2 ? act_fwd(a.act[1], z2) : 0.f;
+            o = warp_sum(s_w3[lane] * a2v) + a.B[2][k];
+        }
+        if (lane == 0) a.out[b] = o;
+        if (!a.want_grad) continue;
+
+        const float s = 1.f / (1.f + expf(-o));
+        const float diff = s - a.targets[b];
+        my_loss += diff * diff;
+        const float dout = (diff + diff) * (s * (1.f - s));
+        float dz2;  // gradient at the second layer's pre-activation, lane = row
+        if (a.n_dense == 2) {
+            dz2 = lane == 0 ? dout : 0.f;
+            if (lane == 0) a.dz[1][b] = dout;
+        } else {
+            dz2 = lane < M2 ? (s_w3[lane] * dout) * act_bwd(a.act[1], a2v) : 0.f;
+            if (lane == 0) a.dz[2][b] = dout;
+            if (lane < M2) {
+                a.dz[1][(size_t)b * M2 + lane] = dz2;
+                a.a2[(size_t)b * M2 + lane] = a2v;
+            }
+        }
+        s_dz2[warp][lane] = dz2;
+        __syncwarp();
+        // dz1[c] = (sum_r2 W2[c][r2] * dz2[r2]) * act'(a1[c]); 32/M1 lanes share one c
+        const int c = lane % M1;
+        float sum = 0.f;
+        for (int r2 = lane / M1; r2 < M2; r2 += 32 / M1) sum += s_w2[c][r2] * s_dz2[warp][r2];
+#pragma unroll
+        for (int o2 = M1; o2 < 32; o2 <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+        if (lane < M1) a.dz[0][(size_t)b * M1 + c] = sum * act_bwd(a.act[0], s_a1[p][c]);
+        __syncwarp();
+    }
+    if (a.want_grad) {
+        if (lane == 0) loss_part[warp] = my_loss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.f;
+            for (int w = 0; w < 8; w++) s += loss_part[w];
+            atomicAdd(a.loss, s);
+        }
+    }
+}
+
 // dx[b][c] = sum_r W1[c][k_b][r] * dz1[b][r]   (Matmul::backward, matmul.rs:99-126, on the
 // selected rows).  Same tiling and weight staging as the forward; grid = ntiles, block = 256.
 template <int M1>

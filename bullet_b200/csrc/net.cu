@@ -237,6 +237,33 @@ int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArg
         default: return b200::fail(B200_ERR_UNSUPPORTED, "rows per bucket %d", m); \
     }
 
+// The first dense layer's forward: register-tiled when its rows per bucket come in fours and
+// more layers follow, else the dot-product kernel (single-output networks).
+template <int MM>
+constexpr bool dense_tiled() { return MM % 4 == 0; }
+
+template <int MM>
+void launch_dense_forward(b200_net* net, const b200::DenseArgs& da, int ntiles) {
+    if constexpr (dense_tiled<MM>()) {
+        if (da.n_dense >= 2) {
+            b200::dense_forward_tile_kernel<MM><<<ntiles, 256, b200::dense_fwd_tile_smem<MM>(), net->stream>>>(da);
+            return;
+        }
+    }
+    b200::dense_forward_kernel<MM><<<ntiles, 256, b200::dense_fwd_smem<MM>(), net->stream>>>(da);
+}
+
+template <int MM>
+cudaError_t set_dense_forward_smem() {
+    if constexpr (dense_tiled<MM>()) {
+        cudaError_t e = cudaFuncSetAttribute(b200::dense_forward_tile_kernel<MM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)b200::dense_fwd_tile_smem<MM>());
+        if (e != cudaSuccess) return e;
+    }
+    return cudaFuncSetAttribute(b200::dense_forward_kernel<MM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)b200::dense_fwd_smem<MM>());
+}
+
 // How many near-equal work items an average block is cut into.  One CTA is resident per SM,
 // so the grid runs in waves of kSmCount; more items even out the last wave but repeat the
 // tile's fixed cost (`overhead`, as a fraction of a whole tile's work: the tile load in the
@@ -376,7 +403,7 @@ int forward_part(b200_net* net, Slot& s, bool want_grad) {
     if (rc) return rc;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
     b200::DenseArgs da = dense_args(net, s, want_grad);
-    DISPATCH_M(d.dense_out[0], b200::dense_forward_kernel<MM><<<s.n_dtiles, 256, b200::dense_fwd_smem<MM>(), net->stream>>>(da));
+    DISPATCH_M(d.dense_out[0], launch_dense_forward<MM>(net, da, s.n_dtiles));
     LAUNCHED(net);
     return 0;
 }
@@ -536,8 +563,9 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         constexpr int MM_unused = 0;
         (void)MM_unused;
         auto set_dense = [&](int m) -> int {
-            DISPATCH_M(m, cudaFuncSetAttribute(b200::dense_forward_kernel<MM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)b200::dense_fwd_smem<MM>()));
+            cudaError_t e = cudaSuccess;
+            DISPATCH_M(m, e = set_dense_forward_smem<MM>());
+            if (e != cudaSuccess) return b200::fail(B200_ERR_CUDA, "dense forward shared memory: %s", cudaGetErrorString(e));
             return 0;
         };
         if (int rc2 = set_dense(d.dense_out[0])) return bail(rc2);
