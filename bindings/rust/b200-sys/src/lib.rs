@@ -20,6 +20,11 @@ pub const B200_KIND_MOMENTUM: c_int = 1;
 pub const B200_KIND_VELOCITY: c_int = 2;
 pub const B200_KIND_GRAD: c_int = 3;
 
+pub const B200_QUANT_FLOAT: i32 = 0;
+pub const B200_QUANT_I8: i32 = 1;
+pub const B200_QUANT_I16: i32 = 2;
+pub const B200_QUANT_I32: i32 = 3;
+
 pub const B200_NUM_SLOTS: c_int = 3;
 pub const B200_OP_NOALLOC_MAX_POSITIONS: i32 = 16384;
 
@@ -86,6 +91,22 @@ pub struct b200_ft_op {
     pub u: *mut f32,
 }
 
+/// One entry of an export in the reference's `SavedFormat` scheme
+/// (crates/trainer/src/model/weights.rs:183-335): custom bytes when `id` is null, else a weight
+/// with the built-in transforms and a quantisation target.
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct b200_saved_format {
+    pub id: *const c_char,
+    pub custom: *const c_void,
+    pub custom_len: i64,
+    pub quant: i32,
+    pub multiplier: i32,
+    pub round: i32,
+    pub transpose: i32,
+    pub merge_factoriser: i32,
+}
+
 extern "C" {
     pub fn b200_last_error() -> *const c_char;
     pub fn b200_version() -> c_int;
@@ -129,6 +150,22 @@ extern "C" {
 
     pub fn b200_checkpoint_save(net: *mut b200_net, dir: *const c_char) -> c_int;
     pub fn b200_checkpoint_load(net: *mut b200_net, dir: *const c_char) -> c_int;
+
+    pub fn b200_net_tensor_shape(net: *mut b200_net, name: *const c_char, rows: *mut i64, cols: *mut i64) -> c_int;
+    pub fn b200_quant_size(quant: i32) -> i64;
+    pub fn b200_quantise(values: *const f32, n: i64, quant: i32, multiplier: i32, round: i32, out: *mut c_void) -> c_int;
+    pub fn b200_transpose(input: *const f32, rows: i64, cols: i64, out: *mut f32) -> c_int;
+    pub fn b200_saved_format_size(net: *mut b200_net, fmt: *const b200_saved_format, n_fmt: i32, pad: i32, bytes: *mut i64) -> c_int;
+    pub fn b200_saved_format_write(
+        net: *mut b200_net,
+        fmt: *const b200_saved_format,
+        n_fmt: i32,
+        pad: i32,
+        out: *mut c_void,
+        out_bytes: i64,
+    ) -> c_int;
+    pub fn b200_save_quantised(net: *mut b200_net, fmt: *const b200_saved_format, n_fmt: i32, path: *const c_char) -> c_int;
+    pub fn b200_save_unquantised(net: *mut b200_net, fmt: *const b200_saved_format, n_fmt: i32, path: *const c_char) -> c_int;
 
     pub fn b200_op_ft_forward(device: c_int, stream: *mut c_void, op: *const b200_ft_op) -> c_int;
     pub fn b200_op_ft_forward_noalloc(device: c_int, stream: *mut c_void, op: *const b200_ft_op) -> c_int;

@@ -13,4 +13,8 @@ def __getattr__(name):
         from . import _lib, net
 
         return getattr(net, name) if hasattr(net, name) else getattr(_lib, name)
+    if name == "SavedFormat":
+        from .saved_format import SavedFormat
+
+        return SavedFormat
     raise AttributeError(name)

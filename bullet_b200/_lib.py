@@ -19,6 +19,8 @@ SYMBOLS = (
     "b200_pack_indices_u16", "b200_unpack_indices_u16", "b200_net_get_stat", "b200_op_ft_forward", "b200_op_ft_forward_noalloc",
     "b200_backward_begin", "b200_backward_ft", "b200_backward_end", "b200_grad_part", "b200_update_range",
     "b200_update_end", "b200_loss_of", "b200_checkpoint_save", "b200_checkpoint_load", "b200_flat_buffer",
+    "b200_net_tensor_shape", "b200_quant_size", "b200_quantise", "b200_transpose", "b200_saved_format_size",
+    "b200_saved_format_write", "b200_save_quantised", "b200_save_unquantised",
 )
 
 
@@ -31,6 +33,13 @@ class CFtOp(ctypes.Structure):
 
     _fields_ = [(n, ctypes.c_int32) for n in ("n_inputs", "nnz", "ft_out", "ft_act", "pairwise", "ft_block_rows", "n")] + \
                [(n, ctypes.c_void_p) for n in ("table", "bias", "idx_stm", "idx_nstm", "x", "u")]
+
+
+class CSavedFormat(ctypes.Structure):
+    """b200_saved_format: one entry of an export (custom bytes, or a weight with transforms and a quantisation)."""
+
+    _fields_ = [("id", ctypes.c_char_p), ("custom", ctypes.c_void_p), ("custom_len", ctypes.c_int64)] + \
+               [(n, ctypes.c_int32) for n in ("quant", "multiplier", "round", "transpose", "merge_factoriser")]
 
 
 class CTimings(ctypes.Structure):
@@ -89,6 +98,13 @@ def load() -> ctypes.CDLL:
         "b200_sync": [vp],
         "b200_checkpoint_save": [vp, cp],
         "b200_checkpoint_load": [vp, cp],
+        "b200_net_tensor_shape": [vp, cp, ctypes.POINTER(i64), ctypes.POINTER(i64)],
+        "b200_quantise": [vp, i64, i32, i32, i32, vp],
+        "b200_transpose": [vp, i64, i64, vp],
+        "b200_saved_format_size": [vp, ctypes.POINTER(CSavedFormat), i32, i32, ctypes.POINTER(i64)],
+        "b200_saved_format_write": [vp, ctypes.POINTER(CSavedFormat), i32, i32, vp, i64],
+        "b200_save_quantised": [vp, ctypes.POINTER(CSavedFormat), i32, cp],
+        "b200_save_unquantised": [vp, ctypes.POINTER(CSavedFormat), i32, cp],
         "b200_get_timings": [vp, ctypes.POINTER(CTimings)],
         "b200_net_get_activation": [vp, ctypes.c_int, vp, i64],
         "b200_net_get_stat": [vp, cp, ctypes.POINTER(i64)],
@@ -106,6 +122,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = ctypes.c_int
+    lib.b200_quant_size.argtypes = [i32]
+    lib.b200_quant_size.restype = i64
     _lib = lib
     return lib
 

@@ -55,6 +55,7 @@ constexpr int kMinItemPairs = 128;         // a forward work item serves at leas
 struct Tensor {
     std::string name;
     int64_t n = 0, off = 0;
+    int64_t rows = 0, cols = 0;  // column-major shape, as the reference's Shape(rows, cols)
     b200_adamw_params hp{0.01f, 0.9f, 0.999f, -1.98f, 1.98f};
 };
 
@@ -469,23 +470,25 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the copy stream"));
 
     // flat layout, tensors in name order
-    auto add = [&](const char* name, int64_t n) {
+    auto add = [&](const char* name, int64_t rows, int64_t cols) {
         Tensor t;
         t.name = name;
-        t.n = n;
+        t.rows = rows;
+        t.cols = cols;
+        t.n = rows * cols;
         net->tensors.push_back(t);
     };
-    add("l0b", d.ft_out);
-    if (d.factoriser_rows) add("l0f", (int64_t)d.factoriser_rows * d.ft_out);
+    add("l0b", d.ft_out, 1);
+    if (d.factoriser_rows) add("l0f", d.ft_out, d.factoriser_rows);
     for (int l = 0; l < d.n_dense; l++) {
         char name[8];
         const int64_t rows = (int64_t)d.n_out_buckets * d.dense_out[l];
         snprintf(name, sizeof name, "l%db", l + 1);
-        add(name, rows);
+        add(name, rows, 1);
         snprintf(name, sizeof name, "l%dw", l + 1);
-        add(name, rows * net->dense_in(l));
+        add(name, rows, net->dense_in(l));
     }
-    add("l0w", (int64_t)d.n_inputs * d.ft_out);  // last, so that everything else is one contiguous head
+    add("l0w", d.ft_out, d.n_inputs);  // last, so that everything else is one contiguous head
     int64_t off = kAlignFloats;                  // float 0 of G is the loss
     for (auto& t : net->tensors) {
         t.off = off;
@@ -638,6 +641,15 @@ int b200_net_tensor_size(b200_net* net, const char* name, int64_t* n) {
     const Tensor* t = net->find(name);
     if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
     *n = t->n;
+    return 0;
+}
+
+int b200_net_tensor_shape(b200_net* net, const char* name, int64_t* rows, int64_t* cols) {
+    if (!net || !name || !rows || !cols) return b200::fail(B200_ERR_ARG, "tensor_shape: null argument");
+    const Tensor* t = net->find(name);
+    if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    *rows = t->rows;
+    *cols = t->cols;
     return 0;
 }
 

@@ -132,6 +132,48 @@ class Net:
     def load_checkpoint(self, directory: str) -> None:
         _lib.check(self.lib.b200_checkpoint_load(self._h, directory.encode()))
 
+    def tensor_shape(self, name: str):
+        """(rows, cols) of a weight, column-major as the reference's Shape."""
+        r, c = ctypes.c_int64(), ctypes.c_int64()
+        _lib.check(self.lib.b200_net_tensor_shape(self._h, name.encode(), ctypes.byref(r), ctypes.byref(c)))
+        return r.value, c.value
+
+    def to_quantised_buffer(self, formats, pad: bool = True) -> bytes:
+        """ModelWeights::to_quantised_buffer (crates/trainer/src/model/weights.rs:158-177)."""
+        from .saved_format import c_formats
+
+        arr, keep = c_formats(formats)
+        size = ctypes.c_int64()
+        _lib.check(self.lib.b200_saved_format_size(self._h, arr, len(formats), int(pad), ctypes.byref(size)))
+        out = ctypes.create_string_buffer(max(1, size.value))
+        _lib.check(self.lib.b200_saved_format_write(self._h, arr, len(formats), int(pad), out, size.value))
+        del keep
+        return out.raw[:size.value]
+
+    def save_quantised(self, path: str, formats) -> None:
+        from .saved_format import c_formats
+
+        arr, keep = c_formats(formats)
+        _lib.check(self.lib.b200_save_quantised(self._h, arr, len(formats), path.encode()))
+        del keep
+
+    def save_unquantised(self, path: str, formats) -> None:
+        from .saved_format import c_formats
+
+        arr, keep = c_formats(formats)
+        _lib.check(self.lib.b200_save_unquantised(self._h, arr, len(formats), path.encode()))
+        del keep
+
+    def save_to_checkpoint(self, path: str, formats) -> None:
+        """`path`/optimiser_state/{weights,momentum,velocity}.bin, raw.bin and quantised.bin
+        (crates/bullet_lib/src/value/save.rs:24-43)."""
+        import os
+
+        os.makedirs(os.path.join(path, "optimiser_state"), exist_ok=True)
+        self.save_checkpoint(os.path.join(path, "optimiser_state"))
+        self.save_unquantised(os.path.join(path, "raw.bin"), formats)
+        self.save_quantised(os.path.join(path, "quantised.bin"), formats)
+
     def sync(self) -> None:
         _lib.check(self.lib.b200_sync(self._h))
 

@@ -184,6 +184,44 @@ int b200_net_get_activation(b200_net* net, int which, float* host, int64_t n);
 int b200_checkpoint_save(b200_net* net, const char* dir);
 int b200_checkpoint_load(b200_net* net, const char* dir);
 
+/* ---- network export in the reference's SavedFormat scheme
+ * (crates/trainer/src/model/weights.rs:183-335; ModelWeights::to_quantised_buffer weights.rs:158-177;
+ * save_quantised / save_unquantised crates/bullet_lib/src/value/save.rs:45-88).
+ * One entry is custom bytes (id == NULL) or a weight id whose values pass, in this order, through
+ * the optional factoriser merge (the transform of examples/progression/3_input_buckets.rs:46-53:
+ * value + l0f repeated over the input buckets), the optional transpose (weights.rs:254-269, using
+ * the weight's column-major shape) and quantisation: round-half-away-from-zero or truncation of
+ * f64(multiplier) * f64(value), stored little-endian.  A value that does not fit its target type
+ * fails the export with B200_ERR_DATA ("Failed quantisation from f32 to i16!"); nothing is clamped. */
+#define B200_QUANT_FLOAT 0
+#define B200_QUANT_I8 1
+#define B200_QUANT_I16 2
+#define B200_QUANT_I32 3
+typedef struct b200_saved_format {
+    const char* id;           /* weight to write, or NULL for custom bytes                        */
+    const void* custom;       /* id == NULL: bytes copied as they are (header, padding, ...)      */
+    int64_t custom_len;
+    int32_t quant;            /* B200_QUANT_*                                                     */
+    int32_t multiplier;       /* i16 range for the i8 and i16 targets, as in the reference        */
+    int32_t round;            /* 1: round half away from zero; 0: truncate                        */
+    int32_t transpose;        /* 1: write the transposed matrix                                   */
+    int32_t merge_factoriser; /* 1: add l0f, repeated over the input buckets, before the rest     */
+} b200_saved_format;
+/* Shape(rows, cols) of a weight, column-major as in the reference (l0w: ft_out x n_inputs). */
+int b200_net_tensor_shape(b200_net* net, const char* name, int64_t* rows, int64_t* cols);
+/* QuantTarget::quantise (weights.rs:281-331) on host values; `out` holds n * b200_quant_size(quant) bytes. */
+int64_t b200_quant_size(int32_t quant);
+int b200_quantise(const float* values, int64_t n, int32_t quant, int32_t multiplier, int32_t round, void* out);
+/* SavedFormat::transpose_impl (weights.rs:254-269): out[cols * i + j] = in[rows * j + i]. */
+int b200_transpose(const float* in, int64_t rows, int64_t cols, float* out);
+/* to_quantised_buffer: size of, and the bytes of, the concatenated entries; `pad` pads to 64 bytes. */
+int b200_saved_format_size(b200_net* net, const b200_saved_format* fmt, int32_t n_fmt, int32_t pad, int64_t* bytes);
+int b200_saved_format_write(b200_net* net, const b200_saved_format* fmt, int32_t n_fmt, int32_t pad, void* out, int64_t out_bytes);
+/* save_quantised (padded) and save_unquantised (the named weights as raw f32, no transforms) to a file;
+ * in the reference these are `<checkpoint>/quantised.bin` and `<checkpoint>/raw.bin`. */
+int b200_save_quantised(b200_net* net, const b200_saved_format* fmt, int32_t n_fmt, const char* path);
+int b200_save_unquantised(b200_net* net, const b200_saved_format* fmt, int32_t n_fmt, const char* path);
+
 /* ---- operator level: the feature-transformer forward on caller-owned DEVICE memory, without a
  * b200_net.  For both perspectives of n positions: the sparse affine of SparseMatmul::evaluate
  * (crates/compiler/src/tensor/operation/linear/sparse.rs:86-119), the bias

@@ -13,10 +13,13 @@
 // error that says what it did not recognise; nothing is ever silently trained differently.
 #pragma once
 #include <cstdint>
+#include <cstdio>
+#include <functional>
 #include <map>
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "bullet_b200.h"
@@ -305,6 +308,116 @@ inline RecognisedNet recognise(const ModelNode& output, int ft_block_rows, int m
 }
 
 // ------------------------------------------------------------------ trainer handle
+// ---- network export: crates/trainer/src/model/weights.rs:183-335 (SavedFormat, QuantTarget)
+// A read-only view of the trained weights that transforms receive, as `&ModelWeights` in the reference.
+struct WeightStore {
+    struct Entry {
+        std::vector<float> values;
+        Shape shape;
+    };
+    std::map<std::string, Entry> stores;
+    const Entry& get(const std::string& id) const {
+        auto it = stores.find(id);
+        if (it == stores.end()) throw std::runtime_error("no weight with id '" + id + "'");
+        return it->second;
+    }
+};
+
+class SavedFormat {
+   public:
+    using Transform = std::function<std::vector<float>(const WeightStore&, std::vector<float>)>;
+
+    // custom bytes: a network header, padding, ...
+    static SavedFormat custom(std::vector<uint8_t> bytes) {
+        SavedFormat f;
+        f.custom_ = std::move(bytes);
+        f.is_custom_ = true;
+        return f;
+    }
+    // starts from the values of weight `id`
+    static SavedFormat id(const std::string& id) {
+        SavedFormat f;
+        f.id_ = id;
+        f.has_id_ = true;
+        return f.transform([id](const WeightStore& store, std::vector<float>) { return store.get(id).values; });
+    }
+    // starts from nothing: for formats that interleave several weights in a transform
+    static SavedFormat empty() { return SavedFormat(); }
+
+    // if quantising, round rather than truncate
+    SavedFormat round() const {
+        SavedFormat f(*this);
+        f.no_custom();
+        f.round_flag_ = true;
+        return f;
+    }
+    template <typename T>
+    SavedFormat quantise(int32_t multiplier) const {
+        static_assert(std::is_same<T, int8_t>::value || std::is_same<T, int16_t>::value || std::is_same<T, int32_t>::value,
+                      "quantise<int8_t | int16_t | int32_t>");
+        SavedFormat f(*this);
+        f.no_custom();
+        f.quant_ = std::is_same<T, int8_t>::value ? B200_QUANT_I8 : std::is_same<T, int16_t>::value ? B200_QUANT_I16 : B200_QUANT_I32;
+        f.multiplier_ = multiplier;
+        return f;
+    }
+    // transposes the current values using the shape of this format's weight
+    SavedFormat transpose() const {
+        if (!has_id_) throw std::logic_error("SavedFormat::transpose needs a weight id");
+        const std::string id = id_;
+        return transform([id](const WeightStore& store, std::vector<float> w) {
+            const Shape sh = store.get(id).shape;
+            std::vector<float> out(w.size());
+            if (b200_transpose(w.data(), (int64_t)sh.rows, (int64_t)sh.cols, out.data()) < 0) throw std::runtime_error(b200_last_error());
+            return out;
+        });
+    }
+    SavedFormat transform(Transform f) const {
+        SavedFormat g(*this);
+        g.no_custom();
+        g.transforms_.push_back(std::move(f));
+        return g;
+    }
+    bool has_id() const { return has_id_; }
+    const std::string& get_id() const { return id_; }
+
+    // SavedFormat::write_to_byte_buffer: transforms in order, then quantisation
+    std::vector<uint8_t> write_to_byte_buffer(const WeightStore& store) const {
+        if (is_custom_) return custom_;
+        std::vector<float> w;
+        for (const auto& t : transforms_) w = t(store, std::move(w));
+        std::vector<uint8_t> out(w.size() * (size_t)b200_quant_size(quant_));
+        if (b200_quantise(w.data(), (int64_t)w.size(), quant_, multiplier_, round_flag_ ? 1 : 0, out.data()) < 0)
+            throw std::runtime_error(b200_last_error());
+        return out;
+    }
+
+   private:
+    void no_custom() const {
+        if (is_custom_) throw std::logic_error("custom bytes take no transform or quantisation");
+    }
+    bool is_custom_ = false, has_id_ = false, round_flag_ = false;
+    std::vector<uint8_t> custom_;
+    std::string id_;
+    int32_t quant_ = B200_QUANT_FLOAT, multiplier_ = 1;
+    std::vector<Transform> transforms_;
+};
+
+// ModelWeights::to_quantised_buffer (weights.rs:158-177)
+inline std::vector<uint8_t> to_quantised_buffer(const WeightStore& store, const std::vector<SavedFormat>& format, bool pad) {
+    std::vector<uint8_t> buf;
+    for (const auto& f : format) {
+        const auto part = f.write_to_byte_buffer(store);
+        buf.insert(buf.end(), part.begin(), part.end());
+    }
+    if (pad && buf.size() % 64) {
+        static const char chs[6] = {'b', 'u', 'l', 'l', 'e', 't'};
+        const size_t extra = 64 - buf.size() % 64;
+        for (size_t i = 0; i < extra; i++) buf.push_back((uint8_t)chs[i % 6]);
+    }
+    return buf;
+}
+
 class Trainer {
    public:
     Trainer(const RecognisedNet& net, int device = 0) : ids_(net.weight_ids) {
@@ -346,12 +459,45 @@ class Trainer {
         check(b200_forward(h_, slot, out.data()));
         return out;
     }
+    // the trained weights on the host, under the ids of the graph (Optimiser::cpu_weights)
+    WeightStore cpu_weights() {
+        WeightStore store;
+        for (const auto& id : ids_) {
+            WeightStore::Entry e;
+            e.values = weights(id);
+            int64_t rows = 0, cols = 0;
+            check(b200_net_tensor_shape(h_, abi(id), &rows, &cols));
+            e.shape = Shape{(int)rows, (int)cols};
+            store.stores[id] = std::move(e);
+        }
+        return store;
+    }
+    // crates/bullet_lib/src/value/save.rs:45-88
+    void save_quantised(const std::string& path, const std::vector<SavedFormat>& format) {
+        write_file(path, to_quantised_buffer(cpu_weights(), format, true));
+    }
+    void save_unquantised(const std::string& path, const std::vector<SavedFormat>& format) {
+        std::vector<uint8_t> buf;
+        for (const auto& f : format)
+            if (f.has_id()) {
+                const auto v = weights(f.get_id());
+                const uint8_t* p = reinterpret_cast<const uint8_t*>(v.data());
+                buf.insert(buf.end(), p, p + v.size() * sizeof(float));
+            }
+        write_file(path, buf);
+    }
     const std::vector<std::string>& weight_ids() const { return ids_; }
     b200_net* handle() { return h_; }
 
    private:
     static void check(int rc) {
         if (rc < 0) throw std::runtime_error(std::string("bullet_b200 error ") + std::to_string(rc) + ": " + b200_last_error());
+    }
+    static void write_file(const std::string& path, const std::vector<uint8_t>& bytes) {
+        FILE* f = std::fopen(path.c_str(), "wb");
+        if (!f) throw std::runtime_error("cannot create " + path);
+        const bool ok = bytes.empty() || std::fwrite(bytes.data(), 1, bytes.size(), f) == bytes.size();
+        if (std::fclose(f) != 0 || !ok) throw std::runtime_error("short write to " + path);
     }
     const char* abi(const std::string& id) const {
         auto it = abi_.find(id);

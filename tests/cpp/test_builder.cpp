@@ -98,6 +98,46 @@ int main(int argc, char** argv) {
                        "same input"));
         EXPECT(refused([&] { l0.weights.matmul(b.sparse_input("bad", 5, 1)); }, "inner dimensions"));
     }
+    {   // SavedFormat on a hand-made store: transforms in order, quantisation last (weights.rs:183-335)
+        WeightStore store;
+        store.stores["w"] = {{0.5f, -0.5f, 0.25f, 1.0f, -1.0f, 0.1f}, Shape(2, 3)};  // column-major 2 x 3
+        store.stores["f"] = {{0.25f, 0.25f}, Shape(2, 1)};
+        const auto merged = SavedFormat::id("w")
+                                .transform([](const WeightStore& st, std::vector<float> w) {
+                                    const auto& f = st.get("f").values;
+                                    for (size_t i = 0; i < w.size(); i++) w[i] += f[i % f.size()];
+                                    return w;
+                                })
+                                .round()
+                                .quantise<int16_t>(2);
+        // (w + f) * 2 = 1.5, -0.5, 1, 2.5, -1.5, 0.7 -> half away from zero
+        const auto mb = merged.write_to_byte_buffer(store);
+        const int16_t want_m[6] = {2, -1, 1, 3, -2, 1};
+        EXPECT(mb.size() == 12 && !std::memcmp(mb.data(), want_m, 12));
+        const auto tb = SavedFormat::id("w").quantise<int8_t>(4).transpose().write_to_byte_buffer(store);
+        const int8_t want_t[6] = {2, 1, -4, -2, 4, 0};  // rows (0.5, 0.25, -1), (-0.5, 1, 0.1) x 4, truncated
+        EXPECT(tb.size() == 6 && !std::memcmp(tb.data(), want_t, 6));
+        const auto all = to_quantised_buffer(store, {SavedFormat::custom({'h', 'd'}), merged, SavedFormat::id("f")}, true);
+        EXPECT(all.size() == 64 && all[0] == 'h' && all[14] == 0 && all[17] == 0x3e);  // 2 + 12 + 8 bytes, then padding
+        EXPECT(!std::memcmp(all.data() + 22, "bulletbulletbulletbulletbulletbulletbullet", 42));
+        auto misuse = [](const std::function<void()>& f, const char* needle) {
+            try {
+                f();
+            } catch (const std::logic_error& e) {
+                return std::strstr(e.what(), needle) != nullptr;
+            }
+            return false;
+        };
+        EXPECT(misuse([] { SavedFormat::custom({1}).round(); }, "custom"));
+        EXPECT(misuse([] { SavedFormat::empty().transpose(); }, "weight id"));
+        bool overflow = false;
+        try {
+            SavedFormat::id("w").quantise<int8_t>(200).write_to_byte_buffer(store);
+        } catch (const std::runtime_error& e) {
+            overflow = std::strstr(e.what(), "Failed quantisation from f32 to i8!") != nullptr;
+        }
+        EXPECT(overflow);
+    }
     if (argc > 1 && !std::strcmp(argv[1], "gpu")) {
         // one training step of a small bucketed pairwise net on a fixed pseudo-random batch
         const int B = 256, H = 128, NNZ = 32;
@@ -136,6 +176,32 @@ int main(int argc, char** argv) {
         const std::vector<float> outs = t.eval(1, B);
         std::printf("loss %.9g %.9g out0 %.9g\n", first, second, outs[0]);
         EXPECT(std::isfinite(first) && second < first);
+        {   // export: the example's closure (3_input_buckets.rs:46-53) against the library's built-in merge
+            const std::vector<SavedFormat> fmt = {
+                SavedFormat::id("l0w")
+                    .transform([](const WeightStore& st, std::vector<float> w) {
+                        const auto& f = st.get("l0f").values;
+                        for (size_t i = 0; i < w.size(); i++) w[i] = w[i] + f[i % f.size()];
+                        return w;
+                    })
+                    .round()
+                    .quantise<int16_t>(255),
+                SavedFormat::id("l0b").round().quantise<int16_t>(255),
+                SavedFormat::id("l1w").transpose().round().quantise<int8_t>(64),
+                SavedFormat::id("l1b"),
+            };
+            const auto ours = to_quantised_buffer(t.cpu_weights(), fmt, true);
+            b200_saved_format c[4] = {};
+            c[0].id = "l0w", c[0].quant = B200_QUANT_I16, c[0].multiplier = 255, c[0].round = 1, c[0].merge_factoriser = 1;
+            c[1].id = "l0b", c[1].quant = B200_QUANT_I16, c[1].multiplier = 255, c[1].round = 1;
+            c[2].id = "l1w", c[2].quant = B200_QUANT_I8, c[2].multiplier = 64, c[2].round = 1, c[2].transpose = 1;
+            c[3].id = "l1b";
+            int64_t bytes = 0;
+            EXPECT(b200_saved_format_size(t.handle(), c, 4, 1, &bytes) == 0 && bytes == (int64_t)ours.size() && bytes % 64 == 0);
+            std::vector<uint8_t> lib((size_t)bytes);
+            EXPECT(b200_saved_format_write(t.handle(), c, 4, 1, lib.data(), bytes) == 0 && lib == ours);
+            EXPECT(b200_saved_format_write(t.handle(), c, 4, 1, lib.data(), bytes - 1) == B200_ERR_ARG);
+        }
         bool threw = false;
         try {
             t.weights("nope");

@@ -19,7 +19,7 @@ def test_rust_declarations_cover_the_header():
     declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
     bound = set(re.findall(r"pub fn (b200_[a-z0-9_]+)\s*\(", rust))
     assert declared == bound
-    for struct in ("b200_net_desc", "b200_adamw_params", "b200_timings", "b200_ft_op"):
+    for struct in ("b200_net_desc", "b200_adamw_params", "b200_timings", "b200_ft_op", "b200_saved_format"):
         assert f"pub struct {struct}" in rust
 
 
