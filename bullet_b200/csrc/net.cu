@@ -93,6 +93,7 @@ struct b200_net {
     float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr, *w1g = nullptr;
     float* dz[3] = {nullptr, nullptr, nullptr};
     int* status = nullptr;
+    int wgrad_per_sm = 0;          // resident CTAs per SM of the first layer's weight-gradient kernel (looked up once)
     uint16_t* ft_lists = nullptr;  // prepared per-pair row lists of the tiled kernels
     int* ft_list_count = nullptr;
     uint16_t* csr_ent = nullptr;                        // per-chunk row-major lists of the tiled backward
@@ -427,8 +428,17 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
     const int groups = w.K / 4 + 1;  // four columns per thread, plus the bias
     const int threads = groups >= 128 ? 128 : ((groups + 31) / 32) * 32;
     const int gx = (groups + threads - 1) / threads;
-    int chunks = std::max(1, std::min((s.n + 63) / 64, 8 * kSmCount / gx));  // 128-thread CTAs, several per SM
-    w.chunk_len = ((s.n + chunks - 1) / chunks + 63) / 64 * 64;
+    // The grid should fill the CTA slots the device offers exactly once or twice: a few CTAs
+    // left over for another wave would double the kernel's time.
+    if (!net->wgrad_per_sm) {
+        int per_sm = 0;
+        DISPATCH_M(d.dense_out[layer], cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, b200::dense_wgrad_kernel<MM>, threads, 0));
+        net->wgrad_per_sm = std::max(1, per_sm);
+    }
+    const int slots = net->wgrad_per_sm * kSmCount;
+    const int waves = s.n >= 65536 ? 2 : 1;
+    int chunks = std::max(1, std::min((s.n + 31) / 32, waves * slots / gx));
+    w.chunk_len = (s.n + chunks - 1) / chunks;
     chunks = (s.n + w.chunk_len - 1) / w.chunk_len;
     dim3 grid(gx, chunks);
     DISPATCH_M(d.dense_out[layer], b200::dense_wgrad_kernel<MM><<<grid, threads, 0, net->stream>>>(w));
