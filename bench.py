@@ -212,7 +212,9 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = True  # collectives that run beside kernels get their SMs first
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
     cfg = config(4)
     if GLOBAL_BATCH % world:
         raise SystemExit("the global batch must divide evenly over the ranks")
@@ -238,7 +240,9 @@ def run_ours(args, rank, world, local_rank):
     net.load_weights(synth.init_weights(desc, seed=cfg.seed))
     parts = args.dp_parts if (world > 1 and net.stat("ft_tiled") & 2) else 1
     shard = bool(args.dp_shard) and world > 1
-    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts, shard_optimiser=shard)
+    peer = bool(args.dp_peer) and world > 1
+    dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts, shard_optimiser=shard,
+                          peer_exchange=peer)
     lr = cfg.lr
 
     def barrier():
@@ -277,6 +281,7 @@ def run_ours(args, rank, world, local_rank):
         ev0.record(stream)
         for i in range(args.steps):
             one_step(i % N_DISTINCT)
+        dp.finish()  # weight gathers still in flight belong to the timed steps
         ev1.record(stream)
         barrier()
         dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
@@ -303,6 +308,7 @@ def run_ours(args, rank, world, local_rank):
             if i:
                 last_loss = net.loss(steps_back=1)                       # D2H read of the previous step's loss
         last_loss = net.loss()                                           # ... and of the last step's
+        dp.finish()
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         h2d_per_step = (net.stat("h2d_bytes") - h2d0) // max(args.steps, 1)
@@ -345,8 +351,13 @@ def run_ours(args, rank, world, local_rank):
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
-                   "parallelism": f"dp{world}", "exchange": ("reduce-scatter + sharded AdamW + all-gather" if shard else
-                                                         f"all-reduce in {parts + 1} pipelined parts" if parts > 1 else "one all-reduce"), "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
+                   "parallelism": f"dp{world}",
+                   "exchange": ("one kernel over peer memory: peer loads of all gradients, AdamW on 1/N, peer stores of the weights"
+                                if peer else
+                                f"reduce-scatter + sharded AdamW + all-gather in {parts} slices, gathers under the next forward"
+                                if shard and parts > 1 else "reduce-scatter + sharded AdamW + all-gather" if shard else
+                                f"all-reduce in {parts + 1} pipelined parts" if parts > 1 else "one all-reduce"),
+                   "ft_kernels": {"forward": "tiled" if net.stat("ft_tiled") & 1 else "gather",
                                   "backward": "tiled" if net.stat("ft_tiled") & 2 else "gather"},
                    "l2": f"inputs larger than L2: {N_DISTINCT} distinct batches cycled, per-step activations "
                          f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
@@ -377,8 +388,10 @@ def main():
     ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads, one CTA per SM")
     ap.add_argument("--dp-shard", type=int, default=1,
                     help="N > 1: 1 = reduce-scatter, AdamW on 1/N of the parameters per rank, all-gather; 0 = all-reduce")
+    ap.add_argument("--dp-peer", type=int, default=0,
+                    help="N > 1: 1 = the exchange as one library kernel over peer memory (reduce + AdamW + gather)")
     ap.add_argument("--dp-parts", type=int, default=1,
-                    help="N > 1: slices of the l0w gradient all-reduced while the backward still runs (1 = one all-reduce)")
+                    help="N > 1: slices of l0w exchanged while the backward (and, with --dp-shard 1, the next forward) still runs")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,

@@ -26,6 +26,7 @@ pub const B200_QUANT_I16: i32 = 2;
 pub const B200_QUANT_I32: i32 = 3;
 
 pub const B200_NUM_SLOTS: c_int = 3;
+pub const B200_IPC_HANDLE_BYTES: usize = 64;
 pub const B200_OP_NOALLOC_MAX_POSITIONS: i32 = 16384;
 
 #[repr(C)]
@@ -133,6 +134,12 @@ extern "C" {
     pub fn b200_backward(net: *mut b200_net, slot: c_int) -> c_int;
     pub fn b200_update(net: *mut b200_net, lr: f32, grad_factor: f32) -> c_int;
     pub fn b200_grad_buffer(net: *mut b200_net, device_ptr: *mut *mut c_void, n_floats: *mut i64) -> c_int;
+    pub fn b200_forward_begin(net: *mut b200_net, slot: c_int) -> c_int;
+    pub fn b200_forward_ft(net: *mut b200_net, slot: c_int, part: c_int, n_parts: c_int) -> c_int;
+    pub fn b200_net_tensor_offset(net: *mut b200_net, name: *const c_char, first_float: *mut i64) -> c_int;
+    pub fn b200_exchange_export(net: *mut b200_net, handles: *mut c_void, bytes: i64) -> c_int;
+    pub fn b200_exchange_import(net: *mut b200_net, rank: c_int, world: c_int, handles: *const c_void, bytes: i64) -> c_int;
+    pub fn b200_update_exchange(net: *mut b200_net, lr: f32, grad_factor: f32) -> c_int;
     pub fn b200_backward_begin(net: *mut b200_net, slot: c_int) -> c_int;
     pub fn b200_backward_ft(net: *mut b200_net, slot: c_int, part: c_int, n_parts: c_int) -> c_int;
     pub fn b200_backward_end(net: *mut b200_net, slot: c_int) -> c_int;

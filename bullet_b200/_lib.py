@@ -21,6 +21,8 @@ SYMBOLS = (
     "b200_update_end", "b200_loss_of", "b200_checkpoint_save", "b200_checkpoint_load", "b200_flat_buffer",
     "b200_net_tensor_shape", "b200_quant_size", "b200_quantise", "b200_transpose", "b200_saved_format_size",
     "b200_saved_format_write", "b200_save_quantised", "b200_save_unquantised",
+    "b200_forward_begin", "b200_forward_ft", "b200_net_tensor_offset",
+    "b200_exchange_export", "b200_exchange_import", "b200_update_exchange",
 )
 
 
@@ -84,6 +86,12 @@ def load() -> ctypes.CDLL:
         "b200_step": [vp, ctypes.c_int, f32, f32],
         "b200_backward": [vp, ctypes.c_int],
         "b200_update": [vp, f32, f32],
+        "b200_forward_begin": [vp, ctypes.c_int],
+        "b200_forward_ft": [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int],
+        "b200_net_tensor_offset": [vp, cp, ctypes.POINTER(i64)],
+        "b200_exchange_export": [vp, vp, i64],
+        "b200_exchange_import": [vp, ctypes.c_int, ctypes.c_int, vp, i64],
+        "b200_update_exchange": [vp, f32, f32],
         "b200_backward_begin": [vp, ctypes.c_int],
         "b200_backward_ft": [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int],
         "b200_backward_end": [vp, ctypes.c_int],

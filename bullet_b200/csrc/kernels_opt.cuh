@@ -66,4 +66,61 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(const __grid_constant__
     }
 }
 
+// Data-parallel update over peer memory: reduce-scatter, AdamW and all-gather in one launch.
+// Every rank's gradient and parameter buffers are mapped into this process (CUDA IPC over
+// NVLink).  A thread owns float4 index i of THIS rank's share of the flat buffer: it loads
+// G_r[i] from every rank r with plain peer loads, sums them in rank order (one owner per
+// element, so all replicas end up bit-identical), runs AdamW on the local p, m, v, and
+// stores the new p into every rank's parameter buffer with plain peer stores.  The leading
+// padding of the buffer carries the summed loss in float 0: its owner writes the reduced
+// value into every rank's parameter buffer, which does not use those floats.
+// The caller orders the launch between two cross-rank barriers: every rank's gradients
+// complete before, every rank's launch complete after.  Nothing in the kernel waits.
+constexpr int kMaxRanks = 8;
+
+struct ExchangeArgs {
+    AdamArgs adam;               // local p, m, v; first4 / total4 = this rank's share; g unused
+    const float4* g[kMaxRanks];  // gradient buffer of every rank, own included, by rank
+    float4* p_out[kMaxRanks];    // parameter buffer of every rank
+    int world;
+    long long head4;             // float4s of leading padding (the loss lives in the first)
+};
+
+__global__ void __launch_bounds__(256) adamw_exchange_kernel(const __grid_constant__ ExchangeArgs x) {
+    const AdamArgs& a = x.adam;
+    for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < a.total4; j += (long long)gridDim.x * blockDim.x) {
+        const long long i = a.first4 + j;
+        float4 gr[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < x.world) gr[r] = x.g[r][i];  // all loads in flight before the first add
+        float4 g = gr[0];
+#pragma unroll
+        for (int r = 1; r < kMaxRanks; r++)
+            if (r < x.world) g.x += gr[r].x, g.y += gr[r].y, g.z += gr[r].z, g.w += gr[r].w;
+        int si = -1;
+#pragma unroll 1
+        for (int k = 0; k < a.nseg; k++)
+            if (i >= a.seg[k].begin4 && i < a.seg[k].end4) si = k;
+        float4 p;
+        if (si < 0) {
+            if (i >= x.head4) continue;  // alignment padding between tensors
+            p = g;                       // the summed loss (and zeros)
+        } else {
+            const AdamSegment& s = a.seg[si];
+            p = a.p[i];
+            float4 m = a.m[i], v = a.v[i];
+            adam_op(s, a.rate, a.adj * g.x, p.x, m.x, v.x);
+            adam_op(s, a.rate, a.adj * g.y, p.y, m.y, v.y);
+            adam_op(s, a.rate, a.adj * g.z, p.z, m.z, v.z);
+            adam_op(s, a.rate, a.adj * g.w, p.w, m.w, v.w);
+            a.m[i] = m;
+            a.v[i] = v;
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < x.world) x.p_out[r][i] = p;
+    }
+}
+
 }  // namespace b200

@@ -68,6 +68,7 @@ struct Slot {
     int n_chunks = 0, chunk_len = 0;  // chunks of the tiled FT backward held in off_chunks, and their size
     int n_fitems = 0;                 // work items of the tiled forward / backward (see TileArgs::items)
     std::vector<int> bitem_begin;     // [nblocks + 1] first backward item of every block
+    std::vector<int> fitem_begin;     // [nblocks + 1] first forward item of every block
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
            off_dtiles = 0, off_chunks = 0, off_fitems = 0, off_bitems = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
@@ -109,6 +110,12 @@ struct b200_net {
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
     int bwd_chunk() const { return b200::ft_bwd_chunk(d.nnz, bwd_wide); }
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
+    int fwd_slot = -1, fwd_parts_done = 0, fwd_parts = 0;  // progress of a forward pass run in pieces
+    // peers of the fused data-parallel update: every rank's gradient and parameter buffer mapped here
+    int xch_rank = -1, xch_world = 0;
+    float* peer_g[b200::kMaxRanks] = {};
+    float* peer_p[b200::kMaxRanks] = {};
+    bool loss_in_param = false;  // the last update left the summed loss in P[0] instead of G[0]
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
     int last_n = 0;
@@ -391,23 +398,42 @@ int check_slot(b200_net* net, int slot, const char* who) {
     return 0;
 }
 
-int forward_part(b200_net* net, Slot& s, bool want_grad) {
-    const b200_net_desc& d = net->d;
-    const bool tiled = net->fwd_tiled();
+// The forward pass in three pieces: the per-pair row lists, the feature-transformer items of a
+// run of work items, and the dense layers.
+int forward_prepare(b200_net* net, Slot& s, bool want_grad) {
     b200::FtArgs fa = ft_args(net, s);
     b200::TileArgs ta = tile_args(net, s, false);
-    if (tiled || (want_grad && net->bwd_tiled())) {
+    if (net->fwd_tiled() || (want_grad && net->bwd_tiled())) {
         b200::ft_prepare_kernel<<<(2 * s.n + 7) / 8, 256, 0, net->stream>>>(fa, ta);
         LAUNCHED(net);
     }
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][0], net->stream));
-    int rc = d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled, s.n_fitems) : launch_ft_forward<false>(net, fa, ta, tiled, s.n_fitems);
-    if (rc) return rc;
+    return 0;
+}
+
+int forward_ft_items(b200_net* net, Slot& s, int first_item, int n_items) {
+    const bool tiled = net->fwd_tiled();
+    b200::FtArgs fa = ft_args(net, s);
+    b200::TileArgs ta = tile_args(net, s, false);
+    if (tiled) {
+        if (n_items < 1) return 0;
+        ta.items += first_item;
+    }
+    return net->d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled, n_items) : launch_ft_forward<false>(net, fa, ta, tiled, n_items);
+}
+
+int forward_dense(b200_net* net, Slot& s, bool want_grad) {
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
     b200::DenseArgs da = dense_args(net, s, want_grad);
-    DISPATCH_M(d.dense_out[0], launch_dense_forward<MM>(net, da, s.n_dtiles));
+    DISPATCH_M(net->d.dense_out[0], launch_dense_forward<MM>(net, da, s.n_dtiles));
     LAUNCHED(net);
     return 0;
+}
+
+int forward_part(b200_net* net, Slot& s, bool want_grad) {
+    if (int rc = forward_prepare(net, s, want_grad)) return rc;
+    if (int rc = forward_ft_items(net, s, 0, s.n_fitems)) return rc;
+    return forward_dense(net, s, want_grad);
 }
 
 int launch_wgrad(b200_net* net, const Slot& s, int layer) {
@@ -607,6 +633,11 @@ int b200_net_destroy(b200_net* net) {
     cudaSetDevice(net->device);
     if (net->stream) cudaStreamSynchronize(net->stream);
     if (net->copy_stream) cudaStreamSynchronize(net->copy_stream);
+    for (int r = 0; r < net->xch_world; r++)
+        if (r != net->xch_rank) {
+            if (net->peer_g[r]) cudaIpcCloseMemHandle(net->peer_g[r]);
+            if (net->peer_p[r]) cudaIpcCloseMemHandle(net->peer_p[r]);
+        }
     for (void* p : net->allocations) cudaFree(p);
     for (auto& s : net->slots) {
         if (s.d_blob) cudaFree(s.d_blob);
@@ -651,6 +682,14 @@ int b200_net_tensor_size(b200_net* net, const char* name, int64_t* n) {
     const Tensor* t = net->find(name);
     if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
     *n = t->n;
+    return 0;
+}
+
+int b200_net_tensor_offset(b200_net* net, const char* name, int64_t* first_float) {
+    if (!net || !name || !first_float) return b200::fail(B200_ERR_ARG, "tensor_offset: null argument");
+    const Tensor* t = net->find(name);
+    if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    *first_float = t->off;
     return 0;
 }
 
@@ -813,11 +852,13 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         const int b_target = std::max(1, (avg_chunks + b_split - 1) / b_split);  // chunks per item
         int nc = 0, nf = 0, nbi = 0;
         s.bitem_begin.assign(nb + 1, 0);
+        s.fitem_begin.assign(nb + 1, 0);
         for (int b = 0; b < nb; b++) {
             const int lo = h_blocks[b], hi = h_blocks[b + 1], cnt = hi - lo;
             const int first_chunk = nc;
             for (int at = lo; at < hi; at += cp) h_chunks[nc++] = make_int4(b, at, std::min(cp, hi - at), 0);
             // forward: at least one item per block (an empty block still has nothing to write, so none is needed)
+            s.fitem_begin[b] = nf;
             const int fpieces = cnt > 0 ? (cnt + f_target - 1) / f_target : 0;
             for (int k = 0; k < fpieces; k++)
                 h_fitems[nf++] = make_int4(b, lo + (int)((long long)cnt * k / fpieces), lo + (int)((long long)cnt * (k + 1) / fpieces), 0);
@@ -829,6 +870,7 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
                                             first_chunk + (int)((long long)chunks_here * (k + 1) / bpieces), 0);
         }
         s.bitem_begin[nb] = nbi;
+        s.fitem_begin[nb] = nf;
         s.n_chunks = nc;
         s.n_fitems = nf;
     }
@@ -841,6 +883,45 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
     return 0;
 }
 
+// ---- the training forward pass in pieces (b200_backward_begin runs them itself when the caller has not)
+
+int b200_forward_begin(b200_net* net, int slot) {
+    if (int rc = check_slot(net, slot, "forward_begin")) return rc;
+    if (net->bwd_slot >= 0) return b200::fail(B200_ERR_STATE, "forward_begin: the backward pass of slot %d is not finished", net->bwd_slot);
+    if (int rc = set_device(net)) return rc;
+    Slot& s = net->slots[slot];
+    CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
+    if (int rc = refresh_table(net)) return rc;
+    CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->stream));  // every gradient is accumulated with reductions
+    if (int rc = forward_prepare(net, s, true)) return rc;
+    net->fwd_slot = slot;
+    net->fwd_parts_done = 0;
+    net->fwd_parts = 0;
+    return 0;
+}
+
+int b200_forward_ft(b200_net* net, int slot, int part, int n_parts) {
+    if (int rc = check_slot(net, slot, "forward_ft")) return rc;
+    if (net->fwd_slot != slot) return b200::fail(B200_ERR_STATE, "forward_ft: call b200_forward_begin on slot %d first", slot);
+    if (n_parts < 1 || part < 0 || part >= n_parts || part != net->fwd_parts_done)
+        return b200::fail(B200_ERR_ARG, "forward_ft: parts must be run in order 0..n_parts-1 (got %d of %d)", part, n_parts);
+    if (n_parts > 1 && (!net->fwd_tiled() || net->nblocks % n_parts))
+        return b200::fail(B200_ERR_UNSUPPORTED, "forward_ft: %d parts need the tiled forward and must divide the %d row blocks", n_parts,
+                          net->nblocks);
+    if (int rc = set_device(net)) return rc;
+    Slot& s = net->slots[slot];
+    int first = 0, count = s.n_fitems;
+    if (n_parts > 1) {  // the work items of this part's run of row blocks
+        const int per = net->nblocks / n_parts;
+        first = s.fitem_begin[part * per];
+        count = s.fitem_begin[(part + 1) * per] - first;
+    }
+    if (int rc = forward_ft_items(net, s, first, count)) return rc;
+    net->fwd_parts_done = part + 1;
+    net->fwd_parts = n_parts;
+    return 0;
+}
+
 // ---- the backward pass in three phases (b200_backward runs them back to back)
 
 int b200_backward_begin(b200_net* net, int slot) {
@@ -848,10 +929,16 @@ int b200_backward_begin(b200_net* net, int slot) {
     if (int rc = set_device(net)) return rc;
     Slot& s = net->slots[slot];
     const b200_net_desc& d = net->d;
-    CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
-    if (int rc = refresh_table(net)) return rc;
-    CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->stream));  // every gradient is accumulated with reductions
-    if (int rc = forward_part(net, s, true)) return rc;
+    if (net->fwd_slot == slot) {  // the forward pass was started in pieces: every piece must be in
+        if (net->fwd_parts_done < 1 || net->fwd_parts_done != net->fwd_parts)
+            return b200::fail(B200_ERR_STATE, "backward_begin: run every b200_forward_ft part of slot %d first", slot);
+    } else {
+        if (net->fwd_slot >= 0) return b200::fail(B200_ERR_STATE, "backward_begin: a forward pass of slot %d is under way", net->fwd_slot);
+        if (int rc = b200_forward_begin(net, slot)) return rc;
+        if (int rc = b200_forward_ft(net, slot, 0, 1)) return rc;
+    }
+    net->fwd_slot = -1;
+    if (int rc = forward_dense(net, s, true)) return rc;
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[2], net->stream));
     if (net->bwd_tiled() && s.n_chunks > 0) {  // row-major lists of every chunk, shared by all column slabs
@@ -1007,12 +1094,100 @@ int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_
     return 0;
 }
 
+// ---- the data-parallel update over peer memory (one process per GPU)
+
+int b200_exchange_export(b200_net* net, void* handles, int64_t bytes) {
+    if (!net || !handles) return b200::fail(B200_ERR_ARG, "exchange_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == B200_IPC_HANDLE_BYTES, "handle size");
+    if (bytes < 2 * B200_IPC_HANDLE_BYTES) return b200::fail(B200_ERR_ARG, "exchange_export: %d bytes are needed", 2 * B200_IPC_HANDLE_BYTES);
+    if (int rc = set_device(net)) return rc;
+    cudaIpcMemHandle_t h[2];
+    CK(cudaIpcGetMemHandle(&h[0], net->G));
+    CK(cudaIpcGetMemHandle(&h[1], net->P));
+    memcpy(handles, h, sizeof h);
+    return 0;
+}
+
+int b200_exchange_import(b200_net* net, int rank, int world, const void* handles, int64_t bytes) {
+    if (!net || !handles) return b200::fail(B200_ERR_ARG, "exchange_import: null argument");
+    if (world < 2 || world > b200::kMaxRanks || rank < 0 || rank >= world)
+        return b200::fail(B200_ERR_ARG, "exchange_import: rank %d of %d (at most %d ranks)", rank, world, b200::kMaxRanks);
+    if (bytes < (int64_t)world * 2 * B200_IPC_HANDLE_BYTES) return b200::fail(B200_ERR_ARG, "exchange_import: handles of %d ranks are needed", world);
+    if (net->xch_world) return b200::fail(B200_ERR_STATE, "exchange_import: peers are already mapped");
+    if (net->n_flat % (4 * world)) return b200::fail(B200_ERR_UNSUPPORTED, "exchange_import: the flat buffer does not split over %d ranks", world);
+    if (int rc = set_device(net)) return rc;
+    const cudaIpcMemHandle_t* h = static_cast<const cudaIpcMemHandle_t*>(handles);
+    for (int r = 0; r < world; r++) {
+        if (r == rank) {
+            net->peer_g[r] = net->G;
+            net->peer_p[r] = net->P;
+            continue;
+        }
+        void *g = nullptr, *p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&g, h[2 * r], cudaIpcMemLazyEnablePeerAccess);
+        if (e == cudaSuccess) e = cudaIpcOpenMemHandle(&p, h[2 * r + 1], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            if (g) cudaIpcCloseMemHandle(g);
+            for (int q = 0; q < r; q++)
+                if (q != rank) {
+                    cudaIpcCloseMemHandle(net->peer_g[q]);
+                    cudaIpcCloseMemHandle(net->peer_p[q]);
+                }
+            memset(net->peer_g, 0, sizeof net->peer_g);
+            memset(net->peer_p, 0, sizeof net->peer_p);
+            return b200::fail(B200_ERR_CUDA, "exchange_import: cannot map the buffers of rank %d: %s", r, cudaGetErrorString(e));
+        }
+        net->peer_g[r] = static_cast<float*>(g);
+        net->peer_p[r] = static_cast<float*>(p);
+    }
+    net->xch_rank = rank;
+    net->xch_world = world;
+    return 0;
+}
+
+int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
+    if (!net) return b200::fail(B200_ERR_ARG, "update_exchange: null net");
+    if (!net->xch_world) return b200::fail(B200_ERR_STATE, "update_exchange: map the peers with b200_exchange_import first");
+    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_exchange: no gradients yet, call b200_backward first");
+    if (int rc = set_device(net)) return rc;
+    b200::ExchangeArgs x{};
+    b200::AdamArgs& a = x.adam;
+    const int64_t per = net->n_flat / net->xch_world;
+    a.p = reinterpret_cast<float4*>(net->P);
+    a.m = reinterpret_cast<float4*>(net->M);
+    a.v = reinterpret_cast<float4*>(net->V);
+    a.g = nullptr;
+    a.first4 = net->xch_rank * per / 4;
+    a.total4 = per / 4;
+    a.rate = lr;
+    a.adj = grad_factor;
+    a.nseg = (int)net->tensors.size();
+    for (int i = 0; i < a.nseg; i++) {
+        const Tensor& t = net->tensors[i];
+        a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
+    }
+    x.world = net->xch_world;
+    x.head4 = kAlignFloats / 4;
+    for (int r = 0; r < x.world; r++) {
+        x.g[r] = reinterpret_cast<const float4*>(net->peer_g[r]);
+        x.p_out[r] = reinterpret_cast<float4*>(net->peer_p[r]);
+    }
+    const long long blocks = std::min<long long>((a.total4 + 255) / 256, kSmCount * 8);
+    b200::adamw_exchange_kernel<<<(unsigned)blocks, 256, 0, net->stream>>>(x);
+    LAUNCHED(net);
+    net->table_dirty = true;
+    net->loss_in_param = true;
+    return 0;
+}
+
 int b200_update_end(b200_net* net) {
     if (!net) return b200::fail(B200_ERR_ARG, "update_end: null net");
     if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_end: no gradients yet");
     if (int rc = set_device(net)) return rc;
     const int ring = (int)(net->updates % b200_net::kLossRing);
-    CK(cudaMemcpyAsync(net->h_loss + ring, net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
+    CK(cudaMemcpyAsync(net->h_loss + ring, net->loss_in_param ? net->P : net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
+    net->loss_in_param = false;
     CK(cudaMemcpyAsync(net->h_status + ring, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
     CK(cudaEventRecord(net->loss_ev[ring], net->stream));
     net->updates++;

@@ -12,6 +12,17 @@ the l0w gradient (by far the largest tensor) travels while the next slice and th
 layers' weight gradients are still being computed; AdamW then runs slice by slice as the
 reduced slices arrive.  Every rank issues the same collectives in the same order.
 
+With `shard_optimiser` the all-reduce becomes a reduce-scatter, AdamW on this rank's 1/world of
+the buffer and an all-gather of the weights: the same bytes on the wire, 1/world of the
+optimiser traffic.  With `peer_exchange` those three steps are ONE kernel of the library over peer memory
+(`b200_update_exchange`: peer loads of every rank's gradients, AdamW on this rank's share, peer
+stores of the new weights to every rank), fenced by two tiny all-reduces.
+With `shard_optimiser` and `parts > 1` together the three are pipelined
+slice by slice of l0w AND across steps: the reduce-scatter of a slice travels under the
+backward of the next, and the all-gather of its updated weights is only waited for by the
+forward pass of the NEXT step, slice by slice again, so that almost all of the exchange hides
+behind kernels (`finish()` waits for what is still in flight).
+
 The reference has no multi-GPU path (one device chosen by ordinal,
 crates/bullet_lib/src/value/builder.rs:97-100); this module is new work on top of its step
 loop (crates/trainer/src/run.rs:166-250).  `torch.distributed` supplies the process group:
@@ -46,7 +57,8 @@ class DataParallelStep:
     `backward_begin/backward_ft/backward_end`, `grad_part`, `update_range`, `update_end`.
     """
 
-    def __init__(self, engine, global_batch: int, parts: int = 1, shard_optimiser: bool = False, process_group=None):
+    def __init__(self, engine, global_batch: int, parts: int = 1, shard_optimiser: bool = False, process_group=None,
+                 peer_exchange: bool = False):
         import torch.distributed as dist
 
         self.engine = engine
@@ -57,7 +69,24 @@ class DataParallelStep:
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.parts = parts if self.world > 1 else 1
         self.shard = shard_optimiser and self.world > 1
-        if self.shard and engine.grad.numel() % self.world:
+        self.peer = peer_exchange and self.world > 1
+        if self.peer:  # map every rank's gradient and parameter buffers into this process
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, (engine.exchange_export(), engine.grad.numel()), group=process_group)
+            if any(n != engine.grad.numel() for _, n in gathered):
+                raise ValueError("the ranks hold networks of different sizes")
+            engine.exchange_import(self.rank, self.world, b"".join(h for h, _ in gathered))
+            self._token = engine.grad.new_zeros(1)
+            self.shard, self.parts = True, 1  # momentum and velocity live sharded, as with shard_optimiser
+        self.pipelined = self.shard and self.parts > 1
+        self._gathers = None  # all-gathers of the previous step's weights, one per slice, still to be waited for
+        if self.pipelined:
+            self.l0w_first, n_l0w = engine.tensor_range("l0w")
+            self.head_split = engine.tensor_range("l1b")[0]  # [0, split): loss, l0b, l0f; [split, l0w): the dense layers
+            self.per_part = n_l0w // self.parts
+            if n_l0w % self.parts or self.per_part % (4 * self.world):
+                raise ValueError("l0w does not split evenly into parts x ranks x 4 floats")
+        elif self.shard and engine.grad.numel() % self.world:
             raise ValueError("the flat buffer does not split evenly over the ranks")
 
     def _sharded_step(self, slot: int, lr: float) -> None:
@@ -82,9 +111,84 @@ class DataParallelStep:
         eng.grad[0:1].copy_(eng.param[0:1])
         eng.update_end()
 
+    def _peer_step(self, slot: int, lr: float) -> None:
+        """The exchange as one kernel over peer memory: gradients summed with peer loads, AdamW on
+        this rank's share, new weights stored to every rank.  The two tiny all-reduces are barriers
+        on the stream: all gradients complete before the kernel, all stores landed after it."""
+        eng, dist = self.engine, self.dist
+        eng.backward(slot)
+        dist.all_reduce(self._token, group=self.group)
+        eng.update_exchange(lr, 1.0 / self.global_batch)
+        dist.all_reduce(self._token, group=self.group)
+        eng.update_end()
+
+    def _slice(self, part: int):
+        """(whole slice, this rank's share of it) of l0w inside the flat buffers, as python slices."""
+        first = self.l0w_first + part * self.per_part
+        share = self.per_part // self.world
+        return slice(first, first + self.per_part), slice(first + self.rank * share, first + (self.rank + 1) * share)
+
+    def _pipelined_sharded_step(self, slot: int, lr: float) -> None:
+        """Sharded optimiser, slice by slice of l0w and across steps.
+
+        Order on every rank: forward (slice p waits for last step's gather of slice p) ->
+        backward with one reduce-scatter per finished slice -> all-reduce of the small tensors
+        (loss, l0b, l0f after the last slice; dense layers after their weight gradients) ->
+        per slice: AdamW on this rank's share, all-gather of the slice (left in flight) ->
+        AdamW on the small tensors, on every rank alike.  Momentum and velocity of l0w live
+        sharded (rank r holds share r of every slice); those of the small tensors are complete
+        everywhere."""
+        eng, dist, P, gf = self.engine, self.dist, self.parts, 1.0 / self.global_batch
+        nccl = dist.get_backend(self.group) == "nccl"
+        eng.forward_begin(slot)
+        for p in range(P):
+            if self._gathers is not None:
+                self._gathers[p].wait()  # the compute stream waits; the host does not
+            eng.forward_ft(slot, p, P)
+        self._gathers = None
+        eng.backward_begin(slot)
+        scatters = []
+        for p in range(P):
+            eng.backward_ft(slot, p, P)
+            whole, mine = self._slice(p)
+            if nccl:
+                work = dist.reduce_scatter_tensor(eng.grad[mine], eng.grad[whole], group=self.group, async_op=True)
+            else:  # gloo has no reduce-scatter: reduce the slice, use this rank's share
+                work = dist.all_reduce(eng.grad[whole], group=self.group, async_op=True)
+            scatters.append(work)
+        head_a = dist.all_reduce(eng.grad[0:self.head_split], group=self.group, async_op=True)
+        eng.backward_end(slot)
+        head_b = dist.all_reduce(eng.grad[self.head_split:self.l0w_first], group=self.group, async_op=True)
+        gathers = []
+        for p in range(P):
+            whole, mine = self._slice(p)
+            scatters[p].wait()
+            eng.update_range(lr, gf, mine.start, mine.stop - mine.start)
+            gathers.append(dist.all_gather_into_tensor(eng.param[whole], eng.param[mine], group=self.group, async_op=True))
+        head_a.wait()
+        head_b.wait()
+        eng.update_range(lr, gf, 0, self.l0w_first)
+        eng.update_end()
+        self._gathers = gathers
+
+    def finish(self) -> None:
+        """Waits (on the compute stream) for weight gathers still in flight; call before reading
+        weights, saving, or leaving the training loop."""
+        if self._gathers is not None:
+            for work in self._gathers:
+                work.wait()
+            self._gathers = None
+
     def gather_state(self) -> None:
         """After sharded steps: make momentum and velocity complete on every rank."""
         if not self.shard:
+            return
+        self.finish()
+        if self.pipelined:
+            for buf in self.engine.state_buffers():
+                for p in range(self.parts):
+                    whole, mine = self._slice(p)
+                    self.dist.all_gather_into_tensor(buf[whole], buf[mine].clone(), group=self.group)
             return
         per = self.engine.grad.numel() // self.world
         mine = slice(self.rank * per, (self.rank + 1) * per)
@@ -93,6 +197,12 @@ class DataParallelStep:
 
     def step(self, slot: int, lr: float) -> None:
         eng, gf = self.engine, 1.0 / self.global_batch
+        if self.peer:
+            self._peer_step(slot, lr)
+            return
+        if self.pipelined:
+            self._pipelined_sharded_step(slot, lr)
+            return
         if self.shard:
             self._sharded_step(slot, lr)
             return
@@ -139,6 +249,7 @@ class NetEngine:
         self.grad = wrap_device_buffer(ptr, count, device)
         self.param, self._m, self._v = (wrap_device_buffer(*net.flat_buffer(kind), device) for kind in (0, 1, 2))
         self.state_buffers = lambda: [self._m, self._v]
-        for name in ("backward", "update", "backward_begin", "backward_ft", "backward_end", "grad_part",
-                     "update_range", "update_end"):
+        for name in ("backward", "update", "forward_begin", "forward_ft", "backward_begin", "backward_ft", "backward_end",
+                     "grad_part", "update_range", "update_end", "tensor_range", "exchange_export", "exchange_import",
+                     "update_exchange"):
             setattr(self, name, getattr(net, name))

@@ -94,6 +94,31 @@ class Net:
         _lib.check(self.lib.b200_update(self._h, lr, grad_factor))
 
     # the same step in phases (see include/bullet_b200.h); used by the data-parallel host
+    def forward_begin(self, slot: int) -> None:
+        _lib.check(self.lib.b200_forward_begin(self._h, slot))
+
+    def forward_ft(self, slot: int, part: int, n_parts: int) -> None:
+        _lib.check(self.lib.b200_forward_ft(self._h, slot, part, n_parts))
+
+    def tensor_range(self, name: str) -> tuple[int, int]:
+        """(first float, count) of a tensor inside the flat buffers."""
+        first, count = ctypes.c_int64(), ctypes.c_int64()
+        _lib.check(self.lib.b200_net_tensor_offset(self._h, name.encode(), ctypes.byref(first)))
+        _lib.check(self.lib.b200_net_tensor_size(self._h, name.encode(), ctypes.byref(count)))
+        return first.value, count.value
+
+    # the data-parallel update over peer memory (see include/bullet_b200.h)
+    def exchange_export(self) -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        _lib.check(self.lib.b200_exchange_export(self._h, buf, 128))
+        return buf.raw
+
+    def exchange_import(self, rank: int, world: int, handles: bytes) -> None:
+        _lib.check(self.lib.b200_exchange_import(self._h, rank, world, handles, len(handles)))
+
+    def update_exchange(self, lr: float, grad_factor: float) -> None:
+        _lib.check(self.lib.b200_update_exchange(self._h, lr, grad_factor))
+
     def backward_begin(self, slot: int) -> None:
         _lib.check(self.lib.b200_backward_begin(self._h, slot))
 

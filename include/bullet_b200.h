@@ -128,6 +128,34 @@ int b200_update(b200_net* net, float lr, float grad_factor);
  * element is the summed loss, so one all-reduce carries both. */
 int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
 
+/* The data-parallel update over peer memory, one process per GPU of one box (new; the reference is
+ * single-GPU).  b200_exchange_export writes two CUDA IPC handles (gradient buffer, parameter
+ * buffer; 2 * B200_IPC_HANDLE_BYTES bytes); the host gathers the handles of all ranks, in rank
+ * order, and hands them to b200_exchange_import, which maps every peer's buffers (at most 8 ranks;
+ * the flat buffer must split into world x 4 floats).  b200_update_exchange then replaces the
+ * all-reduce + b200_update pair: ONE kernel sums this rank's 1/world share of the gradients over all
+ * ranks with peer loads, applies AdamW+clip to it and stores the new weights into every rank's
+ * parameter buffer (reduce-scatter + AdamW + all-gather).  Momentum and velocity stay sharded.
+ * The caller must order it between two cross-rank barriers on the stream (any tiny collective):
+ * all ranks' b200_backward complete before it starts, all ranks' b200_update_exchange complete
+ * before anyone touches weights or gradients again; b200_update_end follows as usual. */
+#define B200_IPC_HANDLE_BYTES 64
+int b200_exchange_export(b200_net* net, void* handles, int64_t bytes);
+int b200_exchange_import(b200_net* net, int rank, int world, const void* handles, int64_t bytes);
+int b200_update_exchange(b200_net* net, float lr, float grad_factor);
+
+/* The training forward pass in pieces, for a host that overlaps an exchange of freshly updated
+ * weights with it (a sharded optimiser gathers l0w slice by slice): b200_forward_begin waits for
+ * the batch, zeroes the gradients and builds the row lists; b200_forward_ft runs the feature
+ * transformer for the part-th of n_parts equal runs of table row blocks, in order, reading only
+ * that run's rows of l0w (plus l0b and l0f); b200_backward_begin on the same slot then carries on
+ * from the dense layers.  Without these calls b200_backward_begin runs the whole forward itself. */
+int b200_forward_begin(b200_net* net, int slot);
+int b200_forward_ft(b200_net* net, int slot, int part, int n_parts);
+/* First float of a tensor inside the flat buffers (b200_flat_buffer); tensors lie in name order
+ * with l0w last, each starting on a 256-byte boundary. */
+int b200_net_tensor_offset(b200_net* net, const char* name, int64_t* first_float);
+
 /* The same step in phases, for a host that overlaps the gradient exchange with the backward
  * pass.  b200_backward = begin + ft(0, 1) + end; b200_update = update_range(whole buffer) + end.
  *   b200_backward_begin  zeroes the gradients, runs the forward, the loss and the backward

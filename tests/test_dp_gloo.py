@@ -63,7 +63,21 @@ class OracleEngine:
         self.update_end()
 
     # ---- phased form: the oracle computes everything at once, the phases only expose the ranges
+    def forward_begin(self, slot):
+        self.forward_parts = []
+
+    def forward_ft(self, slot, part, n_parts):
+        # a forward slice may only run once the gather of that slice of l0w has landed: remember what it saw
+        lo = self.offsets["l0w"] + part * (self.w["l0w"].size // n_parts)
+        self.forward_parts.append(self.flat["w"][lo:lo + self.w["l0w"].size // n_parts].copy())
+
+    def tensor_range(self, name):
+        return self.offsets[name], self.w[name].size
+
     def backward_begin(self, slot):
+        if getattr(self, "forward_parts", None):  # the weights the forward slices saw are the weights now
+            assert np.array_equal(np.concatenate(self.forward_parts), self.w["l0w"])
+            self.forward_parts = []
         self.backward(slot)
 
     def backward_ft(self, slot, part, n_parts):
@@ -122,7 +136,7 @@ def _worker(rank, world, port, out_dir, parts, shard):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("parts,shard", [(1, False), (4, False), (1, True)])
+@pytest.mark.parametrize("parts,shard", [(1, False), (4, False), (1, True), (4, True)])
 def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard):
     from bullet_b200 import config, synth
     from bullet_b200.configs import AdamWParams

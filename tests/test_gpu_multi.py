@@ -1,0 +1,101 @@
+"""Two GPUs, one process each (NCCL): every form of the data-parallel exchange trains the same
+network as a single GPU does on the whole batch.  Skipped on a box with one GPU.
+
+Forms: one all-reduce; reduce-scatter + sharded AdamW + all-gather; the same pipelined slice by
+slice with the gathers waited for by the next forward pass; the library's one-kernel exchange
+over peer memory (b200_update_exchange)."""
+import dataclasses
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+MODES = {"allreduce": dict(), "sharded": dict(shard_optimiser=True), "pipelined": dict(shard_optimiser=True, parts=4),
+         "allreduce_parts": dict(parts=4), "peer": dict(peer_exchange=True)}
+GLOBAL, STEPS, LR = 2048, 3, 1e-2
+
+
+def _setup():
+    from bullet_b200 import config
+
+    c = config(3)
+    return c, dataclasses.replace(c.desc, ft_out=256, max_batch=GLOBAL)
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from bullet_b200 import synth
+    from bullet_b200.dp import DataParallelStep, NetEngine, shard_batch
+    from bullet_b200.net import Net, featurise
+
+    c, desc = _setup()
+    weights = synth.init_weights(desc, seed=3)
+    weights["l0f"] = np.random.default_rng(4).normal(0, 0.05, weights["l0f"].size).astype(np.float32)
+    batches = [featurise(c.game, synth.records(c.game, GLOBAL, seed=70 + s), desc) for s in range(STEPS)]
+    stream = torch.cuda.Stream()
+    out = {}
+    with torch.cuda.stream(stream):
+        for mode, kw in MODES.items():
+            net = Net(dataclasses.replace(desc, max_batch=GLOBAL // world), device=rank, stream=stream.cuda_stream)
+            net.load_weights(weights)
+            dp = DataParallelStep(NetEngine(net, torch.device("cuda", rank)), GLOBAL, **kw)
+            losses = []
+            for s in range(STEPS):
+                net.upload(s % 3, *shard_batch(batches[s], rank, world))
+                dp.step(s % 3, LR)
+                losses.append(net.loss())
+            dp.gather_state()
+            net.sync()
+            torch.cuda.synchronize()
+            dist.barrier()
+            for k, v in net.tensors(0).items():
+                out[f"{mode}/w/{k}"] = v
+            out[f"{mode}/m/l0w"] = net.tensors(1)["l0w"]
+            out[f"{mode}/losses"] = np.array(losses)
+            dist.barrier()  # nobody unmaps peer buffers while another rank may still use them
+            net.close()
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **out)
+    dist.destroy_process_group()
+
+
+def test_every_exchange_form_matches_one_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from bullet_b200 import synth
+    from bullet_b200.net import Net, featurise
+
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    # the single-GPU run on the whole batch
+    c, desc = _setup()
+    weights = synth.init_weights(desc, seed=3)
+    weights["l0f"] = np.random.default_rng(4).normal(0, 0.05, weights["l0f"].size).astype(np.float32)
+    net = Net(desc)
+    net.load_weights(weights)
+    ref_losses = []
+    for s in range(STEPS):
+        net.upload(s % 3, *featurise(c.game, synth.records(c.game, GLOBAL, seed=70 + s), desc))
+        net.step(s % 3, LR, 1.0 / GLOBAL)
+        ref_losses.append(net.loss())
+    w_ref, m_ref = net.tensors(0), net.tensors(1)["l0w"]
+    net.close()
+    rel = lambda a, b: np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30)  # noqa: E731
+    for mode in MODES:
+        np.testing.assert_allclose(r0[f"{mode}/losses"], ref_losses, rtol=1e-5, err_msg=mode)
+        np.testing.assert_array_equal(r0[f"{mode}/losses"], r1[f"{mode}/losses"], err_msg=mode)
+        for k in w_ref:
+            assert np.array_equal(r0[f"{mode}/w/{k}"], r1[f"{mode}/w/{k}"]), f"{mode}: replicas differ in {k}"
+            assert rel(r0[f"{mode}/w/{k}"], w_ref[k]) <= 1e-5, (mode, k)
+        assert np.array_equal(r0[f"{mode}/m/l0w"], r1[f"{mode}/m/l0w"]) and rel(r0[f"{mode}/m/l0w"], m_ref) <= 1e-4, mode

@@ -210,6 +210,10 @@ def test_phased_step_equals_one_piece_step(oracle32):
     for parts in (1, 2, 16):
         net = make_net(desc, FT_TILED, w)
         net.upload(0, *batch)
+        if parts > 1:                   # the forward pass in pieces too
+            net.forward_begin(0)
+            for part in range(parts):
+                net.forward_ft(0, part, parts)
         net.backward_begin(0)
         for part in range(parts):
             net.backward_ft(0, part, parts)
@@ -235,6 +239,23 @@ def test_phased_step_equals_one_piece_step(oracle32):
         net.backward_ft(0, 0, 3)        # 3 does not divide 16 row blocks
     with pytest.raises(B200Error):
         net.backward_end(0)             # no part has run
+    with pytest.raises(B200Error):
+        net.forward_begin(0)            # a backward pass is open
+    net.close()
+    net = make_net(desc, FT_TILED, w)
+    net.upload(0, *batch)
+    with pytest.raises(B200Error):
+        net.forward_ft(0, 0, 2)         # not begun
+    net.forward_begin(0)
+    net.forward_ft(0, 0, 2)
+    with pytest.raises(B200Error):
+        net.forward_ft(0, 0, 2)         # out of order
+    with pytest.raises(B200Error):
+        net.backward_begin(0)           # a forward slice is missing
+    net.forward_ft(0, 1, 2)
+    net.backward(0)                     # carries on from the slices
+    first, count = net.tensor_range("l0w")
+    assert (first, count) == (net.grad_part(0, 1)[0], desc.n_inputs * desc.ft_out) and first % 64 == 0
     net.close()
 
 
