@@ -69,6 +69,13 @@ struct Slot {
     int n_fitems = 0;                 // work items of the tiled forward / backward (see TileArgs::items)
     std::vector<int> bitem_begin;     // [nblocks + 1] first backward item of every block
     std::vector<int> fitem_begin;     // [nblocks + 1] first forward item of every block
+    // derived from the indices alone, so built once per upload on the copy stream (or on first use):
+    uint16_t* lists = nullptr;        // prepared per-pair row lists of the tiled kernels
+    int* list_count = nullptr;
+    uint16_t* csr_ent = nullptr;      // per-chunk row-major lists of the tiled backward
+    int* csr_start = nullptr;
+    bool prepared = false, csr_built = false;
+    size_t off_status = 0;            // one int in the blob, zero on upload: bits raised by ft_prepare_kernel
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
            off_dtiles = 0, off_chunks = 0, off_fitems = 0, off_bitems = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
@@ -93,12 +100,8 @@ struct b200_net {
     float *P = nullptr, *G = nullptr, *M = nullptr, *V = nullptr, *table = nullptr;
     float *x = nullptr, *u = nullptr, *dx = nullptr, *a1 = nullptr, *a2 = nullptr, *out = nullptr, *w1g = nullptr;
     float* dz[3] = {nullptr, nullptr, nullptr};
-    int* status = nullptr;
     int wgrad_per_sm = 0;          // resident CTAs per SM of the first layer's weight-gradient kernel (looked up once)
-    uint16_t* ft_lists = nullptr;  // prepared per-pair row lists of the tiled kernels
-    int* ft_list_count = nullptr;
-    uint16_t* csr_ent = nullptr;                        // per-chunk row-major lists of the tiled backward
-    int* csr_start = nullptr;
+    int status_slot = -1;          // slot whose status word the running step reports (-1: the step used no tiled kernel)
     // pinned read-back ring: loss and status word of the last kLossRing updates
     static constexpr int kLossRing = 4;
     int* h_status = nullptr;
@@ -202,6 +205,7 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.off_chunks = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
     s.off_fitems = take(((size_t)2 * n / kMinItemPairs + net->nblocks + 1) * 16);
     s.off_bitems = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
+    s.off_status = take(4);
     s.bytes = off;
 }
 
@@ -324,13 +328,13 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, bool backward) {
     t.items = s.dev<int4>(backward ? s.off_bitems : s.off_fitems);
     t.pair_order = net->nblocks > 1 ? s.dev<int>(s.off_pairs) : nullptr;
     t.block_begin = s.dev<int>(s.off_blocks);
-    t.status = net->status;
-    t.lists = net->ft_lists;
-    t.list_count = net->ft_list_count;
+    t.status = s.dev<int>(s.off_status);
+    t.lists = s.lists;
+    t.list_count = s.list_count;
     t.list_len = (net->d.nnz + 3) & ~3;
     t.chunks = s.dev<int4>(s.off_chunks);
-    t.csr_ent = net->csr_ent;
-    t.csr_start = net->csr_start;
+    t.csr_ent = s.csr_ent;
+    t.csr_start = s.csr_start;
     t.chunk_len = s.chunk_len;
     t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz, s.chunk_len);
     t.start_cap = b200::ft_bwd_start_cap(net->d.ft_block_rows);
@@ -403,10 +407,13 @@ int check_slot(b200_net* net, int slot, const char* who) {
 int forward_prepare(b200_net* net, Slot& s, bool want_grad) {
     b200::FtArgs fa = ft_args(net, s);
     b200::TileArgs ta = tile_args(net, s, false);
-    if (net->fwd_tiled() || (want_grad && net->bwd_tiled())) {
+    const bool needed = net->fwd_tiled() || (want_grad && net->bwd_tiled());
+    if (needed && !s.prepared) {  // normally built at upload; here only if the kernel choice changed since
         b200::ft_prepare_kernel<<<(2 * s.n + 7) / 8, 256, 0, net->stream>>>(fa, ta);
         LAUNCHED(net);
+        s.prepared = true;
     }
+    if (want_grad) net->status_slot = needed ? (int)(&s - net->slots) : -1;
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][0], net->stream));
     return 0;
 }
@@ -554,10 +561,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     for (int l = 0; l < 3; l++) rc = rc ? rc : dev_alloc(net, &net->dz[l], B * 32);
     rc = rc ? rc : dev_alloc(net, &net->out, B);
     rc = rc ? rc : dev_alloc(net, &net->w1g, (size_t)d.n_out_buckets * d.dense_out[0] * net->D1());
-    rc = rc ? rc : dev_alloc(net, &net->status, 1);
     if (net->tiled_ok) {
-        rc = rc ? rc : dev_alloc(net, &net->ft_lists, 2 * B * ((d.nnz + 3) & ~3));
-        rc = rc ? rc : dev_alloc(net, &net->ft_list_count, 2 * B);
         // sized for whichever backward shape needs more: every block may end in a partly filled chunk
         size_t ent_total = 0, max_chunks = 0;
         for (int wide = 0; wide < 2; wide++) {
@@ -566,8 +570,12 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
             max_chunks = std::max(max_chunks, chunks);
             ent_total = std::max(ent_total, chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz, cp));
         }
-        rc = rc ? rc : dev_alloc(net, &net->csr_ent, ent_total);
-        rc = rc ? rc : dev_alloc(net, &net->csr_start, max_chunks * b200::ft_bwd_start_cap(d.ft_block_rows));
+        for (auto& s : net->slots) {
+            rc = rc ? rc : dev_alloc(net, &s.lists, 2 * B * ((d.nnz + 3) & ~3));
+            rc = rc ? rc : dev_alloc(net, &s.list_count, 2 * B);
+            rc = rc ? rc : dev_alloc(net, &s.csr_ent, ent_total);
+            rc = rc ? rc : dev_alloc(net, &s.csr_start, max_chunks * b200::ft_bwd_start_cap(d.ft_block_rows));
+        }
     }
     if (rc) return bail(rc);
     if (!d.factoriser_rows) net->table = net->P + net->find("l0w")->off;
@@ -575,7 +583,6 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     cudaMemsetAsync(net->G, 0, net->n_flat * 4, net->stream);
     cudaMemsetAsync(net->M, 0, net->n_flat * 4, net->stream);
     cudaMemsetAsync(net->V, 0, net->n_flat * 4, net->stream);
-    cudaMemsetAsync(net->status, 0, 4, net->stream);
 
     for (auto& s : net->slots) {
         slot_layout(net, s, d.max_batch);
@@ -874,8 +881,25 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         s.n_chunks = nc;
         s.n_fitems = nf;
     }
+    *s.host<int>(s.off_status) = 0;
     CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
     net->h2d_bytes += (int64_t)s.bytes;
+    // The row lists of the tiled kernels depend on the indices only: build them right behind the
+    // copy, on the copy stream, where they run beside the step that is still computing.
+    s.prepared = s.csr_built = false;
+    s.n = n;
+    if (net->tiled_ok && (net->fwd_tiled() || net->bwd_tiled())) {
+        b200::FtArgs fa = ft_args(net, s);
+        b200::TileArgs ta = tile_args(net, s, true);
+        b200::ft_prepare_kernel<<<(2 * n + 7) / 8, 256, 0, net->copy_stream>>>(fa, ta);
+        LAUNCHED(net);
+        s.prepared = true;
+        if (net->bwd_tiled() && s.n_chunks > 0) {
+            b200::ft_csr_kernel<<<s.n_chunks, b200::kCsrThreads, b200::ft_csr_smem(d.ft_block_rows, d.nnz, s.chunk_len), net->copy_stream>>>(fa, ta);
+            LAUNCHED(net);
+            s.csr_built = true;
+        }
+    }
     CK(cudaEventRecord(s.ready, net->copy_stream));
     s.has_ready = true;
     s.has_consumed = false;
@@ -941,11 +965,12 @@ int b200_backward_begin(b200_net* net, int slot) {
     if (int rc = forward_dense(net, s, true)) return rc;
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[2], net->stream));
-    if (net->bwd_tiled() && s.n_chunks > 0) {  // row-major lists of every chunk, shared by all column slabs
+    if (net->bwd_tiled() && s.n_chunks > 0 && !s.csr_built) {  // normally built at upload
         b200::FtArgs fa = ft_args(net, s);
         b200::TileArgs ta = tile_args(net, s, true);
         b200::ft_csr_kernel<<<s.n_chunks, b200::kCsrThreads, b200::ft_csr_smem(d.ft_block_rows, d.nnz, s.chunk_len), net->stream>>>(fa, ta);
         LAUNCHED(net);
+        s.csr_built = true;
     }
     {
         b200::DenseArgs da = dense_args(net, s, true);
@@ -1188,7 +1213,12 @@ int b200_update_end(b200_net* net) {
     const int ring = (int)(net->updates % b200_net::kLossRing);
     CK(cudaMemcpyAsync(net->h_loss + ring, net->loss_in_param ? net->P : net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
     net->loss_in_param = false;
-    CK(cudaMemcpyAsync(net->h_status + ring, net->status, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+    if (net->status_slot >= 0) {
+        const Slot& st = net->slots[net->status_slot];
+        CK(cudaMemcpyAsync(net->h_status + ring, st.dev<int>(st.off_status), sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+    } else {
+        net->h_status[ring] = 0;
+    }
     CK(cudaEventRecord(net->loss_ev[ring], net->stream));
     net->updates++;
     if (int rc = refresh_table(net)) return rc;
@@ -1239,7 +1269,6 @@ int b200_loss_of(b200_net* net, int steps_back, float* loss_sum) {
     *loss_sum = net->h_loss[ring];
     if (net->h_status[ring] & b200::kStatusOutsideBlock) {
         net->h_status[ring] = 0;
-        cudaMemsetAsync(net->status, 0, sizeof(int), net->stream);
         return b200::fail(B200_ERR_DATA,
                           "a feature index fell outside the row block of its position (ft_block_rows=%d): those "
                           "features were ignored; create the network with ft_block_rows=0 for such inputs",
