@@ -243,6 +243,7 @@ def run_ours(args, rank, world, local_rank):
     peer = bool(args.dp_peer) and world > 1
     dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts, shard_optimiser=shard,
                           peer_exchange=peer)
+    peer, shard, parts = dp.peer, dp.shard, dp.parts  # what is really in use (peer mapping can be refused by the box)
     lr = cfg.lr
 
     def barrier():

@@ -70,14 +70,33 @@ class DataParallelStep:
         self.parts = parts if self.world > 1 else 1
         self.shard = shard_optimiser and self.world > 1
         self.peer = peer_exchange and self.world > 1
+        self.peer_error = None
         if self.peer:  # map every rank's gradient and parameter buffers into this process
+            try:
+                mine = (engine.exchange_export(), engine.grad.numel())
+            except Exception as e:  # noqa: BLE001 - any failure means: use the collectives instead, on every rank
+                mine, self.peer_error = None, str(e)
             gathered = [None] * self.world
-            dist.all_gather_object(gathered, (engine.exchange_export(), engine.grad.numel()), group=process_group)
-            if any(n != engine.grad.numel() for _, n in gathered):
+            dist.all_gather_object(gathered, mine, group=process_group)
+            if any(g is None for g in gathered):
+                self.peer_error = self.peer_error or "another rank could not export its buffers"
+            elif any(n != engine.grad.numel() for _, n in gathered):
                 raise ValueError("the ranks hold networks of different sizes")
-            engine.exchange_import(self.rank, self.world, b"".join(h for h, _ in gathered))
-            self._token = engine.grad.new_zeros(1)
-            self.shard, self.parts = True, 1  # momentum and velocity live sharded, as with shard_optimiser
+            else:
+                try:
+                    engine.exchange_import(self.rank, self.world, b"".join(h for h, _ in gathered))
+                except Exception as e:  # noqa: BLE001
+                    self.peer_error = str(e)
+            # all ranks take the same path: one failure sends everybody to the sharded collectives
+            outcome = [None] * self.world
+            dist.all_gather_object(outcome, self.peer_error, group=process_group)
+            failed = [o for o in outcome if o]
+            if failed:
+                self.peer, self.peer_error = False, failed[0]
+                self.shard = True
+            else:
+                self._token = engine.grad.new_zeros(1)
+                self.shard, self.parts = True, 1  # momentum and velocity live sharded, as with shard_optimiser
         self.pipelined = self.shard and self.parts > 1
         self._gathers = None  # all-gathers of the previous step's weights, one per slice, still to be waited for
         if self.pipelined:

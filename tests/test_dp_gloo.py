@@ -109,8 +109,23 @@ class OracleEngine:
     def update_end(self):
         pass
 
+    # ---- the one-kernel exchange over peer memory, emulated with collectives: what it must compute
+    def exchange_export(self):
+        return bytes(128)
 
-def _worker(rank, world, port, out_dir, parts, shard):
+    def exchange_import(self, rank, world, handles):
+        assert len(handles) == 128 * world
+        self.xch = (rank, world)
+
+    def update_exchange(self, lr, grad_factor):
+        rank, world = self.xch
+        per = self.grad.numel() // world
+        dist.all_reduce(self.grad)
+        self.update_range(lr, grad_factor, rank * per, per)
+        dist.all_gather_into_tensor(self.param, self.param[rank * per:(rank + 1) * per].clone())
+
+
+def _worker(rank, world, port, out_dir, parts, shard, peer=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -124,7 +139,7 @@ def _worker(rank, world, port, out_dir, parts, shard):
     orc = Oracle("f32")
     weights = synth.init_weights(desc, seed=3)
     eng = OracleEngine(desc, weights, AdamWParams())
-    dp = DataParallelStep(eng, global_batch=256, parts=parts, shard_optimiser=shard)
+    dp = DataParallelStep(eng, global_batch=256, parts=parts, shard_optimiser=shard, peer_exchange=peer)
     losses = []
     for step in range(3):
         full = orc.map_batch(c.game, synth.records(c.game, 256, seed=50 + step), desc)
@@ -136,8 +151,9 @@ def _worker(rank, world, port, out_dir, parts, shard):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("parts,shard", [(1, False), (4, False), (1, True), (4, True)])
-def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard):
+@pytest.mark.parametrize("parts,shard,peer", [(1, False, False), (4, False, False), (1, True, False), (4, True, False),
+                                              (1, False, True)])
+def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard, peer):
     from bullet_b200 import config, synth
     from bullet_b200.configs import AdamWParams
     from bullet_b200.dp import shard_bounds
@@ -146,8 +162,8 @@ def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard):
     assert shard_bounds(8, 1, 2) == (4, 8)
     with pytest.raises(ValueError):
         shard_bounds(7, 0, 2)
-    port = 29500 + (os.getpid() + 7 * parts + 3 * shard) % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path), parts, shard), nprocs=2, join=True)
+    port = 29500 + (os.getpid() + 7 * parts + 3 * shard + 11 * peer) % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path), parts, shard, peer), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     c = config(3)
     desc = dataclasses.replace(c.desc, ft_out=64, max_batch=256)
