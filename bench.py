@@ -43,9 +43,11 @@ WORKLOAD = "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->3
 # positions per GPU.  16384 is measured (ncu, profiles/step_kernels_c3_16384.txt); the larger sizes are
 # scaled from it: per-position terms linearly, the one table-sized term (100.7 MB read in the forward,
 # 63 MB of gradient write-back in the backward) kept fixed.
-FT_DRAM_BYTES = {
-    "ft_forward": {16384: 447804416, 32768: 794945536, 65536: 1489227776, 131072: 2877792256},
-    "ft_backward": {16384: 556155136, 32768: 1049104640, 65536: 2035003648, 131072: 4006801664},
+# DRAM traffic model of the tiled kernels, from the ncu capture at 16384 positions (profiles/): one pass over
+# what is read once per launch (the table; in the backward the row lists) plus a per-position term.
+FT_DRAM_MODEL = {  # kernel: (bytes per launch that do not grow with the batch, bytes per position)
+    "ft_forward": (100_663_296, 22_067),
+    "ft_backward": (63_200_000, 30_327),
 }
 N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)
 
@@ -327,7 +329,7 @@ def run_ours(args, rank, world, local_rank):
         k["achieved_gbs"] = k["algorithmic_bytes"] / (k["ms"] * 1e-3) / 1e9 if k["ms"] > 0 else None
         k["frac_of_hbm_peak"] = k["achieved_gbs"] / peak if k["achieved_gbs"] else None
     dom = max(kernels, key=lambda n: kernels[n]["ms"])
-    traffic = FT_DRAM_BYTES.get(dom, {}).get(n_local)
+    traffic = FT_DRAM_MODEL[dom][0] + FT_DRAM_MODEL[dom][1] * n_local if dom in FT_DRAM_MODEL else None
     roofline = {
         "bound": "hbm", "kernel": dom, "achieved": kernels[dom]["achieved_gbs"], "peak": peak, "unit": "GB/s",
         "frac": kernels[dom]["frac_of_hbm_peak"], "traffic": traffic, "peak_kind": f"of {peak_kind}",
