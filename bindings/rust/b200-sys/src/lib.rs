@@ -140,6 +140,16 @@ extern "C" {
     pub fn b200_exchange_export(net: *mut b200_net, handles: *mut c_void, bytes: i64) -> c_int;
     pub fn b200_exchange_import(net: *mut b200_net, rank: c_int, world: c_int, handles: *const c_void, bytes: i64) -> c_int;
     pub fn b200_update_exchange(net: *mut b200_net, lr: f32, grad_factor: f32) -> c_int;
+    pub fn b200_update_exchange_range(
+        net: *mut b200_net,
+        lr: f32,
+        grad_factor: f32,
+        first_float: i64,
+        n_floats: i64,
+        gather: c_int,
+        stream: *mut c_void,
+    ) -> c_int;
+    pub fn b200_grad_zero_range(net: *mut b200_net, first_float: i64, n_floats: i64) -> c_int;
     pub fn b200_backward_begin(net: *mut b200_net, slot: c_int) -> c_int;
     pub fn b200_backward_ft(net: *mut b200_net, slot: c_int, part: c_int, n_parts: c_int) -> c_int;
     pub fn b200_backward_end(net: *mut b200_net, slot: c_int) -> c_int;

@@ -74,6 +74,8 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(const __grid_constant__
 // stores the new p into every rank's parameter buffer with plain peer stores.  The leading
 // padding of the buffer carries the summed loss in float 0: its owner writes the reduced
 // value into every rank's parameter buffer, which does not use those floats.
+// With store_peers = 0 the new weights stay local: every rank then runs the SAME range and ends
+// up with the same values (used for the small tensors, which every rank needs at once).
 // The caller orders the launch between two cross-rank barriers: every rank's gradients
 // complete before, every rank's launch complete after.  Nothing in the kernel waits.
 constexpr int kMaxRanks = 8;
@@ -83,10 +85,13 @@ struct ExchangeArgs {
     const float4* g[kMaxRanks];  // gradient buffer of every rank, own included, by rank
     float4* p_out[kMaxRanks];    // parameter buffer of every rank
     int world;
+    int store_peers;             // 1: new weights go to every rank; 0: to this rank only (every rank runs the same range)
     long long head4;             // float4s of leading padding (the loss lives in the first)
 };
 
-__global__ void __launch_bounds__(256) adamw_exchange_kernel(const __grid_constant__ ExchangeArgs x) {
+// 128 threads and at most 64 registers: one such CTA still fits on an SM beside a 1024-thread
+// feature-transformer CTA, so the exchange can run under those kernels instead of in their place.
+__global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_constant__ ExchangeArgs x) {
     const AdamArgs& a = x.adam;
     for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < a.total4; j += (long long)gridDim.x * blockDim.x) {
         const long long i = a.first4 + j;
@@ -117,9 +122,13 @@ __global__ void __launch_bounds__(256) adamw_exchange_kernel(const __grid_consta
             a.m[i] = m;
             a.v[i] = v;
         }
+        if (x.store_peers) {
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; r++)
-            if (r < x.world) x.p_out[r][i] = p;
+            for (int r = 0; r < kMaxRanks; r++)
+                if (r < x.world) x.p_out[r][i] = p;
+        } else {
+            a.p[i] = p;
+        }
     }
 }
 

@@ -119,6 +119,7 @@ struct b200_net {
     float* peer_g[b200::kMaxRanks] = {};
     float* peer_p[b200::kMaxRanks] = {};
     bool loss_in_param = false;  // the last update left the summed loss in P[0] instead of G[0]
+    bool manual_grad_zero = false;  // the caller zeroes the gradient buffer range by range (b200_grad_zero_range)
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
     int last_n = 0;
@@ -479,6 +480,35 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
     return 0;
 }
 
+// Weight and bias gradients of every dense layer.  They need the forward pass and the loss
+// gradient only, so they run before the feature-transformer backward: once that ends, every
+// gradient outside l0w is complete as well.
+int launch_dense_grads(b200_net* net, Slot& s) {
+    const b200_net_desc& d = net->d;
+    if (net->d.n_dense > 1) {  // the narrow layers' weight and bias gradients, one launch
+        b200::SmallGradArgs g{};
+        g.order = s.dev<int>(s.off_order);
+        g.tiles = s.dev<int2>(s.off_dtiles);
+        g.buckets = s.dev<int>(s.off_buckets);
+        g.O = d.n_out_buckets;
+        g.n_layers = d.n_dense - 1;
+        for (int l = 1; l < d.n_dense; l++) {
+            char name[8];
+            g.K[l - 1] = d.dense_out[l - 1];
+            g.M[l - 1] = d.dense_out[l];
+            g.X[l - 1] = l == 1 ? net->a1 : net->a2;
+            g.dY[l - 1] = net->dz[l];
+            snprintf(name, sizeof name, "l%dw", l + 1);
+            g.gW[l - 1] = net->G + net->find(name)->off;
+            snprintf(name, sizeof name, "l%db", l + 1);
+            g.gB[l - 1] = net->G + net->find(name)->off;
+        }
+        b200::dense_small_grads_kernel<<<s.n_dtiles, 256, 0, net->stream>>>(g);
+        LAUNCHED(net);
+    }
+    return launch_wgrad(net, s, 0);
+}
+
 }  // namespace
 
 extern "C" {
@@ -675,6 +705,10 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
         net->table_dirty = true;  // the gather forward reads the merged table, the tiled one does not keep it fresh
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "manual_grad_zero")) {
+        net->manual_grad_zero = value != 0;
         return 0;
     }
     if (!strcmp(key, "ft_bwd_wide")) {  // takes effect for batches uploaded afterwards
@@ -916,7 +950,8 @@ int b200_forward_begin(b200_net* net, int slot) {
     Slot& s = net->slots[slot];
     CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
     if (int rc = refresh_table(net)) return rc;
-    CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->stream));  // every gradient is accumulated with reductions
+    if (!net->manual_grad_zero)
+        CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->stream));  // every gradient is accumulated with reductions
     if (int rc = forward_prepare(net, s, true)) return rc;
     net->fwd_slot = slot;
     net->fwd_parts_done = 0;
@@ -977,6 +1012,7 @@ int b200_backward_begin(b200_net* net, int slot) {
         DISPATCH_M(d.dense_out[0], b200::dense_dx_kernel<MM><<<s.n_dtiles, 256, 0, net->stream>>>(da, net->dx));
         LAUNCHED(net);
     }
+    if (int rc = launch_dense_grads(net, s)) return rc;
     CK(cudaEventRecord(ev[3], net->stream));
     net->bwd_slot = slot;
     net->bwd_parts_done = 0;
@@ -1036,29 +1072,6 @@ int b200_backward_end(b200_net* net, int slot) {
         return b200::fail(B200_ERR_STATE, "backward_end: run b200_backward_begin and every b200_backward_ft part first");
     if (int rc = set_device(net)) return rc;
     Slot& s = net->slots[slot];
-    if (net->d.n_dense > 1) {  // the narrow layers' weight and bias gradients, one launch
-        const b200_net_desc& d = net->d;
-        b200::SmallGradArgs g{};
-        g.order = s.dev<int>(s.off_order);
-        g.tiles = s.dev<int2>(s.off_dtiles);
-        g.buckets = s.dev<int>(s.off_buckets);
-        g.O = d.n_out_buckets;
-        g.n_layers = d.n_dense - 1;
-        for (int l = 1; l < d.n_dense; l++) {
-            char name[8];
-            g.K[l - 1] = d.dense_out[l - 1];
-            g.M[l - 1] = d.dense_out[l];
-            g.X[l - 1] = l == 1 ? net->a1 : net->a2;
-            g.dY[l - 1] = net->dz[l];
-            snprintf(name, sizeof name, "l%dw", l + 1);
-            g.gW[l - 1] = net->G + net->find(name)->off;
-            snprintf(name, sizeof name, "l%db", l + 1);
-            g.gB[l - 1] = net->G + net->find(name)->off;
-        }
-        b200::dense_small_grads_kernel<<<s.n_dtiles, 256, 0, net->stream>>>(g);
-        LAUNCHED(net);
-    }
-    if (int rc = launch_wgrad(net, s, 0)) return rc;
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[6], net->stream));
     CK(cudaEventRecord(s.consumed, net->stream));
@@ -1171,20 +1184,22 @@ int b200_exchange_import(b200_net* net, int rank, int world, const void* handles
     return 0;
 }
 
-int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
+int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64_t first_float, int64_t n_floats, int gather,
+                               void* stream) {
     if (!net) return b200::fail(B200_ERR_ARG, "update_exchange: null net");
     if (!net->xch_world) return b200::fail(B200_ERR_STATE, "update_exchange: map the peers with b200_exchange_import first");
-    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_exchange: no gradients yet, call b200_backward first");
+    if (first_float < 0 || n_floats < 1 || first_float + n_floats > net->n_flat || first_float % 4 || n_floats % 4)
+        return b200::fail(B200_ERR_ARG, "update_exchange: [%lld, +%lld) is not a 4-float-aligned range of the flat buffer",
+                          (long long)first_float, (long long)n_floats);
     if (int rc = set_device(net)) return rc;
     b200::ExchangeArgs x{};
     b200::AdamArgs& a = x.adam;
-    const int64_t per = net->n_flat / net->xch_world;
     a.p = reinterpret_cast<float4*>(net->P);
     a.m = reinterpret_cast<float4*>(net->M);
     a.v = reinterpret_cast<float4*>(net->V);
     a.g = nullptr;
-    a.first4 = net->xch_rank * per / 4;
-    a.total4 = per / 4;
+    a.first4 = first_float / 4;
+    a.total4 = n_floats / 4;
     a.rate = lr;
     a.adj = grad_factor;
     a.nseg = (int)net->tensors.size();
@@ -1193,16 +1208,37 @@ int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
         a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
     }
     x.world = net->xch_world;
+    x.store_peers = gather ? 1 : 0;
     x.head4 = kAlignFloats / 4;
     for (int r = 0; r < x.world; r++) {
         x.g[r] = reinterpret_cast<const float4*>(net->peer_g[r]);
         x.p_out[r] = reinterpret_cast<float4*>(net->peer_p[r]);
     }
-    const long long blocks = std::min<long long>((a.total4 + 255) / 256, kSmCount * 8);
-    b200::adamw_exchange_kernel<<<(unsigned)blocks, 256, 0, net->stream>>>(x);
+    const long long blocks = std::min<long long>((a.total4 + 127) / 128, kSmCount * 8);
+    cudaStream_t on = stream ? static_cast<cudaStream_t>(stream) : net->stream;
+    b200::adamw_exchange_kernel<<<(unsigned)blocks, 128, 0, on>>>(x);
     LAUNCHED(net);
     net->table_dirty = true;
-    net->loss_in_param = true;
+    if (first_float == 0) net->loss_in_param = true;  // the range holds the loss: it now sits in P[0]
+    return 0;
+}
+
+int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
+    if (!net) return b200::fail(B200_ERR_ARG, "update_exchange: null net");
+    if (!net->xch_world) return b200::fail(B200_ERR_STATE, "update_exchange: map the peers with b200_exchange_import first");
+    if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_exchange: no gradients yet, call b200_backward first");
+    const int64_t per = net->n_flat / net->xch_world;
+    if (int rc = b200_update_exchange_range(net, lr, grad_factor, net->xch_rank * per, per, 1, nullptr)) return rc;
+    net->loss_in_param = true;  // rank 0's share starts with the loss and stores it to every rank
+    return 0;
+}
+
+int b200_grad_zero_range(b200_net* net, int64_t first_float, int64_t n_floats) {
+    if (!net) return b200::fail(B200_ERR_ARG, "grad_zero_range: null net");
+    if (first_float < 0 || n_floats < 1 || first_float + n_floats > net->n_flat)
+        return b200::fail(B200_ERR_ARG, "grad_zero_range: [%lld, +%lld) is outside the flat buffer", (long long)first_float, (long long)n_floats);
+    if (int rc = set_device(net)) return rc;
+    CK(cudaMemsetAsync(net->G + first_float, 0, (size_t)n_floats * 4, net->stream));
     return 0;
 }
 

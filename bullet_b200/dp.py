@@ -71,6 +71,7 @@ class DataParallelStep:
         self.shard = shard_optimiser and self.world > 1
         self.peer = peer_exchange and self.world > 1
         self.peer_error = None
+        self.peer_pipelined = False
         if self.peer:  # map every rank's gradient and parameter buffers into this process
             try:
                 mine = (engine.exchange_export(), engine.grad.numel())
@@ -96,10 +97,13 @@ class DataParallelStep:
                 self.shard = True
             else:
                 self._token = engine.grad.new_zeros(1)
-                self.shard, self.parts = True, 1  # momentum and velocity live sharded, as with shard_optimiser
-        self.pipelined = self.shard and self.parts > 1
+                self.shard = True  # momentum and velocity live sharded, as with shard_optimiser
+                self.peer_pipelined = self.parts > 1
+                if not self.peer_pipelined:
+                    self.parts = 1
+        self.pipelined = self.shard and self.parts > 1 and not self.peer
         self._gathers = None  # all-gathers of the previous step's weights, one per slice, still to be waited for
-        if self.pipelined:
+        if self.pipelined or self.peer_pipelined:
             self.l0w_first, n_l0w = engine.tensor_range("l0w")
             self.head_split = engine.tensor_range("l1b")[0]  # [0, split): loss, l0b, l0f; [split, l0w): the dense layers
             self.per_part = n_l0w // self.parts
@@ -107,6 +111,15 @@ class DataParallelStep:
                 raise ValueError("l0w does not split evenly into parts x ranks x 4 floats")
         elif self.shard and engine.grad.numel() % self.world:
             raise ValueError("the flat buffer does not split evenly over the ranks")
+        if self.peer_pipelined:
+            import torch
+
+            engine.set_option("manual_grad_zero", 1)  # peers read slices of the gradients while the next step runs
+            self._side = torch.cuda.Stream(priority=-1)
+            self._ev_bwd = [torch.cuda.Event() for _ in range(self.parts)]
+            self._ev_done = [torch.cuda.Event() for _ in range(self.parts)]
+            self._ev_head_ready, self._ev_head_free = torch.cuda.Event(), torch.cuda.Event()
+            self._in_flight = False
 
     def _sharded_step(self, slot: int, lr: float) -> None:
         """reduce-scatter the gradients, AdamW on this rank's 1/world of the flat buffer only,
@@ -140,6 +153,56 @@ class DataParallelStep:
         eng.update_exchange(lr, 1.0 / self.global_batch)
         dist.all_reduce(self._token, group=self.group)
         eng.update_end()
+
+    def _peer_pipelined_step(self, slot: int, lr: float) -> None:
+        """The peer exchange slice by slice of l0w, on a side stream, beside the kernels.
+
+        Compute stream: forward (slice p waits until last step's exchange of slice p is done on
+        every rank) -> dense layers, loss, dense gradients -> per slice: clear its gradients,
+        backward, mark.  Side stream, per slice, behind its mark: barrier, the exchange kernel on
+        this rank's share (peer loads, AdamW, peer stores), barrier.  The small tensors (loss, l0b,
+        l0f, dense layers) are complete after the last slice; every rank then sums them over all
+        ranks and updates them for itself (no stores to peers), ahead of the last slice's exchange
+        on the side stream, because the next forward needs them first."""
+        import torch
+
+        eng, dist, P, gf = self.engine, self.dist, self.parts, 1.0 / self.global_batch
+        cur, side = torch.cuda.current_stream(), self._side
+        share = self.per_part // self.world
+
+        def fenced(first, count, gather):  # on the side stream: barrier, kernel, barrier
+            dist.all_reduce(self._token, group=self.group)
+            eng.update_exchange_range(lr, gf, first, count, gather, side.cuda_stream)
+            dist.all_reduce(self._token, group=self.group)
+
+        eng.forward_begin(slot)
+        for p in range(P):
+            if self._in_flight:
+                cur.wait_event(self._ev_done[p])
+            eng.forward_ft(slot, p, P)
+        if self._in_flight:
+            cur.wait_event(self._ev_head_free)  # every rank has read the small tensors' gradients of the last step
+        eng.grad_zero_range(0, self.l0w_first)
+        eng.backward_begin(slot)
+        for p in range(P):
+            whole, mine = self._slice(p)
+            eng.grad_zero_range(whole.start, self.per_part)
+            eng.backward_ft(slot, p, P)
+            self._ev_bwd[p].record(cur)
+            with torch.cuda.stream(side):
+                side.wait_event(self._ev_bwd[p])
+                if p == P - 1:  # the small tensors first: complete now, and the next forward starts with them
+                    dist.all_reduce(self._token, group=self.group)
+                    eng.update_exchange_range(lr, gf, 0, self.l0w_first, False, side.cuda_stream)
+                    self._ev_head_ready.record(side)
+                fenced(mine.start, share, True)
+                if p == P - 1:
+                    self._ev_head_free.record(side)  # behind a barrier that follows every rank's read of them
+                self._ev_done[p].record(side)
+        eng.backward_end(slot)
+        cur.wait_event(self._ev_head_ready)
+        eng.update_end()
+        self._in_flight = True
 
     def _slice(self, part: int):
         """(whole slice, this rank's share of it) of l0w inside the flat buffers, as python slices."""
@@ -197,13 +260,19 @@ class DataParallelStep:
             for work in self._gathers:
                 work.wait()
             self._gathers = None
+        if self.peer_pipelined and self._in_flight:
+            import torch
+
+            for ev in self._ev_done + [self._ev_head_free]:
+                torch.cuda.current_stream().wait_event(ev)
+            self._in_flight = False
 
     def gather_state(self) -> None:
         """After sharded steps: make momentum and velocity complete on every rank."""
         if not self.shard:
             return
         self.finish()
-        if self.pipelined:
+        if self.pipelined or self.peer_pipelined:
             for buf in self.engine.state_buffers():
                 for p in range(self.parts):
                     whole, mine = self._slice(p)
@@ -216,6 +285,9 @@ class DataParallelStep:
 
     def step(self, slot: int, lr: float) -> None:
         eng, gf = self.engine, 1.0 / self.global_batch
+        if self.peer_pipelined:
+            self._peer_pipelined_step(slot, lr)
+            return
         if self.peer:
             self._peer_step(slot, lr)
             return
@@ -270,5 +342,5 @@ class NetEngine:
         self.state_buffers = lambda: [self._m, self._v]
         for name in ("backward", "update", "forward_begin", "forward_ft", "backward_begin", "backward_ft", "backward_end",
                      "grad_part", "update_range", "update_end", "tensor_range", "exchange_export", "exchange_import",
-                     "update_exchange"):
+                     "update_exchange", "update_exchange_range", "grad_zero_range", "set_option"):
             setattr(self, name, getattr(net, name))

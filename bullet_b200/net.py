@@ -119,6 +119,13 @@ class Net:
     def update_exchange(self, lr: float, grad_factor: float) -> None:
         _lib.check(self.lib.b200_update_exchange(self._h, lr, grad_factor))
 
+    def update_exchange_range(self, lr: float, grad_factor: float, first: int, count: int, gather: bool, stream: int = 0) -> None:
+        _lib.check(self.lib.b200_update_exchange_range(self._h, lr, grad_factor, first, count, int(gather),
+                                                       ctypes.c_void_p(stream or 0)))
+
+    def grad_zero_range(self, first: int, count: int) -> None:
+        _lib.check(self.lib.b200_grad_zero_range(self._h, first, count))
+
     def backward_begin(self, slot: int) -> None:
         _lib.check(self.lib.b200_backward_begin(self._h, slot))
 

@@ -143,6 +143,16 @@ int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
 int b200_exchange_export(b200_net* net, void* handles, int64_t bytes);
 int b200_exchange_import(b200_net* net, int rank, int world, const void* handles, int64_t bytes);
 int b200_update_exchange(b200_net* net, float lr, float grad_factor);
+/* The same kernel on any 4-float-aligned range, on `stream` (a cudaStream_t, NULL = the net's), for a
+ * host that exchanges slice by slice beside the backward and the next forward.  gather = 1: the range is
+ * this rank's own share of a slice; the new weights are stored to every rank.  gather = 0: every rank
+ * runs the same range and keeps the result to itself (the small tensors, which all ranks need at once).
+ * The same two barriers apply per launch.  b200_grad_zero_range clears a range of the gradient buffer
+ * on the net's stream; with b200_net_set_option("manual_grad_zero", 1) the library no longer clears the
+ * whole buffer at the start of a step, because peers may still be reading parts of it. */
+int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64_t first_float, int64_t n_floats, int gather,
+                               void* stream);
+int b200_grad_zero_range(b200_net* net, int64_t first_float, int64_t n_floats);
 
 /* The training forward pass in pieces, for a host that overlaps an exchange of freshly updated
  * weights with it (a sharded optimiser gathers l0w slice by slice): b200_forward_begin waits for

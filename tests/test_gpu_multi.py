@@ -3,7 +3,7 @@ network as a single GPU does on the whole batch.  Skipped on a box with one GPU.
 
 Forms: one all-reduce; reduce-scatter + sharded AdamW + all-gather; the same pipelined slice by
 slice with the gathers waited for by the next forward pass; the library's one-kernel exchange
-over peer memory (b200_update_exchange)."""
+over peer memory (b200_update_exchange), whole and slice by slice on a side stream."""
 import dataclasses
 import os
 import sys
@@ -17,8 +17,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 MODES = {"allreduce": dict(), "sharded": dict(shard_optimiser=True), "pipelined": dict(shard_optimiser=True, parts=4),
-         "allreduce_parts": dict(parts=4), "peer": dict(peer_exchange=True)}
-GLOBAL, STEPS, LR = 2048, 3, 1e-2
+         "allreduce_parts": dict(parts=4), "peer": dict(peer_exchange=True),
+         "peer_pipelined": dict(peer_exchange=True, parts=4)}
+GLOBAL, STEPS, LR = 2048, 4, 1e-2
 
 
 def _setup():
