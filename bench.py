@@ -391,8 +391,9 @@ def main():
     ap.add_argument("--ft-bwd-wide", type=int, default=None, help="tiled backward shape: 1 = 1024 threads, one CTA per SM")
     ap.add_argument("--dp-shard", type=int, default=1,
                     help="N > 1: 1 = reduce-scatter, AdamW on 1/N of the parameters per rank, all-gather; 0 = all-reduce")
-    ap.add_argument("--dp-peer", type=int, default=0,
-                    help="N > 1: 1 = the exchange as one library kernel over peer memory (reduce + AdamW + gather)")
+    ap.add_argument("--dp-peer", type=int, default=1,
+                    help="N > 1: 1 = the exchange as one library kernel over peer memory (reduce + AdamW + gather); "
+                         "0, or a box that refuses the peer mapping = NCCL collectives (--dp-shard)")
     ap.add_argument("--dp-parts", type=int, default=1,
                     help="N > 1: slices of l0w exchanged while the backward (and, with --dp-shard 1, the next forward) still runs")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="positions per timed CPU-oracle pass")

@@ -26,7 +26,7 @@ pub const B200_QUANT_I16: i32 = 2;
 pub const B200_QUANT_I32: i32 = 3;
 
 pub const B200_NUM_SLOTS: c_int = 3;
-pub const B200_IPC_HANDLE_BYTES: usize = 64;
+pub const B200_EXCHANGE_HANDLE_BYTES: usize = 192;
 pub const B200_OP_NOALLOC_MAX_POSITIONS: i32 = 16384;
 
 #[repr(C)]

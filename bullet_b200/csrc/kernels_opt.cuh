@@ -76,9 +76,62 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(const __grid_constant__
 // value into every rank's parameter buffer, which does not use those floats.
 // With store_peers = 0 the new weights stay local: every rank then runs the SAME range and ends
 // up with the same values (used for the small tensors, which every rank needs at once).
-// The caller orders the launch between two cross-rank barriers: every rank's gradients
-// complete before, every rank's launch complete after.  Nothing in the kernel waits.
+// The launch sits between two cross-rank fences: every rank's gradients complete before, every
+// rank's launch complete after.  Either the caller provides them (any tiny collective), or
+// wait_ready makes the kernel itself wait, bounded, for the peers' counters (see PeerFlags).
 constexpr int kMaxRanks = 8;
+
+// Cross-rank fences of the exchange, without a collective: every rank owns an array of counters
+// that its peers write with release stores over NVLink and that it polls locally.
+//   [kFlagReady + r]  rank r's gradients of step n are complete      (value n)
+//   [kFlagDone + r]   rank r's exchange kernel of step n has finished (value n)
+//   [kFlagTimeout]    a wait of this rank gave up
+// Every wait is bounded (about four seconds); when it gives up it raises the timeout word, which the
+// host reports with the step's loss, and the kernel carries on so that the stream never hangs.
+constexpr int kFlagReady = 0, kFlagDone = kMaxRanks, kFlagTimeout = 2 * kMaxRanks, kFlagInts = 2 * kMaxRanks + 8;
+constexpr long long kPeerWaitSpins = 20000000;
+
+struct PeerFlags {
+    int* flags[kMaxRanks];  // every rank's counter array, own included, by rank
+    int world, rank;
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Called by one thread: waits until every rank has written at least `value` at `base`.
+__device__ __forceinline__ bool peer_wait(const PeerFlags& f, int base, int value) {
+    int* mine = f.flags[f.rank];
+    long long spins = 0;  // one budget for all ranks together
+    for (int r = 0; r < f.world; r++) {
+        while (ld_acquire_sys(mine + base + r) < value) {
+            __nanosleep(200);
+            if (++spins > kPeerWaitSpins) {
+                atomicOr(mine + kFlagTimeout, 1);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Everything this rank's stream has done so far is complete: tell every rank.  grid = 1, block = 32.
+static __global__ void peer_signal_kernel(PeerFlags f, int base, int value) {
+    if ((int)threadIdx.x < f.world) {
+        __threadfence_system();
+        st_release_sys(f.flags[threadIdx.x] + base + f.rank, value);
+    }
+}
+// The stream goes on only after every rank has signalled `value` at `base` (or the wait gave up).
+static __global__ void peer_wait_kernel(PeerFlags f, int base, int value) {
+    if (threadIdx.x == 0) peer_wait(f, base, value);
+}
 
 struct ExchangeArgs {
     AdamArgs adam;               // local p, m, v; first4 / total4 = this rank's share; g unused
@@ -87,12 +140,18 @@ struct ExchangeArgs {
     int world;
     int store_peers;             // 1: new weights go to every rank; 0: to this rank only (every rank runs the same range)
     long long head4;             // float4s of leading padding (the loss lives in the first)
+    PeerFlags flags;
+    int wait_ready;              // > 0: every CTA first waits until all ranks signalled this value at kFlagReady
 };
 
 // 128 threads and at most 64 registers: one such CTA still fits on an SM beside a 1024-thread
 // feature-transformer CTA, so the exchange can run under those kernels instead of in their place.
 __global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_constant__ ExchangeArgs x) {
     const AdamArgs& a = x.adam;
+    if (x.wait_ready > 0) {
+        if (threadIdx.x == 0) peer_wait(x.flags, kFlagReady, x.wait_ready);
+        __syncthreads();
+    }
     for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < a.total4; j += (long long)gridDim.x * blockDim.x) {
         const long long i = a.first4 + j;
         float4 gr[kMaxRanks];

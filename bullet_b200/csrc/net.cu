@@ -118,7 +118,14 @@ struct b200_net {
     int xch_rank = -1, xch_world = 0;
     float* peer_g[b200::kMaxRanks] = {};
     float* peer_p[b200::kMaxRanks] = {};
+    int* xch_flags = nullptr;  // this rank's fence counters (kernels_opt.cuh: PeerFlags)
+    int* peer_flags[b200::kMaxRanks] = {};
+    int xch_step = 0;          // fenced exchanges issued so far
+    int xch_wait_ready = 0;    // value the next exchange launch waits for at kFlagReady (0: the caller fences)
+    bool xch_fenced_used = false;
+    int* h_xstatus = nullptr;  // pinned ring beside h_status: the fence timeout word per update
     bool loss_in_param = false;  // the last update left the summed loss in P[0] instead of G[0]
+    int exchange_ctas = 0;          // CTAs of a side-stream exchange launch (0: one per SM)
     bool manual_grad_zero = false;  // the caller zeroes the gradient buffer range by range (b200_grad_zero_range)
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
@@ -591,6 +598,9 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     for (int l = 0; l < 3; l++) rc = rc ? rc : dev_alloc(net, &net->dz[l], B * 32);
     rc = rc ? rc : dev_alloc(net, &net->out, B);
     rc = rc ? rc : dev_alloc(net, &net->w1g, (size_t)d.n_out_buckets * d.dense_out[0] * net->D1());
+    // the fence counters get an allocation of their own size class (2 MiB), so that its IPC handle maps exactly it
+    rc = rc ? rc : dev_alloc(net, &net->xch_flags, (size_t)(2 << 20) / sizeof(int));
+    if (!rc) cudaMemsetAsync(net->xch_flags, 0, (size_t)2 << 20, net->stream);
     if (net->tiled_ok) {
         // sized for whichever backward shape needs more: every block may end in a partly filled chunk
         size_t ent_total = 0, max_chunks = 0;
@@ -631,6 +641,8 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (cudaHostAlloc(&raw, 64, cudaHostAllocDefault) != cudaSuccess) return bail(b200::fail(B200_ERR_CUDA, "net_create: pinned alloc failed"));
     net->h_loss = static_cast<float*>(raw);
     net->h_status = reinterpret_cast<int*>(net->h_loss + 8);
+    net->h_xstatus = net->h_status + b200_net::kLossRing;
+    memset(net->h_loss, 0, 64);
     for (auto& e : net->loss_ev) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
     for (auto& ring : net->tev)
         for (auto& e : ring) cudaEventCreate(&e);
@@ -674,6 +686,7 @@ int b200_net_destroy(b200_net* net) {
         if (r != net->xch_rank) {
             if (net->peer_g[r]) cudaIpcCloseMemHandle(net->peer_g[r]);
             if (net->peer_p[r]) cudaIpcCloseMemHandle(net->peer_p[r]);
+            if (net->peer_flags[r]) cudaIpcCloseMemHandle(net->peer_flags[r]);
         }
     for (void* p : net->allocations) cudaFree(p);
     for (auto& s : net->slots) {
@@ -705,6 +718,10 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
         if (strcmp(key, "ft_bwd_mode")) net->ft_fwd_mode = (int)value;
         net->table_dirty = true;  // the gather forward reads the merged table, the tiled one does not keep it fresh
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "exchange_ctas")) {
+        net->exchange_ctas = (int)std::max<int64_t>(0, value);
         return 0;
     }
     if (!strcmp(key, "manual_grad_zero")) {
@@ -1136,12 +1153,13 @@ int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_
 
 int b200_exchange_export(b200_net* net, void* handles, int64_t bytes) {
     if (!net || !handles) return b200::fail(B200_ERR_ARG, "exchange_export: null argument");
-    static_assert(sizeof(cudaIpcMemHandle_t) == B200_IPC_HANDLE_BYTES, "handle size");
-    if (bytes < 2 * B200_IPC_HANDLE_BYTES) return b200::fail(B200_ERR_ARG, "exchange_export: %d bytes are needed", 2 * B200_IPC_HANDLE_BYTES);
+    static_assert(3 * sizeof(cudaIpcMemHandle_t) == B200_EXCHANGE_HANDLE_BYTES, "handle size");
+    if (bytes < B200_EXCHANGE_HANDLE_BYTES) return b200::fail(B200_ERR_ARG, "exchange_export: %d bytes are needed", B200_EXCHANGE_HANDLE_BYTES);
     if (int rc = set_device(net)) return rc;
-    cudaIpcMemHandle_t h[2];
+    cudaIpcMemHandle_t h[3];
     CK(cudaIpcGetMemHandle(&h[0], net->G));
     CK(cudaIpcGetMemHandle(&h[1], net->P));
+    CK(cudaIpcGetMemHandle(&h[2], net->xch_flags));
     memcpy(handles, h, sizeof h);
     return 0;
 }
@@ -1150,34 +1168,40 @@ int b200_exchange_import(b200_net* net, int rank, int world, const void* handles
     if (!net || !handles) return b200::fail(B200_ERR_ARG, "exchange_import: null argument");
     if (world < 2 || world > b200::kMaxRanks || rank < 0 || rank >= world)
         return b200::fail(B200_ERR_ARG, "exchange_import: rank %d of %d (at most %d ranks)", rank, world, b200::kMaxRanks);
-    if (bytes < (int64_t)world * 2 * B200_IPC_HANDLE_BYTES) return b200::fail(B200_ERR_ARG, "exchange_import: handles of %d ranks are needed", world);
+    if (bytes < (int64_t)world * B200_EXCHANGE_HANDLE_BYTES) return b200::fail(B200_ERR_ARG, "exchange_import: handles of %d ranks are needed", world);
     if (net->xch_world) return b200::fail(B200_ERR_STATE, "exchange_import: peers are already mapped");
     if (net->n_flat % (4 * world)) return b200::fail(B200_ERR_UNSUPPORTED, "exchange_import: the flat buffer does not split over %d ranks", world);
     if (int rc = set_device(net)) return rc;
     const cudaIpcMemHandle_t* h = static_cast<const cudaIpcMemHandle_t*>(handles);
+    auto unmap_all = [&]() {
+        for (int q = 0; q < world; q++)
+            if (q != rank) {
+                if (net->peer_g[q]) cudaIpcCloseMemHandle(net->peer_g[q]);
+                if (net->peer_p[q]) cudaIpcCloseMemHandle(net->peer_p[q]);
+                if (net->peer_flags[q]) cudaIpcCloseMemHandle(net->peer_flags[q]);
+            }
+        memset(net->peer_g, 0, sizeof net->peer_g);
+        memset(net->peer_p, 0, sizeof net->peer_p);
+        memset(net->peer_flags, 0, sizeof net->peer_flags);
+    };
     for (int r = 0; r < world; r++) {
         if (r == rank) {
             net->peer_g[r] = net->G;
             net->peer_p[r] = net->P;
+            net->peer_flags[r] = net->xch_flags;
             continue;
         }
-        void *g = nullptr, *p = nullptr;
-        cudaError_t e = cudaIpcOpenMemHandle(&g, h[2 * r], cudaIpcMemLazyEnablePeerAccess);
-        if (e == cudaSuccess) e = cudaIpcOpenMemHandle(&p, h[2 * r + 1], cudaIpcMemLazyEnablePeerAccess);
+        void* mapped[3] = {nullptr, nullptr, nullptr};
+        cudaError_t e = cudaSuccess;
+        for (int k = 0; k < 3 && e == cudaSuccess; k++) e = cudaIpcOpenMemHandle(&mapped[k], h[3 * r + k], cudaIpcMemLazyEnablePeerAccess);
+        net->peer_g[r] = static_cast<float*>(mapped[0]);
+        net->peer_p[r] = static_cast<float*>(mapped[1]);
+        net->peer_flags[r] = static_cast<int*>(mapped[2]);
         if (e != cudaSuccess) {
             cudaGetLastError();
-            if (g) cudaIpcCloseMemHandle(g);
-            for (int q = 0; q < r; q++)
-                if (q != rank) {
-                    cudaIpcCloseMemHandle(net->peer_g[q]);
-                    cudaIpcCloseMemHandle(net->peer_p[q]);
-                }
-            memset(net->peer_g, 0, sizeof net->peer_g);
-            memset(net->peer_p, 0, sizeof net->peer_p);
+            unmap_all();
             return b200::fail(B200_ERR_CUDA, "exchange_import: cannot map the buffers of rank %d: %s", r, cudaGetErrorString(e));
         }
-        net->peer_g[r] = static_cast<float*>(g);
-        net->peer_p[r] = static_cast<float*>(p);
     }
     net->xch_rank = rank;
     net->xch_world = world;
@@ -1210,11 +1234,19 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     x.world = net->xch_world;
     x.store_peers = gather ? 1 : 0;
     x.head4 = kAlignFloats / 4;
+    x.flags.world = net->xch_world;
+    x.flags.rank = net->xch_rank;
+    x.wait_ready = net->xch_wait_ready;
     for (int r = 0; r < x.world; r++) {
         x.g[r] = reinterpret_cast<const float4*>(net->peer_g[r]);
         x.p_out[r] = reinterpret_cast<float4*>(net->peer_p[r]);
+        x.flags.flags[r] = net->peer_flags[r];
     }
-    const long long blocks = std::min<long long>((a.total4 + 127) / 128, kSmCount * 8);
+    // On the net's own stream the kernel runs alone and takes the whole device.  On a caller's side
+    // stream it runs beside the feature-transformer kernels, whose CTAs leave room for exactly one
+    // such CTA per SM: more CTAs would take whole SMs away from them instead of filling the gaps.
+    const long long cap = stream ? (net->exchange_ctas > 0 ? net->exchange_ctas : kSmCount) : kSmCount * 8;
+    const long long blocks = std::min<long long>((a.total4 + 127) / 128, cap);
     cudaStream_t on = stream ? static_cast<cudaStream_t>(stream) : net->stream;
     b200::adamw_exchange_kernel<<<(unsigned)blocks, 128, 0, on>>>(x);
     LAUNCHED(net);
@@ -1228,8 +1260,27 @@ int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
     if (!net->xch_world) return b200::fail(B200_ERR_STATE, "update_exchange: map the peers with b200_exchange_import first");
     if (!net->have_backward) return b200::fail(B200_ERR_STATE, "update_exchange: no gradients yet, call b200_backward first");
     const int64_t per = net->n_flat / net->xch_world;
-    if (int rc = b200_update_exchange_range(net, lr, grad_factor, net->xch_rank * per, per, 1, nullptr)) return rc;
+    if (int rc = set_device(net)) return rc;
+    // fences without a collective: tell the peers that this rank's gradients are complete; the exchange
+    // kernel waits for every peer's word before it reads; afterwards the same once more for "finished",
+    // so that nobody overwrites gradients or reads weights while a peer's kernel is still at work
+    b200::PeerFlags f{};
+    f.world = net->xch_world;
+    f.rank = net->xch_rank;
+    for (int r = 0; r < f.world; r++) f.flags[r] = net->peer_flags[r];
+    const int step = ++net->xch_step;
+    b200::peer_signal_kernel<<<1, 32, 0, net->stream>>>(f, b200::kFlagReady, step);
+    LAUNCHED(net);
+    net->xch_wait_ready = step;
+    int rc = b200_update_exchange_range(net, lr, grad_factor, net->xch_rank * per, per, 1, nullptr);
+    net->xch_wait_ready = 0;
+    if (rc) return rc;
+    b200::peer_signal_kernel<<<1, 32, 0, net->stream>>>(f, b200::kFlagDone, step);
+    LAUNCHED(net);
+    b200::peer_wait_kernel<<<1, 32, 0, net->stream>>>(f, b200::kFlagDone, step);
+    LAUNCHED(net);
     net->loss_in_param = true;  // rank 0's share starts with the loss and stores it to every rank
+    net->xch_fenced_used = true;
     return 0;
 }
 
@@ -1255,6 +1306,8 @@ int b200_update_end(b200_net* net) {
     } else {
         net->h_status[ring] = 0;
     }
+    if (net->xch_fenced_used)
+        CK(cudaMemcpyAsync(net->h_xstatus + ring, net->xch_flags + b200::kFlagTimeout, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
     CK(cudaEventRecord(net->loss_ev[ring], net->stream));
     net->updates++;
     if (int rc = refresh_table(net)) return rc;
@@ -1303,6 +1356,10 @@ int b200_loss_of(b200_net* net, int steps_back, float* loss_sum) {
     const int ring = (int)((net->updates - 1 - steps_back) % b200_net::kLossRing);
     CK(cudaEventSynchronize(net->loss_ev[ring]));
     *loss_sum = net->h_loss[ring];
+    if (net->h_xstatus[ring]) {
+        net->h_xstatus[ring] = 0;
+        return b200::fail(B200_ERR_STATE, "data-parallel exchange: a peer did not reach the fence in time; the update of this step is not valid");
+    }
     if (net->h_status[ring] & b200::kStatusOutsideBlock) {
         net->h_status[ring] = 0;
         return b200::fail(B200_ERR_DATA,

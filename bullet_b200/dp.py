@@ -16,7 +16,7 @@ With `shard_optimiser` the all-reduce becomes a reduce-scatter, AdamW on this ra
 the buffer and an all-gather of the weights: the same bytes on the wire, 1/world of the
 optimiser traffic.  With `peer_exchange` those three steps are ONE kernel of the library over peer memory
 (`b200_update_exchange`: peer loads of every rank's gradients, AdamW on this rank's share, peer
-stores of the new weights to every rank), fenced by two tiny all-reduces.
+stores of the new weights to every rank), fenced by counters the ranks write into each other's memory.
 With `shard_optimiser` and `parts > 1` together the three are pipelined
 slice by slice of l0w AND across steps: the reduce-scatter of a slice travels under the
 backward of the next, and the all-gather of its updated weights is only waited for by the
@@ -145,13 +145,11 @@ class DataParallelStep:
 
     def _peer_step(self, slot: int, lr: float) -> None:
         """The exchange as one kernel over peer memory: gradients summed with peer loads, AdamW on
-        this rank's share, new weights stored to every rank.  The two tiny all-reduces are barriers
-        on the stream: all gradients complete before the kernel, all stores landed after it."""
-        eng, dist = self.engine, self.dist
+        this rank's share, new weights stored to every rank.  The library fences the kernel itself
+        (counters exchanged with the peers), so no collective runs in the step at all."""
+        eng = self.engine
         eng.backward(slot)
-        dist.all_reduce(self._token, group=self.group)
         eng.update_exchange(lr, 1.0 / self.global_batch)
-        dist.all_reduce(self._token, group=self.group)
         eng.update_end()
 
     def _peer_pipelined_step(self, slot: int, lr: float) -> None:

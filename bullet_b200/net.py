@@ -109,8 +109,8 @@ class Net:
 
     # the data-parallel update over peer memory (see include/bullet_b200.h)
     def exchange_export(self) -> bytes:
-        buf = ctypes.create_string_buffer(128)
-        _lib.check(self.lib.b200_exchange_export(self._h, buf, 128))
+        buf = ctypes.create_string_buffer(192)
+        _lib.check(self.lib.b200_exchange_export(self._h, buf, 192))
         return buf.raw
 
     def exchange_import(self, rank: int, world: int, handles: bytes) -> None:

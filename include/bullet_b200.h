@@ -129,17 +129,19 @@ int b200_update(b200_net* net, float lr, float grad_factor);
 int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
 
 /* The data-parallel update over peer memory, one process per GPU of one box (new; the reference is
- * single-GPU).  b200_exchange_export writes two CUDA IPC handles (gradient buffer, parameter
- * buffer; 2 * B200_IPC_HANDLE_BYTES bytes); the host gathers the handles of all ranks, in rank
- * order, and hands them to b200_exchange_import, which maps every peer's buffers (at most 8 ranks;
- * the flat buffer must split into world x 4 floats).  b200_update_exchange then replaces the
+ * single-GPU).  b200_exchange_export writes three CUDA IPC handles (gradient buffer, parameter buffer,
+ * fence counters; B200_EXCHANGE_HANDLE_BYTES bytes); the host gathers the handles of all ranks, in
+ * rank order, and hands them to b200_exchange_import, which maps every peer's buffers (at most 8
+ * ranks; the flat buffer must split into world x 4 floats).  b200_update_exchange then replaces the
  * all-reduce + b200_update pair: ONE kernel sums this rank's 1/world share of the gradients over all
  * ranks with peer loads, applies AdamW+clip to it and stores the new weights into every rank's
  * parameter buffer (reduce-scatter + AdamW + all-gather).  Momentum and velocity stay sharded.
- * The caller must order it between two cross-rank barriers on the stream (any tiny collective):
- * all ranks' b200_backward complete before it starts, all ranks' b200_update_exchange complete
- * before anyone touches weights or gradients again; b200_update_end follows as usual. */
-#define B200_IPC_HANDLE_BYTES 64
+ * It fences itself: small kernels around it exchange counters with the peers (release stores over
+ * NVLink, bounded local polling), so every rank's b200_backward is complete before its gradients are
+ * read and every rank's kernel has finished before anyone goes on.  All ranks must call it the same
+ * number of times.  A peer that does not arrive within about four seconds makes the wait give up: the
+ * stream carries on and b200_loss reports B200_ERR_STATE for that step.  b200_update_end follows as usual. */
+#define B200_EXCHANGE_HANDLE_BYTES 192
 int b200_exchange_export(b200_net* net, void* handles, int64_t bytes);
 int b200_exchange_import(b200_net* net, int rank, int world, const void* handles, int64_t bytes);
 int b200_update_exchange(b200_net* net, float lr, float grad_factor);
@@ -147,7 +149,8 @@ int b200_update_exchange(b200_net* net, float lr, float grad_factor);
  * host that exchanges slice by slice beside the backward and the next forward.  gather = 1: the range is
  * this rank's own share of a slice; the new weights are stored to every rank.  gather = 0: every rank
  * runs the same range and keeps the result to itself (the small tensors, which all ranks need at once).
- * The same two barriers apply per launch.  b200_grad_zero_range clears a range of the gradient buffer
+ * This form does NOT fence itself: the caller orders every launch between two cross-rank barriers on
+ * `stream` (any tiny collective).  b200_grad_zero_range clears a range of the gradient buffer
  * on the net's stream; with b200_net_set_option("manual_grad_zero", 1) the library no longer clears the
  * whole buffer at the start of a step, because peers may still be reading parts of it. */
 int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64_t first_float, int64_t n_floats, int gather,

@@ -111,10 +111,10 @@ class OracleEngine:
 
     # ---- the one-kernel exchange over peer memory, emulated with collectives: what it must compute
     def exchange_export(self):
-        return bytes(128)
+        return bytes(192)
 
     def exchange_import(self, rank, world, handles):
-        assert len(handles) == 128 * world
+        assert len(handles) == 192 * world
         self.xch = (rank, world)
 
     def update_exchange(self, lr, grad_factor):
