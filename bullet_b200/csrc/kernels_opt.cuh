@@ -89,11 +89,12 @@ constexpr int kMaxRanks = 8;
 // Every wait is bounded (about four seconds); when it gives up it raises the timeout word, which the
 // host reports with the step's loss, and the kernel carries on so that the stream never hangs.
 constexpr int kFlagReady = 0, kFlagDone = kMaxRanks, kFlagTimeout = 2 * kMaxRanks, kFlagInts = 2 * kMaxRanks + 8;
-constexpr long long kPeerWaitSpins = 20000000;
+constexpr long long kPeerWaitSpins = 20000000;  // default spin_limit
 
 struct PeerFlags {
     int* flags[kMaxRanks];  // every rank's counter array, own included, by rank
     int world, rank;
+    long long spin_limit;   // polls (each at least 200 ns apart) before a wait gives up
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -112,7 +113,7 @@ __device__ __forceinline__ bool peer_wait(const PeerFlags& f, int base, int valu
     for (int r = 0; r < f.world; r++) {
         while (ld_acquire_sys(mine + base + r) < value) {
             __nanosleep(200);
-            if (++spins > kPeerWaitSpins) {
+            if (++spins > f.spin_limit) {
                 atomicOr(mine + kFlagTimeout, 1);
                 return false;
             }

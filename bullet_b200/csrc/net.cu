@@ -121,6 +121,7 @@ struct b200_net {
     int* xch_flags = nullptr;  // this rank's fence counters (kernels_opt.cuh: PeerFlags)
     int* peer_flags[b200::kMaxRanks] = {};
     int xch_step = 0;          // fenced exchanges issued so far
+    long long xch_spin_limit = b200::kPeerWaitSpins;
     int xch_wait_ready = 0;    // value the next exchange launch waits for at kFlagReady (0: the caller fences)
     bool xch_fenced_used = false;
     int* h_xstatus = nullptr;  // pinned ring beside h_status: the fence timeout word per update
@@ -720,6 +721,10 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
         if (strcmp(key, "ft_fwd_mode")) net->ft_bwd_mode = (int)value;
         return 0;
     }
+    if (!strcmp(key, "exchange_wait_ms")) {  // how long a fence of the peer exchange polls before it gives up
+        net->xch_spin_limit = std::max<int64_t>(1, value) * 5000;
+        return 0;
+    }
     if (!strcmp(key, "exchange_ctas")) {
         net->exchange_ctas = (int)std::max<int64_t>(0, value);
         return 0;
@@ -1236,6 +1241,7 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     x.head4 = kAlignFloats / 4;
     x.flags.world = net->xch_world;
     x.flags.rank = net->xch_rank;
+    x.flags.spin_limit = net->xch_spin_limit;
     x.wait_ready = net->xch_wait_ready;
     for (int r = 0; r < x.world; r++) {
         x.g[r] = reinterpret_cast<const float4*>(net->peer_g[r]);
@@ -1267,6 +1273,7 @@ int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
     b200::PeerFlags f{};
     f.world = net->xch_world;
     f.rank = net->xch_rank;
+    f.spin_limit = net->xch_spin_limit;
     for (int r = 0; r < f.world; r++) f.flags[r] = net->peer_flags[r];
     const int step = ++net->xch_step;
     b200::peer_signal_kernel<<<1, 32, 0, net->stream>>>(f, b200::kFlagReady, step);

@@ -100,3 +100,56 @@ def test_every_exchange_form_matches_one_gpu(tmp_path):
             assert np.array_equal(r0[f"{mode}/w/{k}"], r1[f"{mode}/w/{k}"]), f"{mode}: replicas differ in {k}"
             assert rel(r0[f"{mode}/w/{k}"], w_ref[k]) <= 1e-5, (mode, k)
         assert np.array_equal(r0[f"{mode}/m/l0w"], r1[f"{mode}/m/l0w"]) and rel(r0[f"{mode}/m/l0w"], m_ref) <= 1e-4, mode
+
+
+def _late_peer_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from bullet_b200 import synth
+    from bullet_b200._lib import B200Error
+    from bullet_b200.dp import DataParallelStep, NetEngine, shard_batch
+    from bullet_b200.net import Net, featurise
+
+    c, desc = _setup()
+    batch = shard_batch(featurise(c.game, synth.records(c.game, GLOBAL, seed=5), desc), rank, world)
+    stream = torch.cuda.Stream()
+    result = "no error"
+    with torch.cuda.stream(stream):
+        net = Net(dataclasses.replace(desc, max_batch=GLOBAL // world), device=rank, stream=stream.cuda_stream)
+        net.load_weights(synth.init_weights(desc, seed=3))
+        net.set_option("exchange_wait_ms", 200)
+        dp = DataParallelStep(NetEngine(net, torch.device("cuda", rank)), GLOBAL, peer_exchange=True)
+        assert dp.peer
+        net.upload(0, *batch)
+        dp.step(0, LR)
+        first = net.loss()                      # both ranks arrive: fine
+        if rank == 0:                           # rank 1 never starts this step: rank 0's fences run out
+            dp.step(0, LR)
+            try:
+                net.loss()
+            except B200Error as e:
+                result = f"{e.code} {e}"
+        net.sync()
+        torch.cuda.synchronize()
+        dist.barrier()                          # rank 1 waits here, on the host, with nothing in flight
+        net.close()
+    with open(os.path.join(out_dir, f"late{rank}.txt"), "w") as f:
+        f.write(f"{first}\n{result}\n")
+    dist.destroy_process_group()
+
+
+def test_a_peer_that_never_arrives_is_reported_not_waited_for_forever(tmp_path):
+    """The fences of the peer exchange give up after their limit and the host sees it with the loss."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    port = 29500 + (os.getpid() + 13) % 2000
+    mp.spawn(_late_peer_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = open(tmp_path / "late0.txt").read().splitlines()
+    r1 = open(tmp_path / "late1.txt").read().splitlines()
+    assert float(r0[0]) == float(r1[0]) > 0
+    assert r0[1].startswith("-2") and "did not reach the fence" in r0[1]
+    assert r1[1] == "no error"
