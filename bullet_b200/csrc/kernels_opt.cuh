@@ -147,47 +147,63 @@ struct ExchangeArgs {
 
 // 128 threads and at most 64 registers: one such CTA still fits on an SM beside a 1024-thread
 // feature-transformer CTA, so the exchange can run under those kernels instead of in their place.
+// WORLD > 0 fixes the number of ranks at compile time; a thread then takes 8 / WORLD float4s per
+// round, so that about eight 16-byte loads per thread are in flight over NVLink whatever the
+// number of ranks (remote latency is microseconds).  WORLD = 0: any number of ranks up to 8.
+template <int WORLD>
 __global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_constant__ ExchangeArgs x) {
+    constexpr int W = WORLD > 0 ? WORLD : kMaxRanks;  // loads held per element
+    constexpr int U = WORLD > 0 ? kMaxRanks / WORLD : 1;  // elements per thread and round
     const AdamArgs& a = x.adam;
     if (x.wait_ready > 0) {
         if (threadIdx.x == 0) peer_wait(x.flags, kFlagReady, x.wait_ready);
         __syncthreads();
     }
-    for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < a.total4; j += (long long)gridDim.x * blockDim.x) {
-        const long long i = a.first4 + j;
-        float4 gr[kMaxRanks];
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long j0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; j0 < a.total4; j0 += stride * U) {
+        float4 gr[U][W];
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; r++)
-            if (r < x.world) gr[r] = x.g[r][i];  // all loads in flight before the first add
-        float4 g = gr[0];
+        for (int u = 0; u < U; u++) {
+            const long long j = j0 + u * stride;
 #pragma unroll
-        for (int r = 1; r < kMaxRanks; r++)
-            if (r < x.world) g.x += gr[r].x, g.y += gr[r].y, g.z += gr[r].z, g.w += gr[r].w;
-        int si = -1;
-#pragma unroll 1
-        for (int k = 0; k < a.nseg; k++)
-            if (i >= a.seg[k].begin4 && i < a.seg[k].end4) si = k;
-        float4 p;
-        if (si < 0) {
-            if (i >= x.head4) continue;  // alignment padding between tensors
-            p = g;                       // the summed loss (and zeros)
-        } else {
-            const AdamSegment& s = a.seg[si];
-            p = a.p[i];
-            float4 m = a.m[i], v = a.v[i];
-            adam_op(s, a.rate, a.adj * g.x, p.x, m.x, v.x);
-            adam_op(s, a.rate, a.adj * g.y, p.y, m.y, v.y);
-            adam_op(s, a.rate, a.adj * g.z, p.z, m.z, v.z);
-            adam_op(s, a.rate, a.adj * g.w, p.w, m.w, v.w);
-            a.m[i] = m;
-            a.v[i] = v;
+            for (int r = 0; r < W; r++)
+                if (j < a.total4 && r < x.world) gr[u][r] = x.g[r][a.first4 + j];  // all loads in flight before the first add
         }
-        if (x.store_peers) {
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; r++)
-                if (r < x.world) x.p_out[r][i] = p;
-        } else {
-            a.p[i] = p;
+        for (int u = 0; u < U; u++) {
+            const long long j = j0 + u * stride;
+            if (j >= a.total4) break;
+            const long long i = a.first4 + j;
+            float4 g = gr[u][0];
+#pragma unroll
+            for (int r = 1; r < W; r++)
+                if (r < x.world) g.x += gr[u][r].x, g.y += gr[u][r].y, g.z += gr[u][r].z, g.w += gr[u][r].w;
+            int si = -1;
+#pragma unroll 1
+            for (int k = 0; k < a.nseg; k++)
+                if (i >= a.seg[k].begin4 && i < a.seg[k].end4) si = k;
+            float4 p;
+            if (si < 0) {
+                if (i >= x.head4) continue;  // alignment padding between tensors
+                p = g;                       // the summed loss (and zeros)
+            } else {
+                const AdamSegment& s = a.seg[si];
+                p = a.p[i];
+                float4 m = a.m[i], v = a.v[i];
+                adam_op(s, a.rate, a.adj * g.x, p.x, m.x, v.x);
+                adam_op(s, a.rate, a.adj * g.y, p.y, m.y, v.y);
+                adam_op(s, a.rate, a.adj * g.z, p.z, m.z, v.z);
+                adam_op(s, a.rate, a.adj * g.w, p.w, m.w, v.w);
+                a.m[i] = m;
+                a.v[i] = v;
+            }
+            if (x.store_peers) {
+#pragma unroll
+                for (int r = 0; r < W; r++)
+                    if (r < x.world) x.p_out[r][i] = p;
+            } else {
+                a.p[i] = p;
+            }
         }
     }
 }

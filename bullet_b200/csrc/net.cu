@@ -1254,7 +1254,12 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     const long long cap = stream ? (net->exchange_ctas > 0 ? net->exchange_ctas : kSmCount) : kSmCount * 8;
     const long long blocks = std::min<long long>((a.total4 + 127) / 128, cap);
     cudaStream_t on = stream ? static_cast<cudaStream_t>(stream) : net->stream;
-    b200::adamw_exchange_kernel<<<(unsigned)blocks, 128, 0, on>>>(x);
+    switch (x.world) {
+        case 2: b200::adamw_exchange_kernel<2><<<(unsigned)blocks, 128, 0, on>>>(x); break;
+        case 4: b200::adamw_exchange_kernel<4><<<(unsigned)blocks, 128, 0, on>>>(x); break;
+        case 8: b200::adamw_exchange_kernel<8><<<(unsigned)blocks, 128, 0, on>>>(x); break;
+        default: b200::adamw_exchange_kernel<0><<<(unsigned)blocks, 128, 0, on>>>(x); break;
+    }
     LAUNCHED(net);
     net->table_dirty = true;
     if (first_float == 0) net->loss_in_param = true;  // the range holds the loss: it now sits in P[0]
