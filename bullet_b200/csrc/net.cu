@@ -48,7 +48,6 @@
 namespace {
 
 constexpr int kSmCount = 148;
-constexpr int kTargetCtas = 4 * kSmCount;  // two resident CTAs per SM, two waves
 constexpr int64_t kAlignFloats = 64;       // 256-byte tensor alignment in the flat buffers
 constexpr int kMinItemPairs = 128;         // a forward work item serves at least this many pairs per tile load
 
@@ -363,7 +362,7 @@ b200::DenseArgs dense_args(b200_net* net, const Slot& s, bool want_grad) {
     for (int l = 0; l < d.n_dense; l++) {
         a.M[l] = d.dense_out[l];
         a.act[l] = d.dense_act[l];
-        char name[8];
+        char name[16];
         snprintf(name, sizeof name, "l%dw", l + 1);
         a.W[l] = net->P + net->find(name)->off;
         snprintf(name, sizeof name, "l%db", l + 1);
@@ -462,7 +461,7 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
     w.n = s.n;
     w.K = net->dense_in(layer);
     w.O = d.n_out_buckets;
-    char name[8];
+    char name[16];
     snprintf(name, sizeof name, "l%dw", layer + 1);
     w.gW = net->G + net->find(name)->off;
     snprintf(name, sizeof name, "l%db", layer + 1);
@@ -501,7 +500,7 @@ int launch_dense_grads(b200_net* net, Slot& s) {
         g.O = d.n_out_buckets;
         g.n_layers = d.n_dense - 1;
         for (int l = 1; l < d.n_dense; l++) {
-            char name[8];
+            char name[16];
             g.K[l - 1] = d.dense_out[l - 1];
             g.M[l - 1] = d.dense_out[l];
             g.X[l - 1] = l == 1 ? net->a1 : net->a2;
@@ -562,7 +561,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     add("l0b", d.ft_out, 1);
     if (d.factoriser_rows) add("l0f", d.ft_out, d.factoriser_rows);
     for (int l = 0; l < d.n_dense; l++) {
-        char name[8];
+        char name[16];
         const int64_t rows = (int64_t)d.n_out_buckets * d.dense_out[l];
         snprintf(name, sizeof name, "l%db", l + 1);
         add(name, rows, 1);
