@@ -495,8 +495,8 @@ __global__ void __launch_bounds__(256, (M1 > 16 ? 1 : 2)) dense_dx_kernel(DenseA
 // reduce over the batch for the bias: model/builder.rs:263-267).
 // Positions are visited in bucket-sorted order (`order`), so a thread keeps M running sums
 // for the current bucket and flushes them with atomics only when the bucket changes.
-// A thread owns four neighbouring columns (one 16-byte load of x per position); the thread
-// after the last column owns the bias.  grid = (ceil((K/4 + 1) / 128), chunks), block = 128.
+// A thread owns four neighbouring columns (16 bytes of x per position, prefetched eight positions
+// ahead through shared memory); the thread after the last column owns the bias.  grid = (ceil((K/4 + 1) / 128), chunks), block = 128.
 struct WgradArgs {
     const float* X;      // [n][K]
     const float* dY;     // [n][M]
@@ -543,6 +543,11 @@ __global__ void __launch_bounds__(128) dense_wgrad_kernel(WgradArgs a) {
             }
         }
     };
+    // x reaches the thread through a private ring of D shared-memory slots filled by cp.async:
+    // D positions' loads stay in flight at no register cost, so HBM latency hides behind the FMAs
+    constexpr int D = 8;
+    __shared__ float4 s_x[D][128];
+    float4* my_slot = &s_x[0][threadIdx.x];
     for (int base = begin; base < end; base += S) {
         const int cnt = min(S, end - base);
         __syncthreads();
@@ -553,33 +558,30 @@ __global__ void __launch_bounds__(128) dense_wgrad_kernel(WgradArgs a) {
         }
         __syncthreads();
         for (int i = threadIdx.x; i < cnt * M; i += blockDim.x) s_dy[i / M][i % M] = a.dY[(size_t)s_pos[i / M] * M + i % M];
+#pragma unroll
+        for (int u = 0; u < D; u++) {
+            if (u < cnt && is_col) dense_cp_async16(my_slot + u * 128, a.X + (size_t)s_pos[u] * a.K + c);
+            dense_cp_commit();
+        }
         __syncthreads();
-        for (int j0 = 0; j0 < cnt; j0 += 4) {  // four positions' loads in flight per thread
-            float4 xv[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int j = j0 + u;
-                xv[u] = make_float4(is_bias ? 1.f : 0.f, 0.f, 0.f, 0.f);  // the bias "column" sees x = 1
-                if (j < cnt && is_col) xv[u] = __ldg(reinterpret_cast<const float4*>(a.X + (size_t)s_pos[j] * a.K + c));
+        for (int j = 0; j < cnt; j++) {
+            dense_cp_wait<D - 1>();  // position j's 16 bytes have landed
+            const float4 xv = is_col ? my_slot[(j & (D - 1)) * 128] : make_float4(is_bias ? 1.f : 0.f, 0.f, 0.f, 0.f);  // the bias "column" sees x = 1
+            const int k = s_bucket[j];
+            if (k != cur) {
+                flush();
+                cur = k;
             }
+            const float xs[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int j = j0 + u;
-                if (j < cnt) {
-                    const int k = s_bucket[j];
-                    if (k != cur) {
-                        flush();
-                        cur = k;
-                    }
-                    const float xs[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+            for (int r = 0; r < M; r++) {
+                const float dy = s_dy[j][r];
 #pragma unroll
-                    for (int r = 0; r < M; r++) {
-                        const float dy = s_dy[j][r];
-#pragma unroll
-                        for (int q = 0; q < 4; q++) acc[q][r] += dy * xs[q];
-                    }
-                }
+                for (int q = 0; q < 4; q++) acc[q][r] += dy * xs[q];
             }
+            // refill the slot just read (after its value has been used) with position j + D
+            if (j + D < cnt && is_col) dense_cp_async16(my_slot + (j & (D - 1)) * 128, a.X + (size_t)s_pos[j + D] * a.K + c);
+            dense_cp_commit();
         }
     }
     flush();
