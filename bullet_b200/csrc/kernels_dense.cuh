@@ -38,6 +38,11 @@ struct DenseArgs {
     float* out;        // [n] network output
     float* loss;       // scalar, accumulated
     int want_grad;
+    // the register-tiled forward also forms the weight and bias gradients of the layers after the
+    // first (it holds everything they need in shared memory): gradient tensors of layers 2 and 3
+    int fuse_small;
+    float* gW[3];
+    float* gB[3];
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -290,7 +295,8 @@ __global__ void __launch_bounds__(256, 2) dense_forward_tile_kernel(DenseArgs a)
     constexpr int kStageFloats = kDenseChunk * M1 + kDenseTile * XS;
     static_assert(8 * kDenseTile * M1 <= kDenseStages * kStageFloats, "partial sums reuse the stage buffers");
     extern __shared__ __align__(16) float dense_smem[];
-    __shared__ float s_w2[M1][33], s_b2[32], s_w3[32], s_a1[kDenseTile][M1], s_dz2[8][32], loss_part[8];
+    __shared__ float s_w2[M1][33], s_b2[32], s_w3[32], s_a1[kDenseTile][M1], loss_part[8];
+    __shared__ float s_dz2[kDenseTile][33], s_a2[kDenseTile][33], s_dout[kDenseTile];  // kept per position for the small gradients
     __shared__ int s_pos[kDenseTile];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rg = lane % RG, pg = lane / RG;
@@ -411,21 +417,25 @@ __global__ void __launch_bounds__(256, 2) dense_forward_tile_kernel(DenseArgs a)
         float dz2;  // gradient at the second layer's pre-activation, lane = row
         if (a.n_dense == 2) {
             dz2 = lane == 0 ? dout : 0.f;
-            if (lane == 0) a.dz[1][b] = dout;
+            if (lane == 0 && !a.fuse_small) a.dz[1][b] = dout;
         } else {
             dz2 = lane < M2 ? (s_w3[lane] * dout) * act_bwd(a.act[1], a2v) : 0.f;
-            if (lane == 0) a.dz[2][b] = dout;
-            if (lane < M2) {
-                a.dz[1][(size_t)b * M2 + lane] = dz2;
-                a.a2[(size_t)b * M2 + lane] = a2v;
+            if (!a.fuse_small) {
+                if (lane == 0) a.dz[2][b] = dout;
+                if (lane < M2) {
+                    a.dz[1][(size_t)b * M2 + lane] = dz2;
+                    a.a2[(size_t)b * M2 + lane] = a2v;
+                }
             }
         }
-        s_dz2[warp][lane] = dz2;
+        s_dz2[p][lane] = dz2;
+        s_a2[p][lane] = a2v;
+        if (lane == 0) s_dout[p] = dout;
         __syncwarp();
         // dz1[c] = (sum_r2 W2[c][r2] * dz2[r2]) * act'(a1[c]); 32/M1 lanes share one c
         const int c = lane % M1;
         float sum = 0.f;
-        for (int r2 = lane / M1; r2 < M2; r2 += 32 / M1) sum += s_w2[c][r2] * s_dz2[warp][r2];
+        for (int r2 = lane / M1; r2 < M2; r2 += 32 / M1) sum += s_w2[c][r2] * s_dz2[p][r2];
 #pragma unroll
         for (int o2 = M1; o2 < 32; o2 <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
         if (lane < M1) a.dz[0][(size_t)b * M1 + c] = sum * act_bwd(a.act[0], s_a1[p][c]);
@@ -438,6 +448,24 @@ __global__ void __launch_bounds__(256, 2) dense_forward_tile_kernel(DenseArgs a)
             float s = 0.f;
             for (int w = 0; w < 8; w++) s += loss_part[w];
             atomicAdd(a.loss, s);
+        }
+        if (a.fuse_small) {
+            // Weight and bias gradients of the narrow layers for this tile's bucket: a thread owns
+            // entries (row r, column c) of the M x (K+1) block (column K is the bias), sums over the
+            // tile's positions from shared memory and adds the result with one atomic per entry
+            // (Matmul::backward on the zero-padded gradient, bias = sum over the batch).
+            for (int o = threadIdx.x; o < M2 * (M1 + 1); o += blockDim.x) {  // layer 2: X = a1, dY = dz2
+                const int r = o % M2, c = o / M2;
+                float sum = 0.f;
+                for (int p = 0; p < t.y; p++) sum += s_dz2[p][r] * (c < M1 ? s_a1[p][c] : 1.f);
+                if (sum != 0.f) atomicAdd(c < M1 ? a.gW[1] + (size_t)c * OM2 + k * M2 + r : a.gB[1] + k * M2 + r, sum);
+            }
+            if (a.n_dense == 3)
+                for (int o = threadIdx.x; o < M2 + 1; o += blockDim.x) {  // layer 3: X = a2, dY = dout (one row)
+                    float sum = 0.f;
+                    for (int p = 0; p < t.y; p++) sum += s_dout[p] * (o < M2 ? s_a2[p][o] : 1.f);
+                    if (sum != 0.f) atomicAdd(o < M2 ? a.gW[2] + (size_t)o * a.O + k : a.gB[2] + k, sum);
+                }
         }
     }
 }

@@ -149,6 +149,9 @@ struct b200_net {
     // at 16384 positions, H = 2048: backward 0.50 ms against 0.61 ms for global vector reductions)
     bool fwd_tiled() const { return ft_fwd_mode == B200_FT_TILED || (ft_fwd_mode == B200_FT_AUTO && tiled_ok); }
     bool bwd_tiled() const { return ft_bwd_mode == B200_FT_TILED || (ft_bwd_mode == B200_FT_AUTO && tiled_ok); }
+    // the register-tiled dense forward (rows per bucket in fours, more layers after the first) also
+    // forms the gradients of those later layers
+    bool fused_small_grads() const { return d.dense_out[0] % 4 == 0 && d.n_dense >= 2; }
 };
 
 namespace {
@@ -378,6 +381,14 @@ b200::DenseArgs dense_args(b200_net* net, const Slot& s, bool want_grad) {
     a.out = net->out;
     a.loss = net->G;
     a.want_grad = want_grad ? 1 : 0;
+    a.fuse_small = want_grad && net->fused_small_grads() ? 1 : 0;
+    for (int l = 1; l < d.n_dense; l++) {
+        char name[16];
+        snprintf(name, sizeof name, "l%dw", l + 1);
+        a.gW[l] = net->G + net->find(name)->off;
+        snprintf(name, sizeof name, "l%db", l + 1);
+        a.gB[l] = net->G + net->find(name)->off;
+    }
     return a;
 }
 
@@ -492,7 +503,7 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
 // gradient outside l0w is complete as well.
 int launch_dense_grads(b200_net* net, Slot& s) {
     const b200_net_desc& d = net->d;
-    if (net->d.n_dense > 1) {  // the narrow layers' weight and bias gradients, one launch
+    if (net->d.n_dense > 1 && !net->fused_small_grads()) {  // the narrow layers' weight and bias gradients, one launch
         b200::SmallGradArgs g{};
         g.order = s.dev<int>(s.off_order);
         g.tiles = s.dev<int2>(s.off_dtiles);
