@@ -337,6 +337,14 @@ def run_ours(args, rank, world, local_rank):
         "note": "algorithmic bytes count every gathered/updated table row once per active feature; the tiled "
                 "kernels serve those rows from shared memory, so achieved can exceed the HBM peak",
     }
+    # what really bounds the tiled kernels: every active feature's 256-byte row piece passes the SM's
+    # shared-memory data pipe (128 bytes per clock per SM) once per 64-column slab
+    sm_mhz = (clocks or {}).get("sm_mhz") if rank == 0 else None
+    if sm_mhz and kernels[dom]["achieved_gbs"]:
+        pipe_gbs = 148 * 128 * sm_mhz * 1e6 / 1e9
+        roofline["on_chip"] = {"bound": "shared-memory data pipe", "peak": pipe_gbs, "unit": "GB/s",
+                               "frac": kernels[dom]["achieved_gbs"] / pipe_gbs,
+                               "peak_kind": "148 SMs x 128 B/clk x median SM clock during the run"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
