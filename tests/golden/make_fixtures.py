@@ -11,7 +11,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_fixtures.py /path/to/bullet")
+    ref = sys.argv[1]
     with open(os.path.join(ref, "examples", "tests", "batch.bf"), "rb") as f:
         data = f.read()
     assert len(data) == 16273 * 32
