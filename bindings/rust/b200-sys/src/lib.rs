@@ -20,6 +20,10 @@ pub const B200_KIND_MOMENTUM: c_int = 1;
 pub const B200_KIND_VELOCITY: c_int = 2;
 pub const B200_KIND_GRAD: c_int = 3;
 
+pub const B200_GAME_CHESS768: i32 = 0;
+pub const B200_GAME_CHESS_BUCKETS_MIRRORED: i32 = 1;
+pub const B200_GAME_ATAXX147: i32 = 2;
+
 pub const B200_QUANT_FLOAT: i32 = 0;
 pub const B200_QUANT_I8: i32 = 1;
 pub const B200_QUANT_I16: i32 = 2;
@@ -128,6 +132,17 @@ extern "C" {
         buckets: *const i32,
         targets: *const f32,
         n: i32,
+    ) -> c_int;
+
+    pub fn b200_batch_upload_records(
+        net: *mut b200_net,
+        slot: c_int,
+        records: *const c_void,
+        n: i32,
+        game: i32,
+        layout32: *const i32,
+        scale: f32,
+        blend: f32,
     ) -> c_int;
 
     pub fn b200_step(net: *mut b200_net, slot: c_int, lr: f32, grad_factor: f32) -> c_int;

@@ -23,7 +23,7 @@ SYMBOLS = (
     "b200_saved_format_write", "b200_save_quantised", "b200_save_unquantised",
     "b200_forward_begin", "b200_forward_ft", "b200_net_tensor_offset",
     "b200_exchange_export", "b200_exchange_import", "b200_update_exchange", "b200_update_exchange_range",
-    "b200_grad_zero_range",
+    "b200_grad_zero_range", "b200_batch_upload_records",
 )
 
 
@@ -84,6 +84,7 @@ def load() -> ctypes.CDLL:
         "b200_net_get_tensor": [vp, cp, ctypes.c_int, vp, i64],
         "b200_net_set_adamw": [vp, cp, ctypes.POINTER(CAdamW)],
         "b200_batch_upload": [vp, ctypes.c_int, vp, vp, vp, vp, i32],
+        "b200_batch_upload_records": [vp, ctypes.c_int, vp, i32, i32, vp, f32, f32],
         "b200_step": [vp, ctypes.c_int, f32, f32],
         "b200_backward": [vp, ctypes.c_int],
         "b200_update": [vp, f32, f32],

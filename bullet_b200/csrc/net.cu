@@ -29,6 +29,7 @@
 #include "kernels_dense.cuh"
 #include "kernels_ft.cuh"
 #include "kernels_opt.cuh"
+#include "host_map.h"
 
 #define CK(call)                                                                                          \
     do {                                                                                                  \
@@ -824,21 +825,29 @@ int b200_net_set_adamw(b200_net* net, const char* name, const b200_adamw_params*
     return 0;
 }
 
-int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t* nstm, const int32_t* buckets,
-                      const float* targets, int32_t n) {
-    if (!net || !stm || !nstm || !targets) return b200::fail(B200_ERR_ARG, "batch_upload: null argument");
-    if (slot < 0 || slot >= B200_NUM_SLOTS) return b200::fail(B200_ERR_ARG, "batch_upload: slot %d out of range", slot);
-    const b200_net_desc& d = net->d;
-    if (n < 1 || n > d.max_batch) return b200::fail(B200_ERR_ARG, "batch_upload: %d positions, capacity is %d", n, d.max_batch);
-    if (d.n_out_buckets > 1 && !buckets) return b200::fail(B200_ERR_ARG, "batch_upload: this network needs output buckets");
+// Common start of both uploads: the slot's pinned block is free once its last copy has landed and
+// the last step that read the device block has finished.
+static int upload_begin(b200_net* net, int slot, int32_t n, const char* who) {
+    if (slot < 0 || slot >= B200_NUM_SLOTS) return b200::fail(B200_ERR_ARG, "%s: slot %d out of range", who, slot);
+    if (n < 1 || n > net->d.max_batch) return b200::fail(B200_ERR_ARG, "%s: %d positions, capacity is %d", who, n, net->d.max_batch);
     if (int rc = set_device(net)) return rc;
     Slot& s = net->slots[slot];
-    // the pinned block is free once its last copy has landed and the last step that read
-    // the device block has finished
     if (s.has_ready) CK(cudaEventSynchronize(s.ready));
     if (s.has_consumed) CK(cudaEventSynchronize(s.consumed));
     slot_layout(net, s, n);
     s.n = 0;
+    return 0;
+}
+
+static int upload_finish(b200_net* net, Slot& s, int32_t n);
+
+int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t* nstm, const int32_t* buckets,
+                      const float* targets, int32_t n) {
+    if (!net || !stm || !nstm || !targets) return b200::fail(B200_ERR_ARG, "batch_upload: null argument");
+    const b200_net_desc& d = net->d;
+    if (d.n_out_buckets > 1 && !buckets) return b200::fail(B200_ERR_ARG, "batch_upload: this network needs output buckets");
+    if (int rc = upload_begin(net, slot, n, "batch_upload")) return rc;
+    Slot& s = net->slots[slot];
     const int64_t count = (int64_t)n * d.nnz;
     uint16_t* h_stm = s.host<uint16_t>(s.off_stm);
     uint16_t* h_nstm = s.host<uint16_t>(s.off_nstm);
@@ -861,6 +870,73 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
         memset(h_buckets, 0, (size_t)n * 4);
     }
     memcpy(s.host<float>(s.off_targets), targets, (size_t)n * 4);
+    return upload_finish(net, s, n);
+}
+
+// Records in, batch on the device: the featuriser, the output bucket and the target blend of
+// ValueTrainerState::make_mapper (crates/bullet_lib/src/value.rs:77-117) write straight into the
+// pinned staging block as packed u16 lists; no int32 arrays in between.
+int b200_batch_upload_records(b200_net* net, int slot, const void* records, int32_t n, int32_t game, const int32_t* layout32,
+                              float scale, float blend) {
+    if (!net || !records) return b200::fail(B200_ERR_ARG, "batch_upload_records: null argument");
+    if (game < B200_GAME_CHESS768 || game > B200_GAME_ATAXX147) return b200::fail(B200_ERR_ARG, "batch_upload_records: unknown game %d", game);
+    if (game == B200_GAME_CHESS_BUCKETS_MIRRORED && !layout32) return b200::fail(B200_ERR_ARG, "batch_upload_records: the king-bucket layout is missing");
+    if (!(blend >= 0.f && blend <= 1.f) || !(scale > 0.f)) return b200::fail(B200_ERR_ARG, "batch_upload_records: bad scale or blend");
+    const b200_net_desc& d = net->d;
+    const int O = d.n_out_buckets;
+    if (O > 1 && game == B200_GAME_ATAXX147) return b200::fail(B200_ERR_UNSUPPORTED, "batch_upload_records: no output buckets for ataxx records");
+    if (int rc = upload_begin(net, slot, n, "batch_upload_records")) return rc;
+    Slot& s = net->slots[slot];
+    uint16_t* h_stm = s.host<uint16_t>(s.off_stm);
+    uint16_t* h_nstm = s.host<uint16_t>(s.off_nstm);
+    int* h_buckets = s.host<int>(s.off_buckets);
+    float* h_targets = s.host<float>(s.off_targets);
+    int32_t expanded[64] = {0};
+    if (game == B200_GAME_CHESS_BUCKETS_MIRRORED) b200::expand_king_buckets(layout32, expanded);
+    const b200::ChessRecord* chess = static_cast<const b200::ChessRecord*>(records);
+    const b200::AtaxxRecord* ataxx = static_cast<const b200::AtaxxRecord*>(records);
+    const int nnz = d.nnz;
+    const uint32_t limit = (uint32_t)d.n_inputs;
+    const float rscale = 1.0f / scale;
+    int bad = n, bad_bucket = n;
+#pragma omp parallel for schedule(static) reduction(min : bad) reduction(min : bad_bucket) if (n >= 4096)
+    for (int32_t i = 0; i < n; i++) {
+        uint16_t* a = h_stm + (size_t)i * nnz;
+        uint16_t* b = h_nstm + (size_t)i * nnz;
+        int count;
+        if (game == B200_GAME_CHESS768)
+            count = b200::map_chess_record<false, uint16_t>(chess[i], expanded, a, b, nnz, (uint16_t)0xFFFFu);
+        else if (game == B200_GAME_CHESS_BUCKETS_MIRRORED)
+            count = b200::map_chess_record<true, uint16_t>(chess[i], expanded, a, b, nnz, (uint16_t)0xFFFFu);
+        else
+            count = b200::map_ataxx_record<uint16_t>(ataxx[i], a, b, nnz, (uint16_t)0xFFFFu);
+        if (count < 0) {
+            bad = i < bad ? i : bad;
+            continue;
+        }
+        for (int k = 0; k < count; k++) {  // as b200_batch_upload: an index the table does not have is an empty slot
+            if (a[k] >= limit) a[k] = 0xFFFFu;
+            if (b[k] >= limit) b[k] = 0xFFFFu;
+        }
+        int bucket = 0;
+        if (O > 1) {
+            bucket = b200::material_bucket(chess[i].occ, O);
+            if ((unsigned)bucket >= (unsigned)O) bad_bucket = i < bad_bucket ? i : bad_bucket;
+        }
+        h_buckets[i] = bucket;
+        h_targets[i] = b200::blended_target(chess[i].score, chess[i].result, rscale, blend);  // same offsets in both record types
+    }
+    if (bad < n) return b200::fail(B200_ERR_DATA, "batch_upload_records: record %d holds more than nnz=%d pieces", bad, nnz);
+    if (bad_bucket < n) return b200::fail(B200_ERR_DATA, "batch_upload_records: record %d has no valid output bucket", bad_bucket);
+    return upload_finish(net, s, n);
+}
+
+static int upload_finish(b200_net* net, Slot& s, int32_t n) {
+    const b200_net_desc& d = net->d;
+    const int O = d.n_out_buckets;
+    int* h_buckets = s.host<int>(s.off_buckets);
+    const uint16_t* h_stm = s.host<uint16_t>(s.off_stm);
+    const uint16_t* h_nstm = s.host<uint16_t>(s.off_nstm);
     // visiting order of the dense weight-gradient kernel: positions grouped by output bucket
     int* h_order = s.host<int>(s.off_order);
     {

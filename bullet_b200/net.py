@@ -84,6 +84,14 @@ class Net:
                                               _p(targets), n))
 
     # -------------------------------------------------------------------- step
+    def upload_records(self, slot: int, game: str, records: np.ndarray, scale: float = 400.0, blend: float = 0.5) -> None:
+        """Raw 32-byte records -> featurised, packed batch in the slot (one pass on all host cores)."""
+        records = np.ascontiguousarray(records)
+        code = {"chess768": 0, "chess_buckets": 1, "ataxx147": 2}[game]
+        layout = np.asarray(KING_BUCKETS_16, dtype=np.int32) if code == 1 else None
+        _lib.check(self.lib.b200_batch_upload_records(self._h, slot, _p(records), len(records), code,
+                                                      _p(layout) if layout is not None else None, scale, blend))
+
     def step(self, slot: int, lr: float, grad_factor: float) -> None:
         _lib.check(self.lib.b200_step(self._h, slot, lr, grad_factor))
 

@@ -115,6 +115,16 @@ int b200_net_set_adamw(b200_net* net, const char* name, const b200_adamw_params*
  * only while `slot` is still being read by an earlier step. */
 int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t* nstm, const int32_t* buckets,
                       const float* targets, int32_t n);
+/* The same from raw 32-byte position records: the featuriser (`game`), MaterialCount<n_out_buckets>
+ * (crates/bullet_lib/src/game/outputs.rs:24-31; networks with output buckets take chess records) and
+ * the target blend of ValueTrainerState::make_mapper (crates/bullet_lib/src/value.rs:77-117) run on
+ * all host cores and write the packed lists straight into the pinned staging block.  `layout32` is the
+ * king-bucket layout of ChessBucketsMirrored (32 entries), NULL for the other games. */
+#define B200_GAME_CHESS768 0
+#define B200_GAME_CHESS_BUCKETS_MIRRORED 1
+#define B200_GAME_ATAXX147 2
+int b200_batch_upload_records(b200_net* net, int slot, const void* records, int32_t n, int32_t game, const int32_t* layout32,
+                              float scale, float blend);
 
 /* ---- the step.  b200_step = Function::execute on the backward graph followed by
  * Optimiser::update (crates/trainer/src/run.rs:185-192).  The split form lets a

@@ -485,3 +485,36 @@ def test_full_size_properties_without_the_oracle():
     # the weights did not move
     assert all(np.array_equal(v, w[k]) for k, v in net.tensors(0).items())
     net.close()
+
+
+@pytest.mark.parametrize("ci", [0, 2, 3])
+def test_upload_from_records_equals_featurise_then_upload(ci):
+    """The one-pass records upload fills the slot exactly as the reference-layout arrays do: the
+    forward outputs are bit-identical and a training step gives the same loss and weights."""
+    from bullet_b200._lib import B200Error
+    from bullet_b200.net import featurise
+
+    c = config(ci)
+    n = 5000
+    desc = dataclasses.replace(c.desc, max_batch=n)
+    rec = synth.records(c.game, n, seed=61 + ci)
+    w = synth.init_weights(desc, seed=ci)
+    a, b = make_net(desc, 0, w), make_net(desc, 0, w)
+    a.upload(0, *featurise(c.game, rec, desc))
+    b.upload_records(0, c.game, rec)
+    assert np.array_equal(a.forward(0, n), b.forward(0, n))
+    a.step(0, 1e-3, 1.0 / n)
+    b.step(0, 1e-3, 1.0 / n)
+    assert abs(a.loss() - b.loss()) <= 1e-6 * abs(a.loss())
+    wa, wb = a.tensors(0), b.tensors(0)
+    for k in wa:
+        assert rel2(wb[k], wa[k]) <= 1e-6, k
+    if c.game != "ataxx147":   # a record with more pieces than slots is refused, not truncated
+        small = make_net(dataclasses.replace(desc, nnz=8), 0, w) if ci == 0 else None
+        if small is not None:
+            with pytest.raises(B200Error) as e:
+                small.upload_records(0, c.game, rec)
+            assert e.value.code == -4
+            small.close()
+    a.close()
+    b.close()
