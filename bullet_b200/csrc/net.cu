@@ -93,6 +93,10 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct b200_net {
     int device = 0;
     cudaStream_t stream = nullptr, copy_stream = nullptr;
+    // clears the gradient buffer beside the feature-transformer forward, which does not touch it
+    cudaStream_t zero_stream = nullptr;
+    cudaEvent_t zero_fork = nullptr, zero_done = nullptr;
+    bool zero_pending = false;
     bool own_stream = false;
     b200_net_desc d{};
     std::vector<Tensor> tensors;
@@ -451,6 +455,10 @@ int forward_ft_items(b200_net* net, Slot& s, int first_item, int n_items) {
 
 int forward_dense(b200_net* net, Slot& s, bool want_grad) {
     if (want_grad) CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][1], net->stream));
+    if (net->zero_pending) {  // the loss and every gradient from here on land in the cleared buffer
+        CK(cudaStreamWaitEvent(net->stream, net->zero_done, 0));
+        net->zero_pending = false;
+    }
     b200::DenseArgs da = dense_args(net, s, want_grad);
     DISPATCH_M(net->d.dense_out[0], launch_dense_forward<MM>(net, da, s.n_dtiles));
     LAUNCHED(net);
@@ -558,6 +566,10 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
             return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create a stream"));
         net->own_stream = true;
     }
+    if (cudaStreamCreateWithFlags(&net->zero_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&net->zero_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&net->zero_done, cudaEventDisableTiming) != cudaSuccess)
+        return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the side stream"));
     if (cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the copy stream"));
 
@@ -694,6 +706,7 @@ int b200_net_destroy(b200_net* net) {
     cudaSetDevice(net->device);
     if (net->stream) cudaStreamSynchronize(net->stream);
     if (net->copy_stream) cudaStreamSynchronize(net->copy_stream);
+    if (net->zero_stream) cudaStreamSynchronize(net->zero_stream);
     for (int r = 0; r < net->xch_world; r++)
         if (r != net->xch_rank) {
             if (net->peer_g[r]) cudaIpcCloseMemHandle(net->peer_g[r]);
@@ -715,6 +728,9 @@ int b200_net_destroy(b200_net* net) {
             if (e) cudaEventDestroy(e);
     if (net->own_stream && net->stream) cudaStreamDestroy(net->stream);
     if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+    if (net->zero_stream) cudaStreamDestroy(net->zero_stream);
+    if (net->zero_fork) cudaEventDestroy(net->zero_fork);
+    if (net->zero_done) cudaEventDestroy(net->zero_done);
     delete net;
     return 0;
 }
@@ -1058,8 +1074,15 @@ int b200_forward_begin(b200_net* net, int slot) {
     Slot& s = net->slots[slot];
     CK(cudaStreamWaitEvent(net->stream, s.ready, 0));
     if (int rc = refresh_table(net)) return rc;
-    if (!net->manual_grad_zero)
-        CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->stream));  // every gradient is accumulated with reductions
+    if (!net->manual_grad_zero) {
+        // every gradient is accumulated with reductions, so the buffer starts at zero; nothing before
+        // the dense layers writes to it, so the clearing runs on a side stream beside the FT forward
+        CK(cudaEventRecord(net->zero_fork, net->stream));
+        CK(cudaStreamWaitEvent(net->zero_stream, net->zero_fork, 0));
+        CK(cudaMemsetAsync(net->G, 0, (size_t)net->n_flat * 4, net->zero_stream));
+        CK(cudaEventRecord(net->zero_done, net->zero_stream));
+        net->zero_pending = true;
+    }
     if (int rc = forward_prepare(net, s, true)) return rc;
     net->fwd_slot = slot;
     net->fwd_parts_done = 0;
