@@ -186,6 +186,8 @@ class DataParallelStep:
             whole, mine = self._slice(p)
             eng.grad_zero_range(whole.start, self.per_part)
             eng.backward_ft(slot, p, P)
+            if p == P - 1:
+                eng.backward_end(slot)  # joins the dense weight gradient: the small tensors are complete
             self._ev_bwd[p].record(cur)
             with torch.cuda.stream(side):
                 side.wait_event(self._ev_bwd[p])
@@ -197,7 +199,6 @@ class DataParallelStep:
                 if p == P - 1:
                     self._ev_head_free.record(side)  # behind a barrier that follows every rank's read of them
                 self._ev_done[p].record(side)
-        eng.backward_end(slot)
         cur.wait_event(self._ev_head_ready)
         eng.update_end()
         self._in_flight = True
