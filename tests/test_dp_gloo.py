@@ -151,9 +151,9 @@ def _worker(rank, world, port, out_dir, parts, shard, peer=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("parts,shard,peer", [(1, False, False), (4, False, False), (1, True, False), (4, True, False),
-                                              (1, False, True)])
-def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard, peer):
+@pytest.mark.parametrize("parts,shard,peer,world", [(1, False, False, 2), (4, False, False, 2), (1, True, False, 2),
+                                                    (4, True, False, 2), (1, False, True, 2), (4, True, False, 4)])
+def test_data_parallel_ranks_match_single_rank(tmp_path, parts, shard, peer, world):
     from bullet_b200 import config, synth
     from bullet_b200.configs import AdamWParams
     from bullet_b200.dp import shard_bounds
@@ -162,9 +162,9 @@ def test_two_rank_data_parallel_matches_single_rank(tmp_path, parts, shard, peer
     assert shard_bounds(8, 1, 2) == (4, 8)
     with pytest.raises(ValueError):
         shard_bounds(7, 0, 2)
-    port = 29500 + (os.getpid() + 7 * parts + 3 * shard + 11 * peer) % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path), parts, shard, peer), nprocs=2, join=True)
-    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    port = 29500 + (os.getpid() + 7 * parts + 3 * shard + 11 * peer + 17 * world) % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path), parts, shard, peer), nprocs=world, join=True)
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / f"rank{world - 1}.npz")
     c = config(3)
     desc = dataclasses.replace(c.desc, ft_out=64, max_batch=256)
     orc = Oracle("f32")
