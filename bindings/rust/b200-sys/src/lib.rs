@@ -214,6 +214,7 @@ extern "C" {
     pub fn b200_map_ataxx147(records: *const c_void, n: i32, stm: *mut i32, nstm: *mut i32, nnz: i32) -> c_int;
     pub fn b200_material_count(records: *const c_void, n: i32, n_buckets: i32, out: *mut i32) -> c_int;
     pub fn b200_make_targets(records: *const c_void, n: i32, scale: f32, blend: f32, out: *mut f32) -> c_int;
+    pub fn b200_set_host_threads(n: i32) -> c_int;
     pub fn b200_pack_indices_u16(idx: *const i32, count: i64, out: *mut u16) -> c_int;
     pub fn b200_unpack_indices_u16(packed: *const u16, count: i64, out: *mut i32) -> c_int;
 }

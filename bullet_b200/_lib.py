@@ -23,7 +23,7 @@ SYMBOLS = (
     "b200_saved_format_write", "b200_save_quantised", "b200_save_unquantised",
     "b200_forward_begin", "b200_forward_ft", "b200_net_tensor_offset",
     "b200_exchange_export", "b200_exchange_import", "b200_update_exchange", "b200_update_exchange_range",
-    "b200_grad_zero_range", "b200_batch_upload_records",
+    "b200_grad_zero_range", "b200_batch_upload_records", "b200_set_host_threads",
 )
 
 
@@ -127,6 +127,7 @@ def load() -> ctypes.CDLL:
         "b200_map_ataxx147": [vp, i32, vp, vp, i32],
         "b200_material_count": [vp, i32, i32, vp],
         "b200_make_targets": [vp, i32, f32, f32, vp],
+        "b200_set_host_threads": [i32],
         "b200_pack_indices_u16": [vp, i64, vp],
         "b200_unpack_indices_u16": [vp, i64, vp],
     }

@@ -8,6 +8,9 @@
 // kernel that skips invalid slots and one that stops at the first agree.
 #include <cmath>
 #include <cstring>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #include "../../include/bullet_b200.h"
 #include "common.h"
@@ -82,6 +85,17 @@ int b200_make_targets(const void* records, int32_t n, float scale, float blend, 
     const float rscale = 1.0f / scale;
 #pragma omp parallel for schedule(static) if (n >= kParallelFrom)
     for (int32_t i = 0; i < n; i++) out[i] = b200::blended_target(rec[i].score, rec[i].result, rscale, blend);
+    return 0;
+}
+
+// How many host threads the featurisers and the batch packing use (OpenMP); n < 1 = the runtime's own
+// choice.  Launchers that start one process per GPU often pin every process to one thread.
+int b200_set_host_threads(int32_t n) {
+#ifdef _OPENMP
+    omp_set_num_threads(n >= 1 ? n : omp_get_num_procs());
+#else
+    (void)n;
+#endif
     return 0;
 }
 

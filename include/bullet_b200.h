@@ -319,6 +319,9 @@ int b200_map_ataxx147(const void* records, int32_t n, int32_t* stm, int32_t* nst
 int b200_material_count(const void* records, int32_t n, int32_t n_buckets, int32_t* out);
 /* target = blend*result/2 + (1-blend)*sigmoid(score/scale) (crates/bullet_lib/src/value.rs:103-115) */
 int b200_make_targets(const void* records, int32_t n, float scale, float blend, float* out);
+/* Host threads (OpenMP) used by the featurisers and by the packing inside the uploads; n < 1 = one per
+ * core.  One-process-per-GPU launchers often set OMP_NUM_THREADS=1, which leaves the packing serial. */
+int b200_set_host_threads(int32_t n);
 /* The packed index format of a staging slot: u16 per slot, 0xFFFF for "no feature". */
 int b200_pack_indices_u16(const int32_t* idx, int64_t count, uint16_t* out);
 int b200_unpack_indices_u16(const uint16_t* packed, int64_t count, int32_t* out);
