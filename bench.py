@@ -214,11 +214,6 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # torchrun pins every rank to one OpenMP thread; the batch packing wants its share of the cores
-        from bullet_b200 import _lib
-
-        _lib.load().b200_set_host_threads(max(1, len(os.sched_getaffinity(0)) // world))
-    if world > 1:
         opts = dist.ProcessGroupNCCL.Options()
         opts.is_high_priority_stream = True  # collectives that run beside kernels get their SMs first
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
