@@ -57,7 +57,15 @@ int b200_checkpoint_save(b200_net* net, const char* dir) {
 
 int b200_checkpoint_load(b200_net* net, const char* dir) {
     if (!net || !dir) return b200::fail(B200_ERR_ARG, "checkpoint_load: null argument");
-    std::vector<unsigned char> bytes;
+    // All three files are read and checked (ids, counts, the set of tensors) before anything reaches the
+    // device: a truncated or foreign file leaves the network exactly as it was.
+    struct Record {
+        std::string id;
+        size_t at;       // offset of the values inside the file's bytes
+        int64_t count;
+    };
+    std::vector<unsigned char> bytes[3];
+    std::vector<Record> records[3];
     for (int kind = 0; kind < 3; kind++) {
         const std::string path = std::string(dir) + "/" + kFiles[kind];
         FILE* f = std::fopen(path.c_str(), "rb");
@@ -65,40 +73,47 @@ int b200_checkpoint_load(b200_net* net, const char* dir) {
         std::fseek(f, 0, SEEK_END);
         const long size = std::ftell(f);
         std::fseek(f, 0, SEEK_SET);
-        bytes.resize((size_t)std::max(0L, size));
-        const bool ok = std::fread(bytes.data(), 1, bytes.size(), f) == bytes.size();
+        std::vector<unsigned char>& buf = bytes[kind];
+        buf.resize((size_t)std::max(0L, size));
+        const bool ok = std::fread(buf.data(), 1, buf.size(), f) == buf.size();
         std::fclose(f);
         if (!ok) return b200::fail(B200_ERR_ARG, "checkpoint_load: short read from %s", path.c_str());
         size_t at = 0;
-        int seen = 0;
-        while (at < bytes.size()) {
+        while (at < buf.size()) {
             std::string id;
-            while (at < bytes.size() && bytes[at] != '\n') id.push_back((char)bytes[at++]);
-            if (at + 1 + 8 > bytes.size()) return b200::fail(B200_ERR_DATA, "checkpoint_load: %s is truncated after id '%s'", path.c_str(), id.c_str());
+            while (at < buf.size() && buf[at] != '\n') id.push_back((char)buf[at++]);
+            if (at + 1 + 8 > buf.size()) return b200::fail(B200_ERR_DATA, "checkpoint_load: %s is truncated after id '%s'", path.c_str(), id.c_str());
             at++;  // the newline
             uint64_t count = 0;
-            std::memcpy(&count, bytes.data() + at, 8);
+            std::memcpy(&count, buf.data() + at, 8);
             at += 8;
-            if (count > (bytes.size() - at) / 4) return b200::fail(B200_ERR_DATA, "checkpoint_load: record '%s' of %s runs past the end", id.c_str(), path.c_str());
+            if (count > (buf.size() - at) / 4) return b200::fail(B200_ERR_DATA, "checkpoint_load: record '%s' of %s runs past the end", id.c_str(), path.c_str());
             int64_t n = 0;
             if (b200_net_tensor_size(net, id.c_str(), &n) != 0)
                 return b200::fail(B200_ERR_DATA, "checkpoint_load: %s holds tensor '%s', which this network does not have", path.c_str(), id.c_str());
             if ((uint64_t)n != count)
                 return b200::fail(B200_ERR_DATA, "checkpoint_load: tensor '%s' has %lld values here, %llu in %s", id.c_str(), (long long)n,
                                   (unsigned long long)count, path.c_str());
-            std::vector<float> values((size_t)count);
-            std::memcpy(values.data(), bytes.data() + at, (size_t)count * 4);
+            for (const Record& r : records[kind])
+                if (r.id == id) return b200::fail(B200_ERR_DATA, "checkpoint_load: %s holds tensor '%s' twice", path.c_str(), id.c_str());
+            records[kind].push_back({id, at, n});
             at += (size_t)count * 4;
-            if (int rc = b200_net_set_tensor(net, id.c_str(), kind, values.data(), n)) return rc;
-            seen++;
         }
         int expected = 0;
         for (const char* id : kIds) {
             int64_t n = 0;
             if (b200_net_tensor_size(net, id, &n) == 0) expected++;
         }
-        if (seen != expected) return b200::fail(B200_ERR_DATA, "checkpoint_load: %s holds %d tensors, the network has %d", path.c_str(), seen, expected);
+        if ((int)records[kind].size() != expected)
+            return b200::fail(B200_ERR_DATA, "checkpoint_load: %s holds %d tensors, the network has %d", path.c_str(), (int)records[kind].size(), expected);
     }
+    std::vector<float> values;
+    for (int kind = 0; kind < 3; kind++)
+        for (const Record& r : records[kind]) {
+            values.resize((size_t)r.count);
+            std::memcpy(values.data(), bytes[kind].data() + r.at, (size_t)r.count * 4);
+            if (int rc = b200_net_set_tensor(net, r.id.c_str(), kind, values.data(), r.count)) return rc;
+        }
     return 0;
 }
 

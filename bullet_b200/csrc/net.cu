@@ -48,7 +48,6 @@
 
 namespace {
 
-constexpr int kSmCount = 148;
 constexpr int64_t kAlignFloats = 64;       // 256-byte tensor alignment in the flat buffers
 constexpr int kMinItemPairs = 128;         // a forward work item serves at least this many pairs per tile load
 
@@ -92,6 +91,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct b200_net {
     int device = 0;
+    int sm_count = 1;  // cudaDevAttrMultiProcessorCount of `device`: grids are sized in waves of it
     cudaStream_t stream = nullptr, copy_stream = nullptr;
     // clears the gradient buffer beside the feature-transformer forward, which does not touch it
     cudaStream_t zero_stream = nullptr;
@@ -109,6 +109,7 @@ struct b200_net {
     // pinned read-back ring: loss and status word of the last kLossRing updates
     static constexpr int kLossRing = 4;
     int* h_status = nullptr;
+    int* d_status = nullptr;       // [kLossRing] the slot's status word, saved before the slot is released to the uploader
     float* h_loss = nullptr;
     cudaEvent_t loss_ev[kLossRing] = {};
     int64_t updates = 0;
@@ -294,7 +295,7 @@ cudaError_t set_dense_forward_smem() {
 }
 
 // How many near-equal work items an average block is cut into.  One CTA is resident per SM,
-// so the grid runs in waves of kSmCount; more items even out the last wave but repeat the
+// so the grid runs in waves of net->sm_count; more items even out the last wave but repeat the
 // tile's fixed cost (`overhead`, as a fraction of a whole tile's work: the tile load in the
 // forward, the gradient flush in the backward).  `most` bounds the count from above.
 int splits_for(const b200_net* net, int most, double overhead) {
@@ -302,7 +303,7 @@ int splits_for(const b200_net* net, int most, double overhead) {
     int best = 1;
     double best_cost = 1e30;
     for (int sp = 1; sp <= std::max(1, std::min(512, most)); sp++) {
-        const double waves = (double)((tiles * sp + kSmCount - 1) / kSmCount);
+        const double waves = (double)((tiles * sp + net->sm_count - 1) / net->sm_count);
         const double cost = waves * (1.0 / sp + overhead);
         if (cost < best_cost * 0.98) {
             best_cost = cost;
@@ -403,14 +404,14 @@ int refresh_table(b200_net* net) {
         const Tensor* w = net->find("l0w");
         const Tensor* f = net->find("l0f");
         const size_t n4 = (size_t)w->n / 4, block4 = (size_t)f->n / 4;
-        b200::factoriser_merge_kernel<<<kSmCount * 8, 256, 0, net->stream>>>(
+        b200::factoriser_merge_kernel<<<net->sm_count * 8, 256, 0, net->stream>>>(
             reinterpret_cast<const float4*>(net->P + w->off), reinterpret_cast<const float4*>(net->P + f->off),
             reinterpret_cast<float4*>(net->table), n4, block4);
         LAUNCHED(net);
     }
     {
         const Tensor* w1 = net->find("l1w");
-        b200::dense_regroup_kernel<<<std::min<int>(kSmCount * 4, (int)((w1->n + 255) / 256)), 256, 0, net->stream>>>(
+        b200::dense_regroup_kernel<<<std::min<int>(net->sm_count * 4, (int)((w1->n + 255) / 256)), 256, 0, net->stream>>>(
             net->P + w1->off, net->w1g, net->D1(), net->d.n_out_buckets, net->d.dense_out[0]);
         LAUNCHED(net);
     }
@@ -496,7 +497,7 @@ int launch_wgrad(b200_net* net, const Slot& s, int layer) {
         DISPATCH_M(d.dense_out[layer], cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, b200::dense_wgrad_kernel<MM>, threads, 0));
         net->wgrad_per_sm = std::max(1, per_sm);
     }
-    const int slots = net->wgrad_per_sm * kSmCount;
+    const int slots = net->wgrad_per_sm * net->sm_count;
     const int waves = s.n >= 65536 ? 2 : 1;
     int chunks = std::max(1, std::min((s.n + 31) / 32, waves * slots / gx));
     w.chunk_len = (s.n + chunks - 1) / chunks;
@@ -559,6 +560,8 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         return rc;
     };
     if (int rc = set_device(net)) return bail(rc);
+    if (cudaDeviceGetAttribute(&net->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || net->sm_count < 1)
+        return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot read the SM count of device %d", device));
     if (stream) {
         net->stream = static_cast<cudaStream_t>(stream);
     } else {
@@ -621,6 +624,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     rc = rc ? rc : dev_alloc(net, &net->a2, B * 32);
     for (int l = 0; l < 3; l++) rc = rc ? rc : dev_alloc(net, &net->dz[l], B * 32);
     rc = rc ? rc : dev_alloc(net, &net->out, B);
+    rc = rc ? rc : dev_alloc(net, &net->d_status, b200_net::kLossRing);
     rc = rc ? rc : dev_alloc(net, &net->w1g, (size_t)d.n_out_buckets * d.dense_out[0] * net->D1());
     // the fence counters get an allocation of their own size class (2 MiB), so that its IPC handle maps exactly it
     rc = rc ? rc : dev_alloc(net, &net->xch_flags, (size_t)(2 << 20) / sizeof(int));
@@ -1186,7 +1190,7 @@ int b200_backward_ft(b200_net* net, int slot, int part, int n_parts) {
         const Tensor* f = net->find("l0f");
         const int copies = (int)(l0w->n / f->n), per_part = copies / n_parts;
         if (copies % n_parts) return b200::fail(B200_ERR_UNSUPPORTED, "backward_ft: %d parts do not divide %d factoriser copies", n_parts, copies);
-        b200::factoriser_grad_kernel<<<kSmCount * 4, 256, 0, net->stream>>>(
+        b200::factoriser_grad_kernel<<<net->sm_count * 4, 256, 0, net->stream>>>(
             reinterpret_cast<const float4*>(net->G + l0w->off + (int64_t)part * per_part * f->n),
             reinterpret_cast<float4*>(net->G + f->off), (size_t)f->n / 4, per_part, part > 0);
         LAUNCHED(net);
@@ -1205,6 +1209,11 @@ int b200_backward_end(b200_net* net, int slot) {
     Slot& s = net->slots[slot];
     cudaEvent_t* ev = net->tev[net->steps_begun % b200_net::kTimingRing];
     CK(cudaEventRecord(ev[6], net->stream));
+    // the status word travels with the step, not with the slot: once `consumed` is recorded the uploader may
+    // clear and refill the slot while the update of this step is still to come
+    if (net->status_slot >= 0)
+        CK(cudaMemcpyAsync(net->d_status + net->updates % b200_net::kLossRing, s.dev<int>(s.off_status), sizeof(int),
+                           cudaMemcpyDeviceToDevice, net->stream));
     CK(cudaEventRecord(s.consumed, net->stream));
     s.has_consumed = true;
     net->have_backward = true;
@@ -1256,7 +1265,7 @@ int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_
         const Tensor& t = net->tensors[i];
         a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
     }
-    const long long blocks = std::min<long long>((a.total4 + 255) / 256, kSmCount * 16);
+    const long long blocks = std::min<long long>((a.total4 + 255) / 256, net->sm_count * 16);
     b200::adamw_flat_kernel<<<(unsigned)blocks, 256, 0, net->stream>>>(a);
     LAUNCHED(net);
     net->table_dirty = true;
@@ -1360,7 +1369,7 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     // On the net's own stream the kernel runs alone and takes the whole device.  On a caller's side
     // stream it runs beside the feature-transformer kernels, whose CTAs leave room for exactly one
     // such CTA per SM: more CTAs would take whole SMs away from them instead of filling the gaps.
-    const long long cap = stream ? (net->exchange_ctas > 0 ? net->exchange_ctas : kSmCount) : kSmCount * 8;
+    const long long cap = stream ? (net->exchange_ctas > 0 ? net->exchange_ctas : net->sm_count) : net->sm_count * 8;
     const long long blocks = std::min<long long>((a.total4 + 127) / 128, cap);
     cudaStream_t on = stream ? static_cast<cudaStream_t>(stream) : net->stream;
     switch (x.world) {
@@ -1422,8 +1431,7 @@ int b200_update_end(b200_net* net) {
     CK(cudaMemcpyAsync(net->h_loss + ring, net->loss_in_param ? net->P : net->G, sizeof(float), cudaMemcpyDeviceToHost, net->stream));
     net->loss_in_param = false;
     if (net->status_slot >= 0) {
-        const Slot& st = net->slots[net->status_slot];
-        CK(cudaMemcpyAsync(net->h_status + ring, st.dev<int>(st.off_status), sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+        CK(cudaMemcpyAsync(net->h_status + ring, net->d_status + ring, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
     } else {
         net->h_status[ring] = 0;
     }

@@ -14,6 +14,7 @@
 // pair order.  b200_op_ft_forward takes that scratch from cudaMalloc for the duration of the
 // call; b200_op_ft_forward_noalloc keeps it in a fixed array that is part of the library image.
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 #include <mutex>
 
@@ -108,6 +109,7 @@ int check_op(const b200_ft_op* op, const char* who) {
     if (!op->table || !op->bias || !op->idx_stm || !op->idx_nstm || !op->x || (op->pairwise && !op->u))
         return b200::fail(B200_ERR_ARG, "%s: null device pointer", who);
     if (op->n < 1) return b200::fail(B200_ERR_ARG, "%s: n must be positive", who);
+    if (op->n > INT32_MAX / 4) return b200::fail(B200_ERR_ARG, "%s: at most %d positions per call", who, INT32_MAX / 4);
     if (op->nnz < 1 || op->nnz > 64 || op->n_inputs < 1 || op->n_inputs > 65534)
         return b200::fail(B200_ERR_UNSUPPORTED, "%s: nnz must be in [1, 64] and n_inputs in [1, 65534]", who);
     if (op->ft_act != B200_ACT_CRELU && op->ft_act != B200_ACT_SCRELU)

@@ -317,7 +317,11 @@ int b200_map_chess_buckets_mirrored(const void* records, int32_t n, const int32_
 int b200_map_ataxx147(const void* records, int32_t n, int32_t* stm, int32_t* nstm, int32_t nnz);
 /* MaterialCount<N>::bucket (crates/bullet_lib/src/game/outputs.rs:24-31) */
 int b200_material_count(const void* records, int32_t n, int32_t n_buckets, int32_t* out);
-/* target = blend*result/2 + (1-blend)*sigmoid(score/scale) (crates/bullet_lib/src/value.rs:103-115) */
+/* target = blend*result/2 + (1-blend)*sigmoid(score/scale) (crates/bullet_lib/src/value.rs:103-115).
+ * The score is multiplied by the fp32 reciprocal of `scale`, as value.rs:69,108 does (`rscale * score`), for
+ * every game, ataxx records included.  The raw-API ataxx example divides instead
+ * (examples/ataxx.rs:58: exp(-score / 400.0)); 1/400 is not exact in fp32, so a target made this way can differ
+ * from that example's by one unit in the last place. */
 int b200_make_targets(const void* records, int32_t n, float scale, float blend, float* out);
 /* Host threads (OpenMP) used by the featurisers and by the packing inside the uploads; n < 1 = one per
  * core.  One-process-per-GPU launchers often set OMP_NUM_THREADS=1, which leaves the packing serial. */

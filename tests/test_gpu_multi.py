@@ -20,6 +20,7 @@ MODES = {"allreduce": dict(), "sharded": dict(shard_optimiser=True), "pipelined"
          "allreduce_parts": dict(parts=4), "peer": dict(peer_exchange=True),
          "peer_pipelined": dict(peer_exchange=True, parts=4)}
 GLOBAL, STEPS, LR = 2048, 4, 1e-2
+ORACLE_GLOBAL, ORACLE_STEPS, ORACLE_MODES = 4096, 100, ("peer",)
 
 
 def _setup():
@@ -100,6 +101,88 @@ def test_every_exchange_form_matches_one_gpu(tmp_path):
             assert np.array_equal(r0[f"{mode}/w/{k}"], r1[f"{mode}/w/{k}"]), f"{mode}: replicas differ in {k}"
             assert rel(r0[f"{mode}/w/{k}"], w_ref[k]) <= 1e-5, (mode, k)
         assert np.array_equal(r0[f"{mode}/m/l0w"], r1[f"{mode}/m/l0w"]) and rel(r0[f"{mode}/m/l0w"], m_ref) <= 1e-4, mode
+
+
+def _oracle_worker(rank, world, port, out_dir):
+    """The benchmark network itself (config 4's descriptor) on two GPUs, 100 steps of the default exchange."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from bullet_b200 import config, synth
+    from bullet_b200.dp import DataParallelStep, NetEngine, shard_batch
+    from bullet_b200.net import Net, featurise
+
+    c = config(4)
+    desc = dataclasses.replace(c.desc, max_batch=ORACLE_GLOBAL // world)
+    weights = synth.init_weights(desc, seed=c.seed)
+    rec = synth.records(c.game, ORACLE_GLOBAL * ORACLE_STEPS, seed=c.seed + 11)
+    stream = torch.cuda.Stream()
+    out = {}
+    with torch.cuda.stream(stream):
+        for mode in ORACLE_MODES:
+            net = Net(desc, device=rank, stream=stream.cuda_stream)
+            net.load_weights(weights)
+            dp = DataParallelStep(NetEngine(net, torch.device("cuda", rank)), ORACLE_GLOBAL, **MODES[mode])
+            losses = []
+            for s in range(ORACLE_STEPS):
+                whole = featurise(c.game, rec[s * ORACLE_GLOBAL:(s + 1) * ORACLE_GLOBAL], desc)
+                net.upload(s % 3, *shard_batch(whole, rank, world))
+                dp.step(s % 3, c.lr)
+                losses.append(net.loss())
+                if s == 0:
+                    dp.finish()
+                    for k, v in net.tensors(0).items():
+                        out[f"{mode}/first/{k}"] = v
+            dp.finish()
+            net.sync()
+            torch.cuda.synchronize()
+            dist.barrier()
+            for k, v in net.tensors(0).items():
+                out[f"{mode}/last/{k}"] = v
+            out[f"{mode}/losses"] = np.array(losses)
+            dist.barrier()
+            net.close()
+    np.savez(os.path.join(out_dir, f"oracle_rank{rank}.npz"), **out)
+    dist.destroy_process_group()
+
+
+def test_two_gpus_match_the_oracle_on_the_whole_batch(tmp_path, oracle32, oracle64):
+    """Config 4's network, a global batch of 4096 cut over two GPUs, against the CPU oracle on the whole
+    batch: loss and parameters within 1e-4 after one step; after 100 steps loss within 1e-3 at every step
+    and parameters within 1e-3 of the fp32 oracle (or, where fp32 noise exceeds that, no further from the
+    fp64 twin than 1.5 x the fp32 oracle's own distance from it)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from bullet_b200 import config, synth
+    from bullet_b200.configs import AdamWParams
+
+    port = 29500 + (os.getpid() + 29) % 2000
+    mp.spawn(_oracle_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "oracle_rank0.npz"), np.load(tmp_path / "oracle_rank1.npz")
+    c = config(4)
+    desc = dataclasses.replace(c.desc, max_batch=ORACLE_GLOBAL)
+    weights = synth.init_weights(desc, seed=c.seed)
+    rec = synth.records(c.game, ORACLE_GLOBAL * ORACLE_STEPS, seed=c.seed + 11)
+    seq = [oracle32.map_batch(c.game, rec[s * ORACLE_GLOBAL:(s + 1) * ORACLE_GLOBAL], desc) for s in range(ORACLE_STEPS)]
+    first32, _, _, _ = oracle32.train(desc, weights, seq[:1], c.lr, AdamWParams())
+    w32, _, _, losses32 = oracle32.train(desc, weights, seq, c.lr, AdamWParams())
+    w64, _, _, _ = oracle64.train(desc, weights, seq, c.lr, AdamWParams())
+    rel = lambda a, b: np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b.astype(np.float64)), 1e-30)  # noqa: E731
+    for mode in ORACLE_MODES:
+        losses = r0[f"{mode}/losses"]
+        assert np.array_equal(losses, r1[f"{mode}/losses"]), mode
+        assert abs(losses[0] - losses32[0]) <= 1e-4 * abs(losses32[0]), mode
+        np.testing.assert_allclose(losses, losses32, rtol=1e-3, err_msg=mode)
+        for k in w32:
+            assert np.array_equal(r0[f"{mode}/last/{k}"], r1[f"{mode}/last/{k}"]), f"{mode}: replicas differ in {k}"
+            assert rel(r0[f"{mode}/first/{k}"], first32[k]) <= 1e-4, (mode, k, "after one step")
+            direct, drift32, drift = rel(r0[f"{mode}/last/{k}"], w32[k]), rel(w32[k], w64[k]), rel(r0[f"{mode}/last/{k}"], w64[k])
+            print({"net": "c4 on 2 GPUs", "mode": mode, "tensor": k, "gpu_vs_oracle32": direct,
+                   "oracle32_vs_oracle64": drift32, "gpu_vs_oracle64": drift})
+            assert direct <= 1e-3 or drift <= max(1e-3, 1.5 * drift32), (mode, k, direct, drift, drift32)
 
 
 def _late_peer_worker(rank, world, port, out_dir):

@@ -44,3 +44,20 @@ def test_noalloc_refuses_more_than_its_scratch_holds(oracle32):
     assert rc == -1 and b"16384" in _lib.load().b200_last_error()
     rc, _, _ = run_op("b200_op_ft_forward_noalloc", desc, table, w["l0b"], stm[:16384], nstm[:16384], 16384)
     assert rc == 0
+
+
+def test_noalloc_wide_index_lists_and_their_smaller_limit(oracle32):
+    """More than 32 index slots per position (ataxx: 49) take twice the list space, so the fixed
+    scratch holds half as many positions: 8192 run bit-exactly, 8193 are refused."""
+    from bullet_b200 import _lib
+
+    name, desc, game = CASES[2]
+    assert desc.nnz == 49
+    n = 8192
+    stm, nstm, w, table, x_ref = op_inputs(oracle32, desc, game, n + 1, 75)
+    rc, x, _ = run_op("b200_op_ft_forward_noalloc", desc, table, w["l0b"], stm[:n], nstm[:n], n)
+    assert rc == 0 and np.array_equal(x, x_ref[:n])
+    rc, _, _ = run_op("b200_op_ft_forward_noalloc", desc, table, w["l0b"], stm, nstm, n + 1)
+    assert rc == -1 and b"8192" in _lib.load().b200_last_error()
+    rc, x, _ = run_op("b200_op_ft_forward", desc, table, w["l0b"], stm, nstm, n + 1)   # the allocating entry takes it
+    assert rc == 0 and np.array_equal(x, x_ref)
