@@ -264,7 +264,7 @@ def run_ours(args, rank, world, local_rank):
     shard = bool(args.dp_shard) and world > 1
     peer = bool(args.dp_peer) and world > 1
     dp = DataParallelStep(NetEngine(net, torch.device("cuda", local_rank)), GLOBAL_BATCH, parts=parts, shard_optimiser=shard,
-                          peer_exchange=peer)
+                          peer_exchange=peer, peer_overlap=peer and parts == 1 and bool(args.dp_overlap))
     peer, shard, parts = dp.peer, dp.shard, dp.parts  # what is really in use (peer mapping can be refused by the box)
     lr = cfg.lr
 
@@ -399,7 +399,10 @@ def run_ours(args, rank, world, local_rank):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
                    "parallelism": f"dp{world}",
-                   "exchange": ("one kernel over peer memory: peer loads of all gradients, AdamW on 1/N, peer stores of the weights"
+                   "exchange": ("one kernel over peer memory, run under the feature-transformer backward on SMs of its own: "
+                                "finished row blocks are announced to all ranks; peer loads of all gradients, AdamW on 1/N, "
+                                "peer stores of the weights" if peer and dp.overlap else
+                                "one kernel over peer memory: peer loads of all gradients, AdamW on 1/N, peer stores of the weights"
                                 if peer else
                                 f"reduce-scatter + sharded AdamW + all-gather in {parts} slices, gathers under the next forward"
                                 if shard and parts > 1 else "reduce-scatter + sharded AdamW + all-gather" if shard else
@@ -440,6 +443,8 @@ def main():
     ap.add_argument("--dp-peer", type=int, default=1,
                     help="N > 1: 1 = the exchange as one library kernel over peer memory (reduce + AdamW + gather); "
                          "0, or a box that refuses the peer mapping = NCCL collectives (--dp-shard)")
+    ap.add_argument("--dp-overlap", type=int, default=1,
+                    help="N > 1 with --dp-peer 1: 1 = the exchange kernel runs under the backward pass (b200_step_exchange)")
     ap.add_argument("--dp-parts", type=int, default=1,
                     help="N > 1: slices of l0w exchanged while the backward (and, with --dp-shard 1, the next forward) still runs")
     ap.add_argument("--cpu-sample", type=int, default=16384,

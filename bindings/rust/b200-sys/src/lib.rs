@@ -155,6 +155,8 @@ extern "C" {
     pub fn b200_exchange_export(net: *mut b200_net, handles: *mut c_void, bytes: i64) -> c_int;
     pub fn b200_exchange_import(net: *mut b200_net, rank: c_int, world: c_int, handles: *const c_void, bytes: i64) -> c_int;
     pub fn b200_update_exchange(net: *mut b200_net, lr: f32, grad_factor: f32) -> c_int;
+    /// One data-parallel step with the exchange hidden under the feature-transformer backward.
+    pub fn b200_step_exchange(net: *mut b200_net, slot: c_int, lr: f32, grad_factor: f32) -> c_int;
     pub fn b200_update_exchange_range(
         net: *mut b200_net,
         lr: f32,

@@ -23,7 +23,7 @@ SYMBOLS = (
     "b200_saved_format_write", "b200_save_quantised", "b200_save_unquantised",
     "b200_forward_begin", "b200_forward_ft", "b200_net_tensor_offset",
     "b200_exchange_export", "b200_exchange_import", "b200_update_exchange", "b200_update_exchange_range",
-    "b200_grad_zero_range", "b200_batch_upload_records", "b200_set_host_threads",
+    "b200_grad_zero_range", "b200_batch_upload_records", "b200_set_host_threads", "b200_step_exchange",
 )
 
 
@@ -94,6 +94,7 @@ def load() -> ctypes.CDLL:
         "b200_exchange_export": [vp, vp, i64],
         "b200_exchange_import": [vp, ctypes.c_int, ctypes.c_int, vp, i64],
         "b200_update_exchange": [vp, f32, f32],
+        "b200_step_exchange": [vp, ctypes.c_int, f32, f32],
         "b200_update_exchange_range": [vp, f32, f32, i64, i64, ctypes.c_int, vp],
         "b200_grad_zero_range": [vp, i64, i64],
         "b200_backward_begin": [vp, ctypes.c_int],

@@ -24,6 +24,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "peer_flags.cuh"
+
 namespace b200 {
 
 constexpr uint32_t kNoFeature = 0xFFFFu;
@@ -47,26 +49,32 @@ struct FtArgs {
 struct TileArgs {
     int block_rows;          // R
     int nslabs;              // H/64 column slabs
-    // Work items: a launch runs one CTA per (item, slab); consecutive CTAs share an item.
-    // forward: (block, first, last+1 index into pair_order, 0); backward: (block, first chunk,
-    // last+1 chunk, 0).  Items of one block are near-equal in size however full the block is.
-    const int4* items;
+    // A launch covers the row blocks [first_block, last_block) with gridDim.x CTAs.  The work of those
+    // blocks is laid out in one line (block by block; inside a block column slab by column slab; inside a
+    // slab pair by pair, for the backward chunk by chunk) and CTA k takes the k-th of gridDim.x near-equal
+    // contiguous pieces of that line: every SM gets the same amount of work whatever the blocks hold, and
+    // a tile is loaded about once per (block, slab) and SM that touches it.
+    int first_block, last_block;
     const int* pair_order;   // [2n] pair ids (position*2 + perspective) grouped by block, or null = identity
     const int* block_begin;  // [nblocks+1] offsets into pair_order
+    const int* chunk_begin;  // backward: [nblocks+1] first chunk of every block
     int* status;
     // written by ft_prepare_kernel, read by the tiled kernels: for the i-th pair in visiting
-    // order its active rows (local to the pair's block), padded to a multiple of four with the
-    // index of the all-zero row (= block_rows)
+    // order its active rows (local to the pair's block) in slot order; the tail of the last
+    // 16-byte group is filled with the index of the all-zero row (= block_rows) and never walked
     uint16_t* lists;  // [2n][list_len]
-    int* list_count;  // [2n] padded length (multiple of 4)
-    int list_len;     // nnz rounded up to a multiple of 4
+    int* list_count;  // [2n] number of active rows
+    int list_len;     // nnz rounded up to a multiple of 8 (16-byte groups)
     // backward only: the visiting order cut into chunks of at most ft_bwd_chunk pairs that never
     // straddle a block, and per chunk the row-major lists built by ft_csr_kernel
     const int4* chunks;            // [nchunks] (block, first index into pair_order, pairs, 0)
-    uint16_t* csr_ent;             // [nchunks][ent_cap] positions of the chunk grouped by row, lists padded to x4
-    int* csr_start;                // [nchunks][start_cap] start of every row's list; start[R] = total
+    uint16_t* csr_ent;             // [nchunks][ent_cap] pairs of the chunk grouped by row, every list starting on 16 bytes
+    int* csr_start;                // [nchunks][start_cap] per row (start / 8) << 16 | length; [R] = entries in all
     int ent_cap, start_cap;
     int chunk_len;  // CP: most pairs per chunk
+    // backward only, data-parallel runs: the last CTA of every row block tells all ranks that the block's
+    // gradient is complete (done_count null: nobody is told)
+    BucketSignal sig;
 };
 
 __device__ __forceinline__ float crelu_f(float v) { return fminf(fmaxf(v, 0.f), 1.f); }
@@ -261,27 +269,14 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
-struct TileWork {
-    int block, slab, begin, end;  // forward: pair_order range [begin, end); backward: chunk range
-};
-__device__ __forceinline__ TileWork tile_work(const TileArgs& t) {
-    const int4 item = t.items[blockIdx.x / t.nslabs];
-    TileWork w;
-    w.slab = blockIdx.x % t.nslabs;
-    w.block = item.x;
-    w.begin = item.y;
-    w.end = item.z;
-    return w;
-}
-
 __device__ __forceinline__ const uint16_t* pair_list(const FtArgs& a, int pair) {
     return ((pair & 1) ? a.idx_nstm : a.idx_stm) + (size_t)(pair >> 1) * a.nnz;
 }
 
 // Per batch, once: turns every (position, perspective) pair's slots into the list the tiled
-// kernels walk — rows local to the pair's block, compacted in slot order and padded to a
-// multiple of four with the index of the all-zero row.  A valid feature outside the block raises the status bit and is dropped.  One warp
-// per pair, in visiting order.  grid = ceil(2n / 8), block = 256.
+// kernels walk — rows local to the pair's block, compacted in slot order, the last 16-byte
+// group filled up with the index of the all-zero row.  A valid feature outside the block raises
+// the status bit and is dropped.  One warp per pair, in visiting order.  grid = ceil(2n / 8), block = 256.
 static __global__ void __launch_bounds__(256) ft_prepare_kernel(FtArgs a, TileArgs t) {
     const int lane = threadIdx.x & 31;
     const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -302,20 +297,25 @@ static __global__ void __launch_bounds__(256) ft_prepare_kernel(FtArgs a, TileAr
     if ((v0 && !in0) || (v1 && !in1)) atomicOr(t.status, kStatusOutsideBlock);
     const unsigned m0 = __ballot_sync(0xffffffffu, in0), m1 = __ballot_sync(0xffffffffu, in1);
     const unsigned lt = (1u << lane) - 1u;
-    const int cnt0 = __popc(m0), cnt = cnt0 + __popc(m1), cnt4 = (cnt + 3) & ~3;
+    const int cnt0 = __popc(m0), cnt = cnt0 + __popc(m1), cnt8 = (cnt + 7) & ~7;
     uint16_t* list = t.lists + (size_t)i * t.list_len;
     if (in0) list[__popc(m0 & lt)] = (uint16_t)row0;
     if (in1) list[cnt0 + __popc(m1 & lt)] = (uint16_t)row1;
-    if (lane < cnt4 - cnt) list[cnt + lane] = (uint16_t)t.block_rows;
-    if (lane == 0) t.list_count[i] = cnt4;
+    if (lane < cnt8 - cnt) list[cnt + lane] = (uint16_t)t.block_rows;
+    if (lane == 0) t.list_count[i] = cnt;
 }
 
-// Forward.  grid = items * nslabs CTAs of 1024 threads (one per SM); dynamic
-// shared memory = (R+1) tile rows, the extra row all zero.  Each warp serves one
-// (position, perspective) at a time: it walks the pair's prepared list four offsets per
-// (warp-uniform) load, and every lane adds its column pair with one 64-bit shared-memory
-// load and one packed add per row, in slot order — the same order and arithmetic as the
-// interpreter (adding the zero row changes nothing).
+// One 256-byte line of shared memory (a tile row, or a staged gradient line), this lane's 8 bytes of it.
+__device__ __forceinline__ f32x2 line_at(const unsigned char* mine, uint32_t index) {
+    return *reinterpret_cast<const f32x2*>(mine + index * kTileRowBytes);
+}
+
+// Forward.  One CTA of 1024 threads per SM; dynamic shared memory = (R+1) tile rows, the extra row all
+// zero.  A CTA walks its piece of the work line segment by segment; a segment is a run of pairs of one
+// (block, slab), whose tile the CTA loads first.  Each warp serves one (position, perspective) at a time:
+// it walks the pair's prepared list four rows per (warp-uniform) 8-byte load, and every lane adds its
+// column pair with one 64-bit shared-memory load and one packed add per row, in slot order — the same
+// order and arithmetic as the interpreter (adding the zero row changes nothing).
 constexpr int kFwdThreads = 1024;
 __host__ __device__ inline size_t ft_fwd_smem(int R) { return (size_t)(R + 1) * kTileRowBytes; }
 
@@ -324,92 +324,110 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int NW = kFwdThreads / 32;
-    const TileWork w = tile_work(t);
     const int R = t.block_rows;
     float* tile = reinterpret_cast<float*>(smem_raw);
-    {   // fill the tile: 8 work items per row, each 8 floats of the row
-        // with a factoriser the table row is l0w[row] + l0f[row mod factor_rows], one fp32 add per
-        // element exactly as the reference forms `l0w + l0f.repeat(n)` (model/builder.rs:421-424)
-        const float* src = a.table + (size_t)w.block * R * a.H;
-        for (int i = threadIdx.x; i < R * 8; i += kFwdThreads) {
-            const int row = i >> 3, q = i & 7;
-            float4* dst = reinterpret_cast<float4*>(tile + row * kTileCols + q * 8);
-            const float* frow = a.factor ? a.factor + (size_t)((w.block * R + row) % a.factor_rows) * a.H : nullptr;
-            if (PAIRWISE) {
-                const int c_lo = w.slab * 32 + q * 4, c_hi = a.H / 2 + c_lo;
-                float4 lo = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_lo));
-                float4 hi = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_hi));
-                if (frow) {
-                    lo = add4(lo, __ldg(reinterpret_cast<const float4*>(frow + c_lo)));
-                    hi = add4(hi, __ldg(reinterpret_cast<const float4*>(frow + c_hi)));
-                }
-                dst[0] = make_float4(lo.x, hi.x, lo.y, hi.y);
-                dst[1] = make_float4(lo.z, hi.z, lo.w, hi.w);
-            } else {
-                const int c0 = w.slab * 64 + q * 8;
-                const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c0);
-                float4 v0 = __ldg(g), v1 = __ldg(g + 1);
-                if (frow) {
-                    v0 = add4(v0, __ldg(reinterpret_cast<const float4*>(frow + c0)));
-                    v1 = add4(v1, __ldg(reinterpret_cast<const float4*>(frow + c0 + 4)));
-                }
-                dst[0] = v0;
-                dst[1] = v1;
-            }
-        }
-        if (threadIdx.x < kTileCols) tile[R * kTileCols + threadIdx.x] = 0.f;
-    }
-    const int col_a = tile_col_a<PAIRWISE>(w.slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(w.slab, lane, a.H);
-    const f32x2 bias = pack2(a.bias[col_a], a.bias[col_b]);
-    __syncthreads();
+    // this CTA's piece [v, v_end) of the line of nslabs x (pairs of the launch's blocks) positions
+    const int pair0 = t.block_begin[t.first_block];
+    const long long line = (long long)t.nslabs * (t.block_begin[t.last_block] - pair0);
+    long long v = line * blockIdx.x / gridDim.x;
+    const long long v_end = line * (blockIdx.x + 1) / gridDim.x;
+    int block = t.first_block;
+    if (threadIdx.x < kTileCols) tile[R * kTileCols + threadIdx.x] = 0.f;  // the zero row
     const unsigned char* mine = smem_raw + lane * 8;
     // outputs of pair p start at p * (row length): x is [n][2 persp][H or H/2], u is [n][2][H]
     const int x_row = PAIRWISE ? a.H / 2 : a.H;
-    float* x_out = a.x + col_a;  // with pairwise col_a is also the product's column within the perspective
-    // pair id and list length are fetched one position ahead
-    int i = w.begin + warp;
-    int pair = 0, cnt4 = 0;
-    if (i < w.end) {
-        pair = t.pair_order ? t.pair_order[i] : i;
-        cnt4 = t.list_count[i];
-    }
-    for (; i < w.end; i += NW) {
-        int pair_next = 0, cnt4_next = 0;
-        if (i + NW < w.end) {
-            pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
-            cnt4_next = t.list_count[i + NW];
+    while (v < v_end) {
+        // the segment v lies in: block, slab, first pair
+        long long base = (long long)t.nslabs * (t.block_begin[block] - pair0);
+        int in_block = t.block_begin[block + 1] - t.block_begin[block];
+        while (v >= base + (long long)t.nslabs * in_block) {
+            base += (long long)t.nslabs * in_block;
+            block++;
+            in_block = t.block_begin[block + 1] - t.block_begin[block];
         }
-        const uint2* list = reinterpret_cast<const uint2*>(t.lists + (size_t)i * t.list_len);
-        f32x2 acc = 0;  // (+0.0f, +0.0f)
-        for (int k = 0; k < cnt4; k += 4) {
-            const uint2 q = __ldg(list + (k >> 2));  // four row indices, the same for every lane
-            const f32x2 v0 = *reinterpret_cast<const f32x2*>(mine + (q.x & 0xffffu) * kTileRowBytes);
-            const f32x2 v1 = *reinterpret_cast<const f32x2*>(mine + (q.x >> 16) * kTileRowBytes);
-            const f32x2 v2 = *reinterpret_cast<const f32x2*>(mine + (q.y & 0xffffu) * kTileRowBytes);
-            const f32x2 v3 = *reinterpret_cast<const f32x2*>(mine + (q.y >> 16) * kTileRowBytes);
-            acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
+        const int slab = (int)((v - base) / in_block), first = (int)((v - base) % in_block);
+        const int last = (int)min((long long)in_block, first + (v_end - v));
+        v += last - first;
+        __syncthreads();  // every warp has left the previous tile
+        {   // fill the tile: 8 work items per row, each 8 floats of the row
+            // with a factoriser the table row is l0w[row] + l0f[row mod factor_rows], one fp32 add per
+            // element exactly as the reference forms `l0w + l0f.repeat(n)` (model/builder.rs:421-424)
+            const float* src = a.table + (size_t)block * R * a.H;
+            for (int i = threadIdx.x; i < R * 8; i += kFwdThreads) {
+                const int row = i >> 3, q = i & 7;
+                float4* dst = reinterpret_cast<float4*>(tile + row * kTileCols + q * 8);
+                const float* frow = a.factor ? a.factor + (size_t)((block * R + row) % a.factor_rows) * a.H : nullptr;
+                if (PAIRWISE) {
+                    const int c_lo = slab * 32 + q * 4, c_hi = a.H / 2 + c_lo;
+                    float4 lo = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_lo));
+                    float4 hi = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_hi));
+                    if (frow) {
+                        lo = add4(lo, __ldg(reinterpret_cast<const float4*>(frow + c_lo)));
+                        hi = add4(hi, __ldg(reinterpret_cast<const float4*>(frow + c_hi)));
+                    }
+                    dst[0] = make_float4(lo.x, hi.x, lo.y, hi.y);
+                    dst[1] = make_float4(lo.z, hi.z, lo.w, hi.w);
+                } else {
+                    const int c0 = slab * 64 + q * 8;
+                    const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c0);
+                    float4 v0 = __ldg(g), v1 = __ldg(g + 1);
+                    if (frow) {
+                        v0 = add4(v0, __ldg(reinterpret_cast<const float4*>(frow + c0)));
+                        v1 = add4(v1, __ldg(reinterpret_cast<const float4*>(frow + c0 + 4)));
+                    }
+                    dst[0] = v0;
+                    dst[1] = v1;
+                }
+            }
         }
-        acc = add2(acc, bias);
-        if (PAIRWISE) {
-            const float ua = crelu_f(lo2(acc)), ub = crelu_f(hi2(acc));
-            float* up = a.u + (size_t)pair * a.H;
-            up[col_a] = ua;
-            up[col_b] = ub;
-            x_out[(size_t)pair * x_row] = ua * ub;
-        } else {
-            *reinterpret_cast<float2*>(x_out + (size_t)pair * x_row) =
-                make_float2(ft_act_fwd(a.act, lo2(acc)), ft_act_fwd(a.act, hi2(acc)));
+        const int col_a = tile_col_a<PAIRWISE>(slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(slab, lane, a.H);
+        const f32x2 bias = pack2(a.bias[col_a], a.bias[col_b]);
+        float* x_out = a.x + col_a;  // with pairwise col_a is also the product's column within the perspective
+        __syncthreads();
+        // pair id and list length are fetched one position ahead
+        const int seg_end = t.block_begin[block] + last;
+        int i = t.block_begin[block] + first + warp;
+        int pair = 0, cnt = 0;
+        if (i < seg_end) {
+            pair = t.pair_order ? t.pair_order[i] : i;
+            cnt = t.list_count[i];
         }
-        pair = pair_next;
-        cnt4 = cnt4_next;
+        for (; i < seg_end; i += NW) {
+            int pair_next = 0, cnt_next = 0;
+            if (i + NW < seg_end) {
+                pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
+                cnt_next = t.list_count[i + NW];
+            }
+            const uint2* list = reinterpret_cast<const uint2*>(t.lists + (size_t)i * t.list_len);
+            f32x2 acc = 0;  // (+0.0f, +0.0f)
+            for (int k = 0; k < cnt; k += 4) {
+                const uint2 g = __ldg(list + (k >> 2));  // the same for every lane
+                const f32x2 v0 = line_at(mine, g.x & 0xffffu), v1 = line_at(mine, g.x >> 16);
+                const f32x2 v2 = line_at(mine, g.y & 0xffffu), v3 = line_at(mine, g.y >> 16);
+                acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
+            }
+            acc = add2(acc, bias);
+            if (PAIRWISE) {
+                const float ua = crelu_f(lo2(acc)), ub = crelu_f(hi2(acc));
+                float* up = a.u + (size_t)pair * a.H;
+                up[col_a] = ua;
+                up[col_b] = ub;
+                x_out[(size_t)pair * x_row] = ua * ub;
+            } else {
+                *reinterpret_cast<float2*>(x_out + (size_t)pair * x_row) =
+                    make_float2(ft_act_fwd(a.act, lo2(acc)), ft_act_fwd(a.act, hi2(acc)));
+            }
+            pair = pair_next;
+            cnt = cnt_next;
+        }
     }
 }
 
 // Backward.  Positions are visited in chunks of at most CP pairs of one row block.
 //   ft_csr_kernel (one CTA per chunk, once per batch) turns the chunk's prepared lists around:
 //     for every table row of the block, the list of the chunk's pairs that hold it (a count
-//     pass, a scan and a fill pass in shared memory), every list padded to a multiple of four
-//     entries that point at an all-zero line.  All column slabs share the result.
+//     pass, a scan and a fill pass in shared memory), every list starting on a 16-byte
+//     boundary and stored with its exact length.  All column slabs share the result.
 //   ft_backward_tiled_kernel (same grid as the forward) then, per chunk, copies that list
 //     structure into shared memory, stages the chunk's pre-activation gradients (from dx and
 //     the kept activations) as one 64-float line per pair, and every warp walks the lists of
@@ -423,8 +441,8 @@ constexpr int kCsrThreads = 512;
 // pairs, otherwise two CTAs of 512 threads on chunks of 256, so that one CTA's global loads
 // overlap the other's shared-memory work.  Chunks halve when nnz > 32.
 __host__ __device__ inline int ft_bwd_chunk(int nnz, bool wide) { return (wide ? 512 : 256) / (nnz <= 32 ? 1 : 2); }
-// entries per chunk: every slot of every pair plus up to three padding entries per row, rounded to 16 bytes
-__host__ __device__ inline int ft_bwd_ent_cap(int R, int nnz, int cp) { return (cp * ((nnz + 3) & ~3) + 4 * R + 7) & ~7; }
+// entries per chunk: every slot of every pair plus up to seven padding entries per row (lists start on 16 bytes)
+__host__ __device__ inline int ft_bwd_ent_cap(int R, int nnz, int cp) { return (cp * nnz + 8 * R + 7) & ~7; }
 __host__ __device__ inline int ft_bwd_start_cap(int R) { return (R + 1 + 3) & ~3; }
 __host__ __device__ inline size_t ft_bwd_smem(int R, int nnz, int cp) {
     return (size_t)(cp + 1) * kTileRowBytes + (size_t)ft_bwd_ent_cap(R, nnz, cp) * 2 + (size_t)ft_bwd_start_cap(R) * 4 + (size_t)cp * 4;
@@ -466,12 +484,12 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
                 if (o[k] != zero_row) atomicAdd(&cursor[o[k]], 1);
         }
     __syncthreads();
-    // exclusive scan of the row counts, each rounded up to a multiple of four
+    // exclusive scan of the row counts, each rounded up to a multiple of eight entries (16 bytes)
     {
         int carry = 0;
         for (int base = 0; base < R; base += kCsrThreads) {
             const int r = base + threadIdx.x;
-            const int v = r < R ? (cursor[r] + 3) & ~3 : 0;
+            const int v = r < R ? (cursor[r] + 7) & ~7 : 0;
             int incl = v;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -510,37 +528,108 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
                 if (o[k] != zero_row) ent[atomicAdd(&cursor[o[k]], 1)] = (uint16_t)(pl0 + k * NW);
         }
     __syncthreads();
-    // pad every list to its rounded length with the all-zero line (index CP)
+    // the unused tail of every list's last 16-byte group points at the all-zero line (index CP)
     for (int r = threadIdx.x; r < R; r += kCsrThreads)
         for (int e = cursor[r]; e < start[r + 1]; e++) ent[e] = (uint16_t)CP;
     __syncthreads();
-    // publish (8-byte and 16-byte copies; both arrays are sized in multiples of four)
+    // publish: the entries in 16-byte pieces, and per row its start (in 16-byte units) and exact length
     const int total = start[R];
-    uint2* ent_out = reinterpret_cast<uint2*>(t.csr_ent + (size_t)blockIdx.x * t.ent_cap);
-    for (int i = threadIdx.x; i < total / 4; i += kCsrThreads) ent_out[i] = reinterpret_cast<const uint2*>(ent)[i];
+    uint4* ent_out = reinterpret_cast<uint4*>(t.csr_ent + (size_t)blockIdx.x * t.ent_cap);
+    for (int i = threadIdx.x; i < total / 8; i += kCsrThreads) ent_out[i] = reinterpret_cast<const uint4*>(ent)[i];
     int* start_out = t.csr_start + (size_t)blockIdx.x * t.start_cap;
-    for (int i = threadIdx.x; i <= R; i += kCsrThreads) start_out[i] = start[i];
+    for (int r = threadIdx.x; r < R; r += kCsrThreads) start_out[r] = ((start[r] >> 3) << 16) | (cursor[r] - start[r]);
+    if (threadIdx.x == 0) start_out[R] = total;
 }
 
-// grid = items * nslabs CTAs of THREADS threads (1024: one per SM; 512: two per SM).
-template <bool PAIRWISE, int THREADS>
+// The backward's work line: block b contributes, per column slab, its pairs plus a fixed amount per chunk
+// (the list copy and the one reduction per row cost about as much as this many pairs).  A unit is one
+// (block, slab, chunk); units are numbered block by block, slab by slab, chunk by chunk.
+constexpr int kChunkFixed = 96;
+__host__ __device__ inline long long ft_bwd_block_weight(int pairs, int chunks) { return pairs + (long long)kChunkFixed * chunks; }
+__host__ __device__ inline long long ft_bwd_line(const int* block_begin, const int* chunk_begin, int first_block, int last_block, int nslabs) {
+    long long line = 0;
+    for (int b = first_block; b < last_block; b++)
+        line += nslabs * ft_bwd_block_weight(block_begin[b + 1] - block_begin[b], chunk_begin[b + 1] - chunk_begin[b]);
+    return line;
+}
+// the unit that holds position `at` of the line (the number of units if `at` is the line's end)
+__host__ __device__ inline int ft_bwd_unit_at(long long at, const int* block_begin, const int* chunk_begin, int first_block, int last_block,
+                                              int nslabs) {
+    long long base = 0;
+    int units = 0;
+    for (int b = first_block; b < last_block; b++) {
+        const int nch = chunk_begin[b + 1] - chunk_begin[b];
+        const long long wb = ft_bwd_block_weight(block_begin[b + 1] - block_begin[b], nch);
+        if (nch > 0 && at < base + nslabs * wb) {
+            const long long local = at - base, within = local % wb;
+            const int slab = (int)(local / wb);
+            const int pairs = block_begin[b + 1] - block_begin[b];
+            const long long j = within / ((pairs + nch - 1) / nch + kChunkFixed);  // a block's chunks are of equal size
+            return units + slab * nch + (int)(j < nch - 1 ? j : nch - 1);
+        }
+        base += nslabs * wb;
+        units += nslabs * nch;
+    }
+    return units;
+}
+
+// grid = one CTA of 1024 threads per SM (or two of 512); CTA k takes the units between the k-th and
+// the (k+1)-th of gridDim.x equal cuts of the work line.
+template <bool PAIRWISE, int THREADS, bool SIGNAL>
 __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int kBwdThreads = THREADS;
     constexpr int NW = kBwdThreads / 32;
-    const TileWork w = tile_work(t);
-    const int slab = w.slab, block = w.block;
     const int R = t.block_rows, CP = t.chunk_len;
     f32x2* g_s = reinterpret_cast<f32x2*>(smem_raw);                                          // [CP + 1][32] (A, B) pairs
     uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists of the chunk
     int* start = reinterpret_cast<int*>(ent + t.ent_cap);                                     // [R + 1]
     int* pairs_s = start + t.start_cap;                                                       // [CP] pair ids of the chunk
-    const int col_a = tile_col_a<PAIRWISE>(slab, lane, a.H), col_b = tile_col_b<PAIRWISE>(slab, lane, a.H);
-    float bsum_a = 0.f, bsum_b = 0.f;
-    if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line
+    if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line that list padding points at
 
-    for (int ch = w.begin; ch < w.end; ch++) {
+    const long long line = ft_bwd_line(t.block_begin, t.chunk_begin, t.first_block, t.last_block, t.nslabs);
+    const int u_begin = ft_bwd_unit_at(line * blockIdx.x / gridDim.x, t.block_begin, t.chunk_begin, t.first_block, t.last_block, t.nslabs);
+    const int u_end = ft_bwd_unit_at(line * (blockIdx.x + 1) / gridDim.x, t.block_begin, t.chunk_begin, t.first_block, t.last_block, t.nslabs);
+
+    // sums of the bias gradient live in registers while the slab stays the same
+    float bsum_a = 0.f, bsum_b = 0.f;
+    int col_a = 0, col_b = 0, slab = -1, block = -1;
+    auto flush_bias = [&]() {  // every pair's gradient once, summed over the warps (all threads call this)
+        float* red = reinterpret_cast<float*>(smem_raw);
+        red[warp * kTileCols + lane] = bsum_a;
+        red[warp * kTileCols + 32 + lane] = bsum_b;
+        __syncthreads();
+        if (warp == 0) {
+            float sa = 0.f, sb = 0.f;
+            for (int k = 0; k < NW; k++) {
+                sa += red[k * kTileCols + lane];
+                sb += red[k * kTileCols + 32 + lane];
+            }
+            if (sa != 0.f) atomicAdd(a.g_bias + col_a, sa);
+            if (sb != 0.f) atomicAdd(a.g_bias + col_b, sb);
+        }
+        bsum_a = bsum_b = 0.f;
+    };
+
+    int scan_block = t.first_block, scan_base = 0;  // units before scan_block
+    for (int u = u_begin; u < u_end; u++) {
+        int nch = t.chunk_begin[scan_block + 1] - t.chunk_begin[scan_block];
+        while (u >= scan_base + t.nslabs * nch) {
+            scan_base += t.nslabs * nch;
+            scan_block++;
+            nch = t.chunk_begin[scan_block + 1] - t.chunk_begin[scan_block];
+        }
+        const int local = u - scan_base, new_slab = local / nch, ch = t.chunk_begin[scan_block] + local % nch;
+        if (new_slab != slab || scan_block != block) {
+            if (slab >= 0 && new_slab != slab) flush_bias();
+            // leaving a block: its gradient from this CTA is complete (data-parallel runs announce it)
+            if (SIGNAL && block >= 0 && scan_block != block) bucket_signal(t.sig, block);
+            slab = new_slab;
+            block = scan_block;
+            col_a = tile_col_a<PAIRWISE>(slab, lane, a.H);
+            col_b = tile_col_b<PAIRWISE>(slab, lane, a.H);
+        }
         const int4 chunk = t.chunks[ch];
         const int c0 = chunk.y, cn = chunk.z;
         // the chunk's row lists: asynchronous copy into shared memory, overlapped with the staging below
@@ -592,17 +681,17 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         }
         cp_async_wait_all();
         __syncthreads();
-        // accumulate: each warp walks the lists of the rows it owns
+        // accumulate: each warp walks the lists of the rows it owns, four entries per 8-byte load
         const unsigned char* gl = smem_raw + lane * 8;
         for (int row = warp; row < R; row += NW) {
-            const int e1 = start[row + 1];
+            const unsigned sl = (unsigned)start[row];
+            const int len = (int)(sl & 0xffffu);
+            const uint2* lp = reinterpret_cast<const uint2*>(ent + (sl >> 16) * 8);
             f32x2 acc = 0;
-            for (int e = start[row]; e < e1; e += 4) {
-                const uint2 q = *reinterpret_cast<const uint2*>(ent + e);
-                const f32x2 v0 = *reinterpret_cast<const f32x2*>(gl + (q.x & 0xffffu) * kTileRowBytes);
-                const f32x2 v1 = *reinterpret_cast<const f32x2*>(gl + (q.x >> 16) * kTileRowBytes);
-                const f32x2 v2 = *reinterpret_cast<const f32x2*>(gl + (q.y & 0xffffu) * kTileRowBytes);
-                const f32x2 v3 = *reinterpret_cast<const f32x2*>(gl + (q.y >> 16) * kTileRowBytes);
+            for (int k = 0; k < len; k += 4) {
+                const uint2 g = lp[k >> 2];
+                const f32x2 v0 = line_at(gl, g.x & 0xffffu), v1 = line_at(gl, g.x >> 16);
+                const f32x2 v2 = line_at(gl, g.y & 0xffffu), v3 = line_at(gl, g.y >> 16);
                 acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
             }
             float* dst = a.g_table + (size_t)(block * R + row) * a.H;
@@ -616,20 +705,8 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         }
         __syncthreads();
     }
-    // bias gradient: every pair's gradient once, summed over the warps
-    float* red = reinterpret_cast<float*>(smem_raw);
-    red[warp * kTileCols + lane] = bsum_a;
-    red[warp * kTileCols + 32 + lane] = bsum_b;
-    __syncthreads();
-    if (warp == 0) {
-        float sa = 0.f, sb = 0.f;
-        for (int k = 0; k < NW; k++) {
-            sa += red[k * kTileCols + lane];
-            sb += red[k * kTileCols + 32 + lane];
-        }
-        if (sa != 0.f) atomicAdd(a.g_bias + col_a, sa);
-        if (sb != 0.f) atomicAdd(a.g_bias + col_b, sb);
-    }
+    if (slab >= 0) flush_bias();
+    if (SIGNAL && block >= 0) bucket_signal(t.sig, block);
 }
 
 // ------------------------------------------------------- factoriser helper kernels

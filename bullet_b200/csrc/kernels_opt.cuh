@@ -15,6 +15,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "peer_flags.cuh"
+
 namespace b200 {
 
 constexpr int kMaxSegments = 12;
@@ -79,61 +81,6 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(const __grid_constant__
 // The launch sits between two cross-rank fences: every rank's gradients complete before, every
 // rank's launch complete after.  Either the caller provides them (any tiny collective), or
 // wait_ready makes the kernel itself wait, bounded, for the peers' counters (see PeerFlags).
-constexpr int kMaxRanks = 8;
-
-// Cross-rank fences of the exchange, without a collective: every rank owns an array of counters
-// that its peers write with release stores over NVLink and that it polls locally.
-//   [kFlagReady + r]  rank r's gradients of step n are complete      (value n)
-//   [kFlagDone + r]   rank r's exchange kernel of step n has finished (value n)
-//   [kFlagTimeout]    a wait of this rank gave up
-// Every wait is bounded (about four seconds); when it gives up it raises the timeout word, which the
-// host reports with the step's loss, and the kernel carries on so that the stream never hangs.
-constexpr int kFlagReady = 0, kFlagDone = kMaxRanks, kFlagTimeout = 2 * kMaxRanks, kFlagInts = 2 * kMaxRanks + 8;
-constexpr long long kPeerWaitSpins = 20000000;  // default spin_limit
-
-struct PeerFlags {
-    int* flags[kMaxRanks];  // every rank's counter array, own included, by rank
-    int world, rank;
-    long long spin_limit;   // polls (each at least 200 ns apart) before a wait gives up
-};
-
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Called by one thread: waits until every rank has written at least `value` at `base`.
-__device__ __forceinline__ bool peer_wait(const PeerFlags& f, int base, int value) {
-    int* mine = f.flags[f.rank];
-    long long spins = 0;  // one budget for all ranks together
-    for (int r = 0; r < f.world; r++) {
-        while (ld_acquire_sys(mine + base + r) < value) {
-            __nanosleep(200);
-            if (++spins > f.spin_limit) {
-                atomicOr(mine + kFlagTimeout, 1);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// Everything this rank's stream has done so far is complete: tell every rank.  grid = 1, block = 32.
-static __global__ void peer_signal_kernel(PeerFlags f, int base, int value) {
-    if ((int)threadIdx.x < f.world) {
-        __threadfence_system();
-        st_release_sys(f.flags[threadIdx.x] + base + f.rank, value);
-    }
-}
-// The stream goes on only after every rank has signalled `value` at `base` (or the wait gave up).
-static __global__ void peer_wait_kernel(PeerFlags f, int base, int value) {
-    if (threadIdx.x == 0) peer_wait(f, base, value);
-}
-
 struct ExchangeArgs {
     AdamArgs adam;               // local p, m, v; first4 / total4 = this rank's share; g unused
     const float4* g[kMaxRanks];  // gradient buffer of every rank, own included, by rank
@@ -155,10 +102,8 @@ __global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_con
     constexpr int W = WORLD > 0 ? WORLD : kMaxRanks;  // loads held per element
     constexpr int U = WORLD > 0 ? kMaxRanks / WORLD : 1;  // elements per thread and round
     const AdamArgs& a = x.adam;
-    if (x.wait_ready > 0) {
-        if (threadIdx.x == 0) peer_wait(x.flags, kFlagReady, x.wait_ready);
-        __syncthreads();
-    }
+    // a fence that gave up means some rank's gradients may be incomplete: leave everything as it is
+    if (x.wait_ready > 0 && !peer_wait_cta(x.flags, kFlagReady, x.wait_ready)) return;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long j0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; j0 < a.total4; j0 += stride * U) {
         float4 gr[U][W];
@@ -205,6 +150,152 @@ __global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_con
                 a.p[i] = p;
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same exchange, run UNDER the feature-transformer backward instead of after it.
+//
+// The backward's work items are ordered by table row block (king bucket), so the gradient of block b
+// is complete long before the kernel ends; the last CTA of every block says so to every rank
+// (bucket_signal, called at the end of the backward kernel; empty blocks are announced up front by
+// bucket_presignal_kernel).  This kernel is launched before the backward on a stream of higher
+// priority, as a few CTAs that each fill an SM (the dynamic shared memory they ask for is only there
+// to keep other CTAs off that SM, so the backward simply runs on the SMs that are left).  It walks the
+// blocks in order: wait until all ranks have announced block b, sum this rank's 1/world share of the
+// block's gradient over all ranks with peer loads (rank order: one owner per element, so the replicas
+// stay bit-identical), AdamW, peer stores of the new weights to every rank.  Only the last block's
+// share, the factoriser and the small tensors are left when the backward ends.
+//
+// Factoriser (l0f, as large as one block): its gradient is the sum of the table gradient over the
+// blocks.  The owner of share r of every block also owns share r of l0f and keeps the running sum of
+// the already reduced block gradients in `facc`, in block order; no separate pass over the table
+// gradient is needed.  The small tensors (bias, dense layers, the loss in float 0) are reduced and
+// updated by every rank for itself after the all-complete fence (kFlagReady), without peer stores.
+//
+// Every wait is bounded; a wait that gives up makes the CTA return at once (see peer_wait).
+struct OverlapArgs {
+    ExchangeArgs x;      // local p, m, v and the segment table; every rank's g and p; flags
+    int step;            // the value the ranks announce this step
+    int nblocks;
+    long long l0w4;      // first float4 of l0w in the flat buffers
+    long long block4;    // float4s per row block
+    int l0w_seg;         // index of l0w in the segment table
+    int l0f_seg;         // index of l0f there when it is summed through facc, else -1
+    long long l0f4;      // first float4 of l0f
+    float4* facc;        // [block4 / world] running block sum of this rank's share, or null
+};
+
+constexpr int kOverlapThreads = 512;      // up to 128 registers each: sixteen 16-byte peer loads in flight per thread
+constexpr int kOverlapSmem = 120 * 1024;  // more than half an SM: one such CTA per SM, and no room beside it for a backward CTA
+
+template <int WORLD>
+__device__ __forceinline__ float4 reduce_ranks(const ExchangeArgs& x, long long i) {
+    constexpr int W = WORLD > 0 ? WORLD : kMaxRanks;
+    float4 gr[W];
+#pragma unroll
+    for (int r = 0; r < W; r++)
+        if (r < x.world) gr[r] = x.g[r][i];  // all loads in flight before the first add
+    float4 g = gr[0];
+#pragma unroll
+    for (int r = 1; r < W; r++)
+        if (r < x.world) g.x += gr[r].x, g.y += gr[r].y, g.z += gr[r].z, g.w += gr[r].w;
+    return g;
+}
+
+__device__ __forceinline__ void adam4(const AdamSegment& s, float rate, float adj, const float4& g, float4& p, float4& m, float4& v) {
+    adam_op(s, rate, adj * g.x, p.x, m.x, v.x);
+    adam_op(s, rate, adj * g.y, p.y, m.y, v.y);
+    adam_op(s, rate, adj * g.z, p.z, m.z, v.z);
+    adam_op(s, rate, adj * g.w, p.w, m.w, v.w);
+}
+
+template <int WORLD>
+__global__ void __launch_bounds__(kOverlapThreads, 1) adamw_exchange_overlap_kernel(const __grid_constant__ OverlapArgs o) {
+    constexpr int W = WORLD > 0 ? WORLD : kMaxRanks;
+    // Elements per thread and round.  Every load of a round (the gradient from each rank, p, m, v and the
+    // running factoriser sum) is issued before the first use: U * (W + 4) = 24 independent 16-byte loads
+    // per thread hide both the NVLink and the HBM latency.
+    constexpr int U = 24 / (W + 4);
+    const ExchangeArgs& x = o.x;
+    const AdamArgs& a = x.adam;
+    const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    const long long share4 = o.block4 / x.world;
+    const AdamSegment& seg_w = a.seg[o.l0w_seg];
+    for (int b = 0; b < o.nblocks; b++) {
+        if (!peer_wait_cta(x.flags, kFlagBucket + b * kMaxRanks, o.step)) return;
+        const long long first4 = o.l0w4 + b * o.block4 + x.flags.rank * share4;
+        const bool have_f = o.facc != nullptr && b > 0;
+        for (long long j0 = tid; j0 < share4; j0 += stride * U) {
+            float4 gr[U][W], p[U], m[U], v[U], f[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const long long j = j0 + u * stride;
+                if (j < share4) {
+#pragma unroll
+                    for (int r = 0; r < W; r++)
+                        if (r < x.world) gr[u][r] = x.g[r][first4 + j];
+                    p[u] = a.p[first4 + j];
+                    m[u] = a.m[first4 + j];
+                    v[u] = a.v[first4 + j];
+                    f[u] = have_f ? o.facc[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const long long j = j0 + u * stride;
+                if (j >= share4) break;
+                const long long i = first4 + j;
+                float4 g = gr[u][0];
+#pragma unroll
+                for (int r = 1; r < W; r++)
+                    if (r < x.world) g.x += gr[u][r].x, g.y += gr[u][r].y, g.z += gr[u][r].z, g.w += gr[u][r].w;
+                if (o.facc) {  // blocks are added in order, by the same thread every time
+                    f[u].x += g.x, f[u].y += g.y, f[u].z += g.z, f[u].w += g.w;
+                    o.facc[j] = f[u];
+                }
+                adam4(seg_w, a.rate, a.adj, g, p[u], m[u], v[u]);
+                a.m[i] = m[u];
+                a.v[i] = v[u];
+#pragma unroll
+                for (int r = 0; r < W; r++)
+                    if (r < x.world) x.p_out[r][i] = p[u];
+            }
+        }
+    }
+    // everything else needs every rank's whole backward
+    if (!peer_wait_cta(x.flags, kFlagReady, o.step)) return;
+    if (o.facc) {
+        const AdamSegment& seg_f = a.seg[o.l0f_seg];
+        const long long first4 = o.l0f4 + x.flags.rank * share4;
+        for (long long j = tid; j < share4; j += stride) {
+            const long long i = first4 + j;
+            float4 p = a.p[i], m = a.m[i], v = a.v[i];
+            adam4(seg_f, a.rate, a.adj, o.facc[j], p, m, v);
+            a.m[i] = m;
+            a.v[i] = v;
+#pragma unroll
+            for (int r = 0; r < W; r++)
+                if (r < x.world) x.p_out[r][i] = p;
+        }
+    }
+    for (long long i = tid; i < o.l0w4; i += stride) {
+        int si = -1;
+#pragma unroll 1
+        for (int k = 0; k < a.nseg; k++)
+            if (i >= a.seg[k].begin4 && i < a.seg[k].end4) si = k;
+        if (si < 0 && i >= x.head4) continue;  // alignment padding between tensors
+        if (si >= 0 && si == o.l0f_seg) continue;
+        const float4 g = reduce_ranks<WORLD>(x, i);
+        if (si < 0) {
+            a.p[i] = g;  // the summed loss (and zeros) in the unused head of the parameter buffer
+            continue;
+        }
+        float4 p = a.p[i], m = a.m[i], v = a.v[i];
+        adam4(a.seg[si], a.rate, a.adj, g, p, m, v);
+        a.p[i] = p;
+        a.m[i] = m;
+        a.v[i] = v;
     }
 }
 

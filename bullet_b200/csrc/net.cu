@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -65,9 +66,9 @@ struct Slot {
     int n = 0;
     int n_dtiles = 0;  // CTA tiles of the dense kernels held in off_dtiles
     int n_chunks = 0, chunk_len = 0;  // chunks of the tiled FT backward held in off_chunks, and their size
-    int n_fitems = 0;                 // work items of the tiled forward / backward (see TileArgs::items)
-    std::vector<int> bitem_begin;     // [nblocks + 1] first backward item of every block
-    std::vector<int> fitem_begin;     // [nblocks + 1] first forward item of every block
+    std::vector<int> block_begin;     // [nblocks + 1] host copy: first pair (in visiting order) of every block
+    std::vector<int> chunk_begin;     // [nblocks + 1] host copy: first chunk of every block
+    int expect_grid = 0;              // grid size the per-block CTA counts in off_bexpect were made for
     // derived from the indices alone, so built once per upload on the copy stream (or on first use):
     uint16_t* lists = nullptr;        // prepared per-pair row lists of the tiled kernels
     int* list_count = nullptr;
@@ -76,7 +77,7 @@ struct Slot {
     bool prepared = false, csr_built = false;
     size_t off_status = 0;            // one int in the blob, zero on upload: bits raised by ft_prepare_kernel
     size_t off_stm = 0, off_nstm = 0, off_buckets = 0, off_targets = 0, off_order = 0, off_pairs = 0, off_blocks = 0,
-           off_dtiles = 0, off_chunks = 0, off_fitems = 0, off_bitems = 0, bytes = 0;
+           off_dtiles = 0, off_chunks = 0, off_cbegin = 0, off_bexpect = 0, bytes = 0;
     cudaEvent_t ready = nullptr, consumed = nullptr;
     bool has_ready = false, has_consumed = false;
     template <class T>
@@ -129,9 +130,19 @@ struct b200_net {
     long long xch_spin_limit = b200::kPeerWaitSpins;
     int xch_wait_ready = 0;    // value the next exchange launch waits for at kFlagReady (0: the caller fences)
     bool xch_fenced_used = false;
-    int* h_xstatus = nullptr;  // pinned ring beside h_status: the fence timeout word per update
+    int* h_xstatus = nullptr;  // pinned ring beside h_status: per update the fence time-out word and what was missing
     bool loss_in_param = false;  // the last update left the summed loss in P[0] instead of G[0]
     int exchange_ctas = 0;          // CTAs of a side-stream exchange launch (0: one per SM)
+    // the exchange that runs under the feature-transformer backward (b200_step_exchange)
+    cudaStream_t xch_stream = nullptr;  // highest priority: its few CTAs take their SMs before the backward's many
+    cudaEvent_t xch_fork = nullptr, xch_join = nullptr;
+    b200::PeerFlags* d_peers = nullptr;  // device copy of the peers' counter arrays, for the backward's CTAs
+    int* done_count = nullptr;           // [nblocks] backward CTAs finished per row block
+    float* facc = nullptr;               // running block sum of this rank's share of the factoriser gradient
+    int overlap_ctas = 20;               // SMs the overlapped exchange occupies
+    bool overlap_mode = false;           // batches are cut for a backward that runs beside the exchange
+    bool sig_on = false;                 // the running backward announces finished row blocks
+    int sig_value = 0;
     bool manual_grad_zero = false;  // the caller zeroes the gradient buffer range by range (b200_grad_zero_range)
     bool tiled_ok = false, table_dirty = true, have_backward = false;
     int nblocks = 1, nslabs = 1;
@@ -220,16 +231,16 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
     s.off_blocks = take((size_t)(net->nblocks + 1) * 4);
     s.off_dtiles = take(((size_t)n / b200::kDenseTile + d.n_out_buckets + 1) * 8);
     s.off_chunks = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
-    s.off_fitems = take(((size_t)2 * n / kMinItemPairs + net->nblocks + 1) * 16);
-    s.off_bitems = take(((size_t)2 * n / b200::ft_bwd_chunk(d.nnz, false) + net->nblocks + 1) * 16);
+    s.off_cbegin = take((size_t)(net->nblocks + 1) * 4);
+    s.off_bexpect = take((size_t)net->nblocks * 4);
     s.off_status = take(4);
     s.bytes = off;
 }
 
 template <bool PW>
-int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int items) {
+int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
-        b200::ft_forward_tiled_kernel<PW><<<items * t.nslabs, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows), net->stream>>>(a, t);
+        b200::ft_forward_tiled_kernel<PW><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -240,13 +251,20 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 }
 
 template <bool PW>
-int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int items) {
+int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
         const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len);
-        if (t.chunk_len == b200::ft_bwd_chunk(a.nnz, true))
-            b200::ft_backward_tiled_kernel<PW, 1024><<<items * t.nslabs, 1024, smem, net->stream>>>(a, t);
+        const bool wide = t.chunk_len == b200::ft_bwd_chunk(a.nnz, true);
+// data-parallel runs that announce finished row blocks take an instantiation of their own: the
+        // fence it ends with makes every CTA wait for its reductions to land (measured: +18 %)
+        if (wide && t.sig.done_count)
+            b200::ft_backward_tiled_kernel<PW, 1024, true><<<grid, 1024, smem, net->stream>>>(a, t);
+        else if (wide)
+            b200::ft_backward_tiled_kernel<PW, 1024, false><<<grid, 1024, smem, net->stream>>>(a, t);
+        else if (t.sig.done_count)
+            b200::ft_backward_tiled_kernel<PW, 512, true><<<grid, 512, smem, net->stream>>>(a, t);
         else
-            b200::ft_backward_tiled_kernel<PW, 512><<<items * t.nslabs, 512, smem, net->stream>>>(a, t);
+            b200::ft_backward_tiled_kernel<PW, 512, false><<<grid, 512, smem, net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -294,23 +312,17 @@ cudaError_t set_dense_forward_smem() {
                                 (int)b200::dense_fwd_smem<MM>());
 }
 
-// How many near-equal work items an average block is cut into.  One CTA is resident per SM,
-// so the grid runs in waves of net->sm_count; more items even out the last wave but repeat the
-// tile's fixed cost (`overhead`, as a fraction of a whole tile's work: the tile load in the
-// forward, the gradient flush in the backward).  `most` bounds the count from above.
-int splits_for(const b200_net* net, int most, double overhead) {
-    const int tiles = net->nblocks * net->nslabs;
-    int best = 1;
-    double best_cost = 1e30;
-    for (int sp = 1; sp <= std::max(1, std::min(512, most)); sp++) {
-        const double waves = (double)((tiles * sp + net->sm_count - 1) / net->sm_count);
-        const double cost = waves * (1.0 / sp + overhead);
-        if (cost < best_cost * 0.98) {
-            best_cost = cost;
-            best = sp;
-        }
-    }
-    return best;
+// Grid of the tiled kernels for the row blocks [first, last): one CTA per SM (two for the 512-thread
+// backward), fewer when there is too little work to give every CTA a worthwhile piece.
+int ft_forward_grid(const b200_net* net, const Slot& s, int first, int last) {
+    const long long line = (long long)net->nslabs * (s.block_begin[last] - s.block_begin[first]);
+    return (int)std::max<long long>(1, std::min<long long>(net->sm_count, line / kMinItemPairs));
+}
+int ft_backward_grid(const b200_net* net, const Slot& s, int first, int last, bool beside_exchange) {
+    const long long units = (long long)net->nslabs * (s.chunk_begin[last] - s.chunk_begin[first]);
+    const int per_sm = s.chunk_len == b200::ft_bwd_chunk(net->d.nnz, true) ? 1 : 2;
+    const int sms = net->sm_count - (beside_exchange ? std::min(net->overlap_ctas, net->sm_count - 1) : 0);
+    return (int)std::max<long long>(1, std::min<long long>((long long)sms * per_sm, units));
 }
 
 b200::FtArgs ft_args(b200_net* net, const Slot& s) {
@@ -342,19 +354,27 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, bool backward) {
     b200::TileArgs t{};
     t.block_rows = net->d.ft_block_rows;
     t.nslabs = net->nslabs;
-    t.items = s.dev<int4>(backward ? s.off_bitems : s.off_fitems);
+    t.first_block = 0;
+    t.last_block = net->nblocks;
+    t.chunk_begin = s.dev<int>(s.off_cbegin);
     t.pair_order = net->nblocks > 1 ? s.dev<int>(s.off_pairs) : nullptr;
     t.block_begin = s.dev<int>(s.off_blocks);
     t.status = s.dev<int>(s.off_status);
     t.lists = s.lists;
     t.list_count = s.list_count;
-    t.list_len = (net->d.nnz + 3) & ~3;
+    t.list_len = (net->d.nnz + 7) & ~7;
     t.chunks = s.dev<int4>(s.off_chunks);
     t.csr_ent = s.csr_ent;
     t.csr_start = s.csr_start;
     t.chunk_len = s.chunk_len;
     t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz, s.chunk_len);
     t.start_cap = b200::ft_bwd_start_cap(net->d.ft_block_rows);
+    if (backward && net->sig_on) {
+        t.sig.done_count = net->done_count;
+        t.sig.done_expect = s.dev<int>(s.off_bexpect);
+        t.sig.peers = net->d_peers;
+        t.sig.value = net->sig_value;
+    }
     return t;
 }
 
@@ -443,15 +463,18 @@ int forward_prepare(b200_net* net, Slot& s, bool want_grad) {
     return 0;
 }
 
-int forward_ft_items(b200_net* net, Slot& s, int first_item, int n_items) {
+int forward_ft_blocks(b200_net* net, Slot& s, int first_block, int last_block) {
     const bool tiled = net->fwd_tiled();
     b200::FtArgs fa = ft_args(net, s);
     b200::TileArgs ta = tile_args(net, s, false);
+    int grid = 0;
     if (tiled) {
-        if (n_items < 1) return 0;
-        ta.items += first_item;
+        if (s.block_begin[last_block] == s.block_begin[first_block]) return 0;  // no position in these blocks
+        ta.first_block = first_block;
+        ta.last_block = last_block;
+        grid = ft_forward_grid(net, s, first_block, last_block);
     }
-    return net->d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled, n_items) : launch_ft_forward<false>(net, fa, ta, tiled, n_items);
+    return net->d.pairwise ? launch_ft_forward<true>(net, fa, ta, tiled, grid) : launch_ft_forward<false>(net, fa, ta, tiled, grid);
 }
 
 int forward_dense(b200_net* net, Slot& s, bool want_grad) {
@@ -468,7 +491,7 @@ int forward_dense(b200_net* net, Slot& s, bool want_grad) {
 
 int forward_part(b200_net* net, Slot& s, bool want_grad) {
     if (int rc = forward_prepare(net, s, want_grad)) return rc;
-    if (int rc = forward_ft_items(net, s, 0, s.n_fitems)) return rc;
+    if (int rc = forward_ft_blocks(net, s, 0, net->nblocks)) return rc;
     return forward_dense(net, s, want_grad);
 }
 
@@ -537,6 +560,47 @@ int launch_dense_grads(b200_net* net, Slot& s) {
     return launch_wgrad(net, s, 0);
 }
 
+// With lazy module loading (the CUDA default) a kernel's code reaches the GPU at its first launch, and
+// that load can wait for running kernels to finish.  The data-parallel exchange has kernels that wait,
+// bounded, for other kernels launched after them, so no kernel of this library may be loaded for the
+// first time while one of those is spinning: load them all when the network is created.
+template <class K>
+bool load_kernel(K* kernel) {
+    cudaFuncAttributes attr;
+    return cudaFuncGetAttributes(&attr, reinterpret_cast<const void*>(kernel)) == cudaSuccess;
+}
+
+template <int MM>
+bool load_dense_kernels() {
+    bool ok = load_kernel(b200::dense_forward_kernel<MM>) && load_kernel(b200::dense_dx_kernel<MM>) && load_kernel(b200::dense_wgrad_kernel<MM>);
+    if constexpr (dense_tiled<MM>()) ok = ok && load_kernel(b200::dense_forward_tile_kernel<MM>);
+    return ok;
+}
+
+int preload_kernels(b200_net* net) {
+    bool ok = true;
+    DISPATCH_M(net->d.dense_out[0], ok = load_dense_kernels<MM>());
+    for (int l = 1; l < net->d.n_dense; l++) DISPATCH_M(net->d.dense_out[l], ok = ok && load_kernel(b200::dense_wgrad_kernel<MM>));
+    ok = ok && load_kernel(b200::dense_regroup_kernel) && load_kernel(b200::dense_small_grads_kernel);
+    ok = ok && load_kernel(b200::ft_forward_gather_kernel<true>) && load_kernel(b200::ft_forward_gather_kernel<false>);
+    ok = ok && load_kernel(b200::ft_backward_gather_kernel<true>) && load_kernel(b200::ft_backward_gather_kernel<false>);
+ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true>) && load_kernel(b200::ft_forward_tiled_kernel<false>);
+    ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, true>);
+    ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, true>);
+    ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, false>);
+    ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, false>);
+    ok = ok && load_kernel(b200::ft_prepare_kernel) && load_kernel(b200::ft_csr_kernel);
+    ok = ok && load_kernel(b200::factoriser_merge_kernel) && load_kernel(b200::factoriser_grad_kernel);
+    ok = ok && load_kernel(b200::adamw_flat_kernel);
+    ok = ok && load_kernel(b200::adamw_exchange_kernel<0>) && load_kernel(b200::adamw_exchange_kernel<2>);
+    ok = ok && load_kernel(b200::adamw_exchange_kernel<4>) && load_kernel(b200::adamw_exchange_kernel<8>);
+    ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<0>) && load_kernel(b200::adamw_exchange_overlap_kernel<2>);
+    ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<4>) && load_kernel(b200::adamw_exchange_overlap_kernel<8>);
+    ok = ok && load_kernel(b200::peer_signal_kernel) && load_kernel(b200::peer_wait_kernel) && load_kernel(b200::bucket_presignal_kernel);
+    if (!ok) return b200::fail(B200_ERR_CUDA, "net_create: loading the kernels failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -575,6 +639,14 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the side stream"));
     if (cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the copy stream"));
+    {
+        int least = 0, greatest = 0;
+        cudaDeviceGetStreamPriorityRange(&least, &greatest);
+        if (cudaStreamCreateWithPriority(&net->xch_stream, cudaStreamNonBlocking, greatest) != cudaSuccess ||
+            cudaEventCreateWithFlags(&net->xch_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&net->xch_join, cudaEventDisableTiming) != cudaSuccess)
+            return bail(b200::fail(B200_ERR_CUDA, "net_create: cannot create the exchange stream"));
+    }
 
     // flat layout, tensors in name order
     auto add = [&](const char* name, int64_t rows, int64_t cols) {
@@ -629,6 +701,11 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     // the fence counters get an allocation of their own size class (2 MiB), so that its IPC handle maps exactly it
     rc = rc ? rc : dev_alloc(net, &net->xch_flags, (size_t)(2 << 20) / sizeof(int));
     if (!rc) cudaMemsetAsync(net->xch_flags, 0, (size_t)2 << 20, net->stream);
+    rc = rc ? rc : dev_alloc(net, &net->d_peers, 1);
+    rc = rc ? rc : dev_alloc(net, &net->done_count, (size_t)net->nblocks);
+    if (!rc) cudaMemsetAsync(net->done_count, 0, (size_t)net->nblocks * sizeof(int), net->stream);
+    if (net->tiled_ok && d.factoriser_rows == d.ft_block_rows)
+        rc = rc ? rc : dev_alloc(net, &net->facc, (size_t)d.ft_block_rows * d.ft_out / 2);
     if (net->tiled_ok) {
         // sized for whichever backward shape needs more: every block may end in a partly filled chunk
         size_t ent_total = 0, max_chunks = 0;
@@ -639,7 +716,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
             ent_total = std::max(ent_total, chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz, cp));
         }
         for (auto& s : net->slots) {
-            rc = rc ? rc : dev_alloc(net, &s.lists, 2 * B * ((d.nnz + 3) & ~3));
+            rc = rc ? rc : dev_alloc(net, &s.lists, 2 * B * ((d.nnz + 7) & ~7));
             rc = rc ? rc : dev_alloc(net, &s.list_count, 2 * B);
             rc = rc ? rc : dev_alloc(net, &s.csr_ent, ent_total);
             rc = rc ? rc : dev_alloc(net, &s.csr_start, max_chunks * b200::ft_bwd_start_cap(d.ft_block_rows));
@@ -666,11 +743,11 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         s.n = 0;
     }
     void* raw = nullptr;
-    if (cudaHostAlloc(&raw, 64, cudaHostAllocDefault) != cudaSuccess) return bail(b200::fail(B200_ERR_CUDA, "net_create: pinned alloc failed"));
+    if (cudaHostAlloc(&raw, 128, cudaHostAllocDefault) != cudaSuccess) return bail(b200::fail(B200_ERR_CUDA, "net_create: pinned alloc failed"));
     net->h_loss = static_cast<float*>(raw);
     net->h_status = reinterpret_cast<int*>(net->h_loss + 8);
     net->h_xstatus = net->h_status + b200_net::kLossRing;
-    memset(net->h_loss, 0, 64);
+    memset(net->h_loss, 0, 128);  // 8 floats, 4 status words, 4 x 4 fence words
     for (auto& e : net->loss_ev) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
     for (auto& ring : net->tev)
         for (auto& e : ring) cudaEventCreate(&e);
@@ -690,15 +767,24 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows);
         const int wide = b200::ft_bwd_chunk(d.nnz, true), narrow = b200::ft_bwd_chunk(d.nnz, false);
         const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
+        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
         cudaFuncSetAttribute(b200::ft_csr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)b200::ft_csr_smem(d.ft_block_rows, d.nnz, wide));
     }
+    cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
+    cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
+    cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
+    cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
+    if (int rc2 = preload_kernels(net)) return bail(rc2);
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaGetLastError());
     *out = net;
@@ -711,6 +797,7 @@ int b200_net_destroy(b200_net* net) {
     if (net->stream) cudaStreamSynchronize(net->stream);
     if (net->copy_stream) cudaStreamSynchronize(net->copy_stream);
     if (net->zero_stream) cudaStreamSynchronize(net->zero_stream);
+    if (net->xch_stream) cudaStreamSynchronize(net->xch_stream);
     for (int r = 0; r < net->xch_world; r++)
         if (r != net->xch_rank) {
             if (net->peer_g[r]) cudaIpcCloseMemHandle(net->peer_g[r]);
@@ -733,6 +820,9 @@ int b200_net_destroy(b200_net* net) {
     if (net->own_stream && net->stream) cudaStreamDestroy(net->stream);
     if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
     if (net->zero_stream) cudaStreamDestroy(net->zero_stream);
+    if (net->xch_stream) cudaStreamDestroy(net->xch_stream);
+    if (net->xch_fork) cudaEventDestroy(net->xch_fork);
+    if (net->xch_join) cudaEventDestroy(net->xch_join);
     if (net->zero_fork) cudaEventDestroy(net->zero_fork);
     if (net->zero_done) cudaEventDestroy(net->zero_done);
     delete net;
@@ -758,6 +848,28 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
     }
     if (!strcmp(key, "exchange_ctas")) {
         net->exchange_ctas = (int)std::max<int64_t>(0, value);
+        return 0;
+    }
+    if (!strcmp(key, "overlap_ctas")) {  // SMs that b200_step_exchange takes away from the backward for the exchange
+        if (value < 1 || value >= net->sm_count) return b200::fail(B200_ERR_ARG, "overlap_ctas must be in [1, %d)", net->sm_count);
+        net->overlap_ctas = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "overlap_mode")) {  // takes effect for batches uploaded afterwards
+        net->overlap_mode = value != 0;
+        return 0;
+    }
+    if (!strcmp(key, "exchange_step")) {
+        // After a step that reported B200_ERR_STATE the ranks' step counters may differ.  Every rank, with nothing
+        // in flight and after a host-side barrier, sets the same value, larger than any count reached so far;
+        // the call also clears this rank's timeout word.
+        if (value < net->xch_step) return b200::fail(B200_ERR_ARG, "exchange_step must not go back (now %d)", net->xch_step);
+        if (int rc = set_device(net)) return rc;
+        CK(cudaStreamSynchronize(net->stream));
+        CK(cudaStreamSynchronize(net->xch_stream));
+        CK(cudaMemset(net->xch_flags + b200::kFlagTimeout, 0, 4 * sizeof(int)));
+        CK(cudaMemset(net->done_count, 0, (size_t)net->nblocks * sizeof(int)));
+        net->xch_step = (int)value;
         return 0;
     }
     if (!strcmp(key, "manual_grad_zero")) {
@@ -1004,44 +1116,39 @@ static int upload_finish(b200_net* net, Slot& s, int32_t n) {
         h_blocks[0] = 0;
         h_blocks[1] = 2 * n;
     }
+    s.block_begin.assign(h_blocks, h_blocks + nb + 1);
     if (net->tiled_ok) {
-        // chunks of the tiled backward: runs of at most ft_bwd_chunk pairs that stay inside one
-        // block; and the work items of both passes: every block cut into near-equal pieces whose
-        // size is set by the AVERAGE block, so a crowded block simply yields more items
+        // chunks of the tiled backward: every block cut into the fewest equal runs of at most ft_bwd_chunk pairs
         int4* h_chunks = s.host<int4>(s.off_chunks);
-        int4* h_fitems = s.host<int4>(s.off_fitems);
-        int4* h_bitems = s.host<int4>(s.off_bitems);
+        int* h_cbegin = s.host<int>(s.off_cbegin);
         const int cp = net->bwd_chunk();
         s.chunk_len = cp;
-        const int avg_pairs = std::max(1, 2 * n / nb);
-        const int f_target = std::max(kMinItemPairs, (avg_pairs + splits_for(net, avg_pairs / kMinItemPairs, 0.1) - 1) /
-                                                         splits_for(net, avg_pairs / kMinItemPairs, 0.1));
-        const int avg_chunks = std::max(1, (avg_pairs + cp - 1) / cp);
-        const int b_split = splits_for(net, avg_chunks, 0.3);
-        const int b_target = std::max(1, (avg_chunks + b_split - 1) / b_split);  // chunks per item
-        int nc = 0, nf = 0, nbi = 0;
-        s.bitem_begin.assign(nb + 1, 0);
-        s.fitem_begin.assign(nb + 1, 0);
+        int nc = 0;
         for (int b = 0; b < nb; b++) {
-            const int lo = h_blocks[b], hi = h_blocks[b + 1], cnt = hi - lo;
-            const int first_chunk = nc;
-            for (int at = lo; at < hi; at += cp) h_chunks[nc++] = make_int4(b, at, std::min(cp, hi - at), 0);
-            // forward: at least one item per block (an empty block still has nothing to write, so none is needed)
-            s.fitem_begin[b] = nf;
-            const int fpieces = cnt > 0 ? (cnt + f_target - 1) / f_target : 0;
-            for (int k = 0; k < fpieces; k++)
-                h_fitems[nf++] = make_int4(b, lo + (int)((long long)cnt * k / fpieces), lo + (int)((long long)cnt * (k + 1) / fpieces), 0);
-            s.bitem_begin[b] = nbi;
-            const int chunks_here = nc - first_chunk;
-            const int bpieces = (chunks_here + b_target - 1) / b_target;
-            for (int k = 0; k < bpieces; k++)
-                h_bitems[nbi++] = make_int4(b, first_chunk + (int)((long long)chunks_here * k / bpieces),
-                                            first_chunk + (int)((long long)chunks_here * (k + 1) / bpieces), 0);
+            h_cbegin[b] = nc;
+            const int pairs = h_blocks[b + 1] - h_blocks[b], pieces = (pairs + cp - 1) / cp;
+            const int size = pieces ? (pairs + pieces - 1) / pieces : 0;
+            for (int at = h_blocks[b]; at < h_blocks[b + 1]; at += size) h_chunks[nc++] = make_int4(b, at, std::min(size, h_blocks[b + 1] - at), 0);
         }
-        s.bitem_begin[nb] = nbi;
-        s.fitem_begin[nb] = nf;
+        h_cbegin[nb] = nc;
         s.n_chunks = nc;
-        s.n_fitems = nf;
+        s.chunk_begin.assign(h_cbegin, h_cbegin + nb + 1);
+        // How many CTAs of a whole-batch backward launch work on each block, for the data-parallel runs
+        // that announce finished blocks: the same cuts of the work line that the kernel makes.
+        int* h_expect = s.host<int>(s.off_bexpect);
+        std::fill(h_expect, h_expect + nb, 0);
+        const int grid = ft_backward_grid(net, s, 0, nb, net->overlap_mode);
+        s.expect_grid = grid;
+        const long long line = b200::ft_bwd_line(h_blocks, h_cbegin, 0, nb, net->nslabs);
+        for (int k = 0; k < grid; k++) {
+            const int u0 = b200::ft_bwd_unit_at(line * k / grid, h_blocks, h_cbegin, 0, nb, net->nslabs);
+            const int u1 = b200::ft_bwd_unit_at(line * (k + 1) / grid, h_blocks, h_cbegin, 0, nb, net->nslabs);
+            for (int blk = 0, base = 0; blk < nb && u0 < u1; blk++) {
+                const int units = net->nslabs * (h_cbegin[blk + 1] - h_cbegin[blk]);
+                if (units > 0 && u0 < base + units && u1 > base) h_expect[blk]++;
+                base += units;
+            }
+        }
     }
     *s.host<int>(s.off_status) = 0;
     CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
@@ -1104,13 +1211,8 @@ int b200_forward_ft(b200_net* net, int slot, int part, int n_parts) {
                           net->nblocks);
     if (int rc = set_device(net)) return rc;
     Slot& s = net->slots[slot];
-    int first = 0, count = s.n_fitems;
-    if (n_parts > 1) {  // the work items of this part's run of row blocks
-        const int per = net->nblocks / n_parts;
-        first = s.fitem_begin[part * per];
-        count = s.fitem_begin[(part + 1) * per] - first;
-    }
-    if (int rc = forward_ft_items(net, s, first, count)) return rc;
+    const int per = net->nblocks / n_parts;  // this part's run of row blocks
+    if (int rc = forward_ft_blocks(net, s, part * per, n_parts > 1 ? (part + 1) * per : net->nblocks)) return rc;
     net->fwd_parts_done = part + 1;
     net->fwd_parts = n_parts;
     return 0;
@@ -1173,19 +1275,23 @@ int b200_backward_ft(b200_net* net, int slot, int part, int n_parts) {
     {
         b200::FtArgs fa = ft_args(net, s);
         b200::TileArgs ta = tile_args(net, s, true);
-        int items = 0;
-        if (tiled) {  // the items of this part's run of blocks
-            const int first = s.bitem_begin[part * per], last = s.bitem_begin[(part + 1) * per];
-            ta.items += first;
-            items = last - first;
+        int grid = 0;
+        bool any = true;
+        if (tiled) {  // this part's run of blocks
+            ta.first_block = part * per;
+            ta.last_block = n_parts > 1 ? (part + 1) * per : net->nblocks;
+            any = s.chunk_begin[ta.last_block] > s.chunk_begin[ta.first_block];
+            grid = ft_backward_grid(net, s, ta.first_block, ta.last_block, net->sig_on);
+            if (net->sig_on && grid != s.expect_grid)
+                return b200::fail(B200_ERR_STATE, "backward_ft: the batch was uploaded before the exchange under the backward was switched on");
         }
-        if (!tiled || items > 0) {
-            int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled, items) : launch_ft_backward<false>(net, fa, ta, tiled, items);
+        if (any) {
+            int rc = d.pairwise ? launch_ft_backward<true>(net, fa, ta, tiled, grid) : launch_ft_backward<false>(net, fa, ta, tiled, grid);
             if (rc) return rc;
         }
     }
     if (part == n_parts - 1) CK(cudaEventRecord(ev[4], net->stream));
-    if (d.factoriser_rows) {
+    if (d.factoriser_rows && !(net->sig_on && net->facc)) {  // (the overlapped exchange sums the reduced blocks itself)
         // sum of this part's copies of the factoriser rows; with one part: all copies, in order
         const Tensor* f = net->find("l0f");
         const int copies = (int)(l0w->n / f->n), per_part = copies / n_parts;
@@ -1328,6 +1434,12 @@ int b200_exchange_import(b200_net* net, int rank, int world, const void* handles
     }
     net->xch_rank = rank;
     net->xch_world = world;
+    b200::PeerFlags f{};
+    f.world = world;
+    f.rank = rank;
+    f.spin_limit = net->xch_spin_limit;
+    for (int r = 0; r < world; r++) f.flags[r] = net->peer_flags[r];
+    CK(cudaMemcpy(net->d_peers, &f, sizeof f, cudaMemcpyHostToDevice));
     return 0;
 }
 
@@ -1414,6 +1526,98 @@ int b200_update_exchange(b200_net* net, float lr, float grad_factor) {
     return 0;
 }
 
+// One data-parallel step with the exchange under the backward pass (see adamw_exchange_overlap_kernel).
+int b200_step_exchange(b200_net* net, int slot, float lr, float grad_factor) {
+    if (!net) return b200::fail(B200_ERR_ARG, "step_exchange: null net");
+    if (!net->xch_world) return b200::fail(B200_ERR_STATE, "step_exchange: map the peers with b200_exchange_import first");
+    const b200_net_desc& d = net->d;
+    const Tensor* l0w = net->find("l0w");
+    const Tensor* l0f = d.factoriser_rows ? net->find("l0f") : nullptr;
+    const int64_t block_floats = (int64_t)d.ft_block_rows * d.ft_out;
+    if (!net->bwd_tiled() || net->nblocks > b200::kMaxSignalBlocks)
+        return b200::fail(B200_ERR_UNSUPPORTED, "step_exchange: needs the tiled backward (ft_block_rows > 0) and at most %d row blocks",
+                          b200::kMaxSignalBlocks);
+    if (block_floats % (4 * net->xch_world)) return b200::fail(B200_ERR_UNSUPPORTED, "step_exchange: a row block does not split over %d ranks", net->xch_world);
+    if (l0f && !net->facc) return b200::fail(B200_ERR_UNSUPPORTED, "step_exchange: the factoriser must have as many rows as a row block");
+    if (int rc = b200_backward_begin(net, slot)) return rc;
+    Slot& s = net->slots[slot];
+    const int step = ++net->xch_step;
+
+    b200::OverlapArgs o{};
+    b200::ExchangeArgs& x = o.x;
+    b200::AdamArgs& a = x.adam;
+    a.p = reinterpret_cast<float4*>(net->P);
+    a.m = reinterpret_cast<float4*>(net->M);
+    a.v = reinterpret_cast<float4*>(net->V);
+    a.rate = lr;
+    a.adj = grad_factor;
+    a.nseg = (int)net->tensors.size();
+    o.l0f_seg = -1;
+    for (int i = 0; i < a.nseg; i++) {
+        const Tensor& t = net->tensors[i];
+        a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
+        if (&t == l0w) o.l0w_seg = i;
+        if (&t == l0f) o.l0f_seg = i;
+    }
+    x.world = net->xch_world;
+    x.store_peers = 1;
+    x.head4 = kAlignFloats / 4;
+    x.flags.world = net->xch_world;
+    x.flags.rank = net->xch_rank;
+    x.flags.spin_limit = net->xch_spin_limit;
+    for (int r = 0; r < x.world; r++) {
+        x.g[r] = reinterpret_cast<const float4*>(net->peer_g[r]);
+        x.p_out[r] = reinterpret_cast<float4*>(net->peer_p[r]);
+        x.flags.flags[r] = net->peer_flags[r];
+    }
+    o.step = step;
+    o.nblocks = net->nblocks;
+    o.l0w4 = l0w->off / 4;
+    o.block4 = block_floats / 4;
+    o.l0f4 = l0f ? l0f->off / 4 : 0;
+    o.facc = l0f ? reinterpret_cast<float4*>(net->facc) : nullptr;
+
+    // the exchange kernel goes first, on its own stream: it is resident (or first in line for an SM) by the
+    // time the backward's CTAs arrive, and it depends on them, never they on it
+    CK(cudaEventRecord(net->xch_fork, net->stream));
+    CK(cudaStreamWaitEvent(net->xch_stream, net->xch_fork, 0));
+    const int ctas = std::min(net->overlap_ctas, net->sm_count - 1);
+    switch (x.world) {
+        case 2: b200::adamw_exchange_overlap_kernel<2><<<ctas, b200::kOverlapThreads, b200::kOverlapSmem, net->xch_stream>>>(o); break;
+        case 4: b200::adamw_exchange_overlap_kernel<4><<<ctas, b200::kOverlapThreads, b200::kOverlapSmem, net->xch_stream>>>(o); break;
+        case 8: b200::adamw_exchange_overlap_kernel<8><<<ctas, b200::kOverlapThreads, b200::kOverlapSmem, net->xch_stream>>>(o); break;
+        default: b200::adamw_exchange_overlap_kernel<0><<<ctas, b200::kOverlapThreads, b200::kOverlapSmem, net->xch_stream>>>(o); break;
+    }
+    LAUNCHED(net);
+    b200::PeerFlags f = x.flags;
+    // ... and behind it the closing fence: every rank's kernel has finished before anyone reuses gradients or weights
+    b200::peer_signal_kernel<<<1, 32, 0, net->xch_stream>>>(f, b200::kFlagDone, step);
+    LAUNCHED(net);
+    b200::peer_wait_kernel<<<1, 32, 0, net->xch_stream>>>(f, b200::kFlagDone, step);
+    LAUNCHED(net);
+    CK(cudaEventRecord(net->xch_join, net->xch_stream));
+
+    // the backward, announcing its row blocks as they finish
+    net->sig_on = true;
+    net->sig_value = step;
+    {
+        b200::TileArgs ta = tile_args(net, s, true);
+        b200::bucket_presignal_kernel<<<1, 256, 0, net->stream>>>(ta.sig, net->nblocks);
+        LAUNCHED(net);
+    }
+    int rc = b200_backward_ft(net, slot, 0, 1);
+    net->sig_on = false;
+    if (rc) return rc;
+    b200::peer_signal_kernel<<<1, 32, 0, net->stream>>>(f, b200::kFlagReady, step);  // bias and dense gradients too
+    LAUNCHED(net);
+    if (int rc2 = b200_backward_end(net, slot)) return rc2;
+    CK(cudaStreamWaitEvent(net->stream, net->xch_join, 0));
+    net->loss_in_param = true;  // every rank reduced the loss into float 0 of its parameter buffer
+    net->xch_fenced_used = true;
+    net->table_dirty = true;
+    return b200_update_end(net);
+}
+
 int b200_grad_zero_range(b200_net* net, int64_t first_float, int64_t n_floats) {
     if (!net) return b200::fail(B200_ERR_ARG, "grad_zero_range: null net");
     if (first_float < 0 || n_floats < 1 || first_float + n_floats > net->n_flat)
@@ -1435,8 +1639,11 @@ int b200_update_end(b200_net* net) {
     } else {
         net->h_status[ring] = 0;
     }
-    if (net->xch_fenced_used)
-        CK(cudaMemcpyAsync(net->h_xstatus + ring, net->xch_flags + b200::kFlagTimeout, sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+    if (net->xch_fenced_used) {
+        // report the word with this step, then clear it: a later good step starts clean
+        CK(cudaMemcpyAsync(net->h_xstatus + 4 * ring, net->xch_flags + b200::kFlagTimeout, 4 * sizeof(int), cudaMemcpyDeviceToHost, net->stream));
+        CK(cudaMemsetAsync(net->xch_flags + b200::kFlagTimeout, 0, 4 * sizeof(int), net->stream));
+    }
     CK(cudaEventRecord(net->loss_ev[ring], net->stream));
     net->updates++;
     if (int rc = refresh_table(net)) return rc;
@@ -1485,9 +1692,18 @@ int b200_loss_of(b200_net* net, int steps_back, float* loss_sum) {
     const int ring = (int)((net->updates - 1 - steps_back) % b200_net::kLossRing);
     CK(cudaEventSynchronize(net->loss_ev[ring]));
     *loss_sum = net->h_loss[ring];
-    if (net->h_xstatus[ring]) {
-        net->h_xstatus[ring] = 0;
-        return b200::fail(B200_ERR_STATE, "data-parallel exchange: a peer did not reach the fence in time; the update of this step is not valid");
+    if (net->h_xstatus[4 * ring]) {
+        const int* x = net->h_xstatus + 4 * ring;
+        const int base = x[1], value = x[2], who = x[3];
+        net->h_xstatus[4 * ring] = 0;
+        if (value == 0)
+            return b200::fail(B200_ERR_STATE, "data-parallel exchange: a peer did not reach the fence in time (reported by another rank); "
+                                              "the update of this step is not valid");
+        return b200::fail(B200_ERR_STATE,
+                          "data-parallel exchange: a peer did not reach the fence in time (rank %d never announced %s%d of step %d); the "
+                          "update of this step is not valid",
+                          who, base >= b200::kFlagBucket ? "row block " : base >= b200::kFlagDone ? "the end of its exchange, fence " : "its gradients, fence ",
+                          base >= b200::kFlagBucket ? (base - b200::kFlagBucket) / b200::kMaxRanks : base, value);
     }
     if (net->h_status[ring] & b200::kStatusOutsideBlock) {
         net->h_status[ring] = 0;

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "../../include/bullet_b200.h"
@@ -43,7 +44,7 @@ constexpr size_t kSectionAlign = 64;  // ints
 constexpr size_t align_ints(size_t v) { return (v + kSectionAlign - 1) / kSectionAlign * kSectionAlign; }
 constexpr size_t kItemsAt = align_ints(1 + (kMaxBlocks + 1) + (kMaxBlocks + 1));
 constexpr size_t kScratchHeader = kItemsAt + 4 * kMaxBlocks;
-int list_len(int nnz) { return (nnz + 3) & ~3; }
+int list_len(int nnz) { return (nnz + 7) & ~7; }  // 16-byte groups of u16 row indices
 size_t scratch_ints(int n, int nnz) { return kScratchHeader + 3 * align_ints((size_t)2 * n) + (size_t)2 * n * list_len(nnz); }
 
 // Scratch of b200_op_ft_forward_noalloc: room for B200_OP_NOALLOC_MAX_POSITIONS positions of
@@ -92,12 +93,6 @@ __global__ void group_scan_kernel(int* counts, int* begin, int nblocks) {
     }
 }
 
-// the forward's work items: one per block, all of the block's pairs
-__global__ void group_items_kernel(const int* begin, int nblocks, int4* items) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < nblocks) items[b] = make_int4(b, begin[b], begin[b + 1], 0);
-}
-
 __global__ void group_fill_kernel(const int* blk, int n, int* cursors, int* order) {
     const int pair = blockIdx.x * blockDim.x + threadIdx.x;
     if (pair >= 2 * n) return;
@@ -127,7 +122,7 @@ int check_op(const b200_ft_op* op, const char* who) {
 
 // Groups the pairs into `scratch` and runs the tiled forward; synchronises the stream and
 // reports a feature outside its block.  Allocates nothing.
-int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
+int run_op(int device, cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     const int n = op->n, R = op->ft_block_rows, nblocks = op->n_inputs / R;
     int* status = scratch;
     int* counts = scratch + 1;
@@ -142,8 +137,6 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     group_count_kernel<<<grid, threads, 0, stream>>>(op->idx_stm, op->idx_nstm, n, op->nnz, op->n_inputs, R, counts, blk);
     group_scan_kernel<<<1, 256, 0, stream>>>(counts, begin, nblocks);
     group_fill_kernel<<<grid, threads, 0, stream>>>(blk, n, counts, order);
-    int4* items = reinterpret_cast<int4*>(scratch + kItemsAt);
-    group_items_kernel<<<(nblocks + 255) / 256, 256, 0, stream>>>(begin, nblocks, items);
     CK(cudaGetLastError());
 
     b200::FtArgs a{};
@@ -161,7 +154,8 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     b200::TileArgs t{};
     t.block_rows = R;
     t.nslabs = op->ft_out / b200::kTileCols;
-    t.items = items;
+    t.first_block = 0;
+    t.last_block = nblocks;
     t.pair_order = order;
     t.block_begin = begin;
     t.status = status;
@@ -171,7 +165,10 @@ int run_op(cudaStream_t stream, const b200_ft_op* op, int* scratch) {
     b200::ft_prepare_kernel<<<(2 * n + 7) / 8, 256, 0, stream>>>(a, t);
     CK(cudaGetLastError());
     const size_t smem = b200::ft_fwd_smem(R);
-    const int ctas = nblocks * t.nslabs;
+    // one CTA per SM, each taking an equal piece of the (block, slab, pair) work line
+    int sms = 0;
+    CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int ctas = (int)std::max<long long>(1, std::min<long long>(sms, (long long)2 * n * t.nslabs / 128));
     if (op->pairwise) {
         CK(cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         b200::ft_forward_tiled_kernel<true><<<ctas, b200::kFwdThreads, smem, stream>>>(a, t);
@@ -197,7 +194,7 @@ int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op) {
     CK(cudaSetDevice(device));
     int* scratch = nullptr;
     CK(cudaMalloc(&scratch, scratch_ints(op->n, op->nnz) * sizeof(int)));
-    const int rc = run_op(static_cast<cudaStream_t>(stream), op, scratch);
+    const int rc = run_op(device, static_cast<cudaStream_t>(stream), op, scratch);
     cudaFree(scratch);
     return rc;
 }
@@ -242,7 +239,7 @@ int b200_op_ft_forward_noalloc(int device, void* stream, const b200_ft_op* op) {
         }
         scratch = address[device];
     }
-    return run_op(static_cast<cudaStream_t>(stream), op, scratch);
+    return run_op(device, static_cast<cudaStream_t>(stream), op, scratch);
 }
 
 }  // extern "C"

@@ -17,6 +17,9 @@ the buffer and an all-gather of the weights: the same bytes on the wire, 1/world
 optimiser traffic.  With `peer_exchange` those three steps are ONE kernel of the library over peer memory
 (`b200_update_exchange`: peer loads of every rank's gradients, AdamW on this rank's share, peer
 stores of the new weights to every rank), fenced by counters the ranks write into each other's memory.
+With `peer_overlap` that kernel runs UNDER the feature-transformer backward (`b200_step_exchange`): the
+backward announces finished table row blocks to all ranks and the exchange, on a few SMs of its own, takes
+them as they arrive, so only the last block and the small tensors are left when the backward ends.
 With `shard_optimiser` and `parts > 1` together the three are pipelined
 slice by slice of l0w AND across steps: the reduce-scatter of a slice travels under the
 backward of the next, and the all-gather of its updated weights is only waited for by the
@@ -58,7 +61,7 @@ class DataParallelStep:
     """
 
     def __init__(self, engine, global_batch: int, parts: int = 1, shard_optimiser: bool = False, process_group=None,
-                 peer_exchange: bool = False):
+                 peer_exchange: bool = False, peer_overlap: bool = False):
         import torch.distributed as dist
 
         self.engine = engine
@@ -72,6 +75,9 @@ class DataParallelStep:
         self.peer = peer_exchange and self.world > 1
         self.peer_error = None
         self.peer_pipelined = False
+        self.overlap = False  # the peer exchange runs under the backward pass (b200_step_exchange)
+        if peer_overlap and self.world > 1:
+            self.peer, parts, self.parts = True, 1, 1
         if self.peer:  # map every rank's gradient and parameter buffers into this process
             try:
                 mine = (engine.exchange_export(), engine.grad.numel())
@@ -99,6 +105,9 @@ class DataParallelStep:
                 self._token = engine.grad.new_zeros(1)
                 self.shard = True  # momentum and velocity live sharded, as with shard_optimiser
                 self.peer_pipelined = self.parts > 1
+                self.overlap = bool(peer_overlap)
+                if self.overlap:
+                    engine.set_option("overlap_mode", 1)  # batches are cut for a backward that shares the GPU with the exchange
                 if not self.peer_pipelined:
                     self.parts = 1
         self.pipelined = self.shard and self.parts > 1 and not self.peer
@@ -151,6 +160,22 @@ class DataParallelStep:
         eng.backward(slot)
         eng.update_exchange(lr, 1.0 / self.global_batch)
         eng.update_end()
+
+    def _overlap_step(self, slot: int, lr: float) -> bool:
+        """The peer exchange hidden under the backward pass: the library announces every finished row block
+        of the table gradient to all ranks and a kernel on a few SMs of its own reduces, updates and
+        redistributes the blocks while the backward is still at work.  False if this network cannot run it
+        (every rank holds the same network, so every rank gets the same answer)."""
+        from ._lib import B200Error
+
+        try:
+            self.engine.step_exchange(slot, lr, 1.0 / self.global_batch)
+        except B200Error as e:
+            if e.code != -5:
+                raise
+            self.overlap = False
+            return False
+        return True
 
     def _peer_pipelined_step(self, slot: int, lr: float) -> None:
         """The peer exchange slice by slice of l0w, on a side stream, beside the kernels.
@@ -271,6 +296,21 @@ class DataParallelStep:
         if not self.shard:
             return
         self.finish()
+        if getattr(self, "used_overlap", False):
+            # rank r holds share r of every row block of l0w and share r of l0f; the small tensors are complete
+            first, count = self.engine.tensor_range("l0w")
+            block = self.engine.overlap_block_floats()
+            ranges = [(first + b * block, block) for b in range(count // block)]
+            try:
+                ranges.append((self.engine.tensor_range("l0f")[0], block))
+            except Exception:  # noqa: BLE001 - no factoriser
+                pass
+            for buf in self.engine.state_buffers():
+                for lo, n in ranges:
+                    share = n // self.world
+                    mine = buf[lo + self.rank * share: lo + (self.rank + 1) * share].clone()
+                    self.dist.all_gather_into_tensor(buf[lo:lo + n], mine, group=self.group)
+            return
         if self.pipelined or self.peer_pipelined:
             for buf in self.engine.state_buffers():
                 for p in range(self.parts):
@@ -286,6 +326,9 @@ class DataParallelStep:
         eng, gf = self.engine, 1.0 / self.global_batch
         if self.peer_pipelined:
             self._peer_pipelined_step(slot, lr)
+            return
+        if self.overlap and self._overlap_step(slot, lr):
+            self.used_overlap = True
             return
         if self.peer:
             self._peer_step(slot, lr)
@@ -341,5 +384,6 @@ class NetEngine:
         self.state_buffers = lambda: [self._m, self._v]
         for name in ("backward", "update", "forward_begin", "forward_ft", "backward_begin", "backward_ft", "backward_end",
                      "grad_part", "update_range", "update_end", "tensor_range", "exchange_export", "exchange_import",
-                     "update_exchange", "update_exchange_range", "grad_zero_range", "set_option"):
+                     "update_exchange", "update_exchange_range", "grad_zero_range", "set_option", "step_exchange"):
             setattr(self, name, getattr(net, name))
+        self.overlap_block_floats = lambda: net.desc.ft_block_rows * net.desc.ft_out

@@ -127,6 +127,10 @@ class Net:
     def update_exchange(self, lr: float, grad_factor: float) -> None:
         _lib.check(self.lib.b200_update_exchange(self._h, lr, grad_factor))
 
+    def step_exchange(self, slot: int, lr: float, grad_factor: float) -> None:
+        """One data-parallel step with the exchange hidden under the backward pass."""
+        _lib.check(self.lib.b200_step_exchange(self._h, slot, lr, grad_factor))
+
     def update_exchange_range(self, lr: float, grad_factor: float, first: int, count: int, gather: bool, stream: int = 0) -> None:
         _lib.check(self.lib.b200_update_exchange_range(self._h, lr, grad_factor, first, count, int(gather),
                                                        ctypes.c_void_p(stream or 0)))

@@ -155,6 +155,18 @@ int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
 int b200_exchange_export(b200_net* net, void* handles, int64_t bytes);
 int b200_exchange_import(b200_net* net, int rank, int world, const void* handles, int64_t bytes);
 int b200_update_exchange(b200_net* net, float lr, float grad_factor);
+/* One whole data-parallel step (= b200_backward + b200_update_exchange + b200_update_end) with the exchange
+ * hidden under the feature-transformer backward.  The backward's work is ordered by table row block (king
+ * bucket) and announces every finished block to all ranks; the exchange runs at the same time on a few SMs
+ * of its own ("overlap_ctas", default 20) and takes the blocks as they arrive: peer loads of this rank's 1/world
+ * share, AdamW, peer stores of the new weights.  The factoriser gradient is formed from the reduced blocks by
+ * the share's owner; bias, dense layers and loss are reduced by every rank for itself after the backward.
+ * Needs the tiled backward, row blocks that split over world x 4 floats, and a factoriser (if any) of exactly
+ * one row block; otherwise B200_ERR_UNSUPPORTED, and the caller uses the calls above.  Momentum and velocity of
+ * l0w and l0f stay sharded (share r of every block with rank r), those of the small tensors are complete on
+ * every rank.  The gradient of l0f is not formed in the gradient buffer.  Fences and time-outs as above.
+ * b200_net_set_option("exchange_step", n) resynchronises the ranks' step counters after a failed step. */
+int b200_step_exchange(b200_net* net, int slot, float lr, float grad_factor);
 /* The same kernel on any 4-float-aligned range, on `stream` (a cudaStream_t, NULL = the net's), for a
  * host that exchanges slice by slice beside the backward and the next forward.  gather = 1: the range is
  * this rank's own share of a slice; the new weights are stored to every rank.  gather = 0: every rank

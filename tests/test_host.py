@@ -23,6 +23,20 @@ def test_rust_declarations_cover_the_header():
         assert f"pub struct {struct}" in rust
 
 
+def test_rust_trainer_source_calls_only_declared_symbols():
+    """bindings/rust/b200 (the recogniser and the train loop for bullet's own crates) is source only:
+    at least every entry point it calls must exist in the header, and it must cover the step."""
+    header = open(os.path.join(ROOT, "include", "bullet_b200.h")).read()
+    declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
+    src_dir = os.path.join(ROOT, "bindings", "rust", "b200", "src")
+    used = set()
+    for name in os.listdir(src_dir):
+        used |= set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", open(os.path.join(src_dir, name)).read()))
+    used -= {"b200_net_desc", "b200_adamw_params"}
+    assert used and used <= declared, used - declared
+    assert {"b200_net_create", "b200_batch_upload", "b200_step", "b200_loss", "b200_checkpoint_save"} <= used
+
+
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "bullet_b200.h")).read()
     declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
