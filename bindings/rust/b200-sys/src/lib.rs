@@ -145,6 +145,27 @@ extern "C" {
         blend: f32,
     ) -> c_int;
 
+    pub fn b200_batch_upload_records_gpu(
+        net: *mut b200_net,
+        slot: c_int,
+        records: *const c_void,
+        n: i32,
+        game: i32,
+        layout32: *const i32,
+        scale: f32,
+        blend: f32,
+    ) -> c_int;
+    pub fn b200_slot_read(
+        net: *mut b200_net,
+        slot: c_int,
+        stm: *mut u16,
+        nstm: *mut u16,
+        buckets: *mut i32,
+        targets: *mut f32,
+        order: *mut i32,
+        pair_order: *mut i32,
+        n: *mut i32,
+    ) -> c_int;
     pub fn b200_step(net: *mut b200_net, slot: c_int, lr: f32, grad_factor: f32) -> c_int;
     pub fn b200_backward(net: *mut b200_net, slot: c_int) -> c_int;
     pub fn b200_update(net: *mut b200_net, lr: f32, grad_factor: f32) -> c_int;

@@ -24,6 +24,7 @@ SYMBOLS = (
     "b200_forward_begin", "b200_forward_ft", "b200_net_tensor_offset",
     "b200_exchange_export", "b200_exchange_import", "b200_update_exchange", "b200_update_exchange_range",
     "b200_grad_zero_range", "b200_batch_upload_records", "b200_set_host_threads", "b200_step_exchange",
+    "b200_batch_upload_records_gpu", "b200_slot_read",
 )
 
 
@@ -85,6 +86,8 @@ def load() -> ctypes.CDLL:
         "b200_net_set_adamw": [vp, cp, ctypes.POINTER(CAdamW)],
         "b200_batch_upload": [vp, ctypes.c_int, vp, vp, vp, vp, i32],
         "b200_batch_upload_records": [vp, ctypes.c_int, vp, i32, i32, vp, f32, f32],
+        "b200_batch_upload_records_gpu": [vp, ctypes.c_int, vp, i32, i32, vp, f32, f32],
+        "b200_slot_read": [vp, ctypes.c_int, vp, vp, vp, vp, vp, vp, ctypes.POINTER(i32)],
         "b200_step": [vp, ctypes.c_int, f32, f32],
         "b200_backward": [vp, ctypes.c_int],
         "b200_update": [vp, f32, f32],

@@ -574,7 +574,12 @@ __host__ __device__ inline int ft_bwd_unit_at(long long at, const int* block_beg
 }
 
 // grid = one CTA of 1024 threads per SM (or two of 512); CTA k takes the units between the k-th and
-// the (k+1)-th of gridDim.x equal cuts of the work line.
+// the (k+1)-th of gridDim.x equal cuts of the work line.  With SIGNAL (data-parallel runs whose exchange
+// takes finished row blocks while this kernel is still running) the blocks must finish one after the
+// other, not all at the end: CTA k then takes the units k, k + gridDim.x, ... of the block-ordered
+// numbering, so that all CTAs move through the blocks together, and announces a block it has left after
+// the staging phase of its next unit, when that block's reductions have had time to land (the fence
+// that must precede the announcement then finds little to wait for).
 template <bool PAIRWISE, int THREADS, bool SIGNAL>
 __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -613,7 +618,9 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
     };
 
     int scan_block = t.first_block, scan_base = 0;  // units before scan_block
-    for (int u = u_begin; u < u_end; u++) {
+    int all_units = 0, left_block = -1;             // SIGNAL: a block this CTA has left and not yet announced
+    if (SIGNAL) all_units = t.nslabs * (t.chunk_begin[t.last_block] - t.chunk_begin[t.first_block]);
+    for (int u = SIGNAL ? (int)blockIdx.x : u_begin; u < (SIGNAL ? all_units : u_end); u += SIGNAL ? (int)gridDim.x : 1) {
         int nch = t.chunk_begin[scan_block + 1] - t.chunk_begin[scan_block];
         while (u >= scan_base + t.nslabs * nch) {
             scan_base += t.nslabs * nch;
@@ -623,8 +630,10 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         const int local = u - scan_base, new_slab = local / nch, ch = t.chunk_begin[scan_block] + local % nch;
         if (new_slab != slab || scan_block != block) {
             if (slab >= 0 && new_slab != slab) flush_bias();
-            // leaving a block: its gradient from this CTA is complete (data-parallel runs announce it)
-            if (SIGNAL && block >= 0 && scan_block != block) bucket_signal(t.sig, block);
+            if (SIGNAL && block >= 0 && scan_block != block) {
+                if (left_block >= 0) bucket_signal(t.sig, left_block);  // (only if a whole block went by within one unit)
+                left_block = block;
+            }
             slab = new_slab;
             block = scan_block;
             col_a = tile_col_a<PAIRWISE>(slab, lane, a.H);
@@ -681,6 +690,10 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         }
         cp_async_wait_all();
         __syncthreads();
+        if (SIGNAL && left_block >= 0) {
+            bucket_signal(t.sig, left_block);
+            left_block = -1;
+        }
         // accumulate: each warp walks the lists of the rows it owns, four entries per 8-byte load
         const unsigned char* gl = smem_raw + lane * 8;
         for (int row = warp; row < R; row += NW) {
@@ -706,6 +719,7 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         __syncthreads();
     }
     if (slab >= 0) flush_bias();
+    if (SIGNAL && left_block >= 0) bucket_signal(t.sig, left_block);
     if (SIGNAL && block >= 0) bucket_signal(t.sig, block);
 }
 

@@ -30,6 +30,7 @@
 #include "kernels_dense.cuh"
 #include "kernels_ft.cuh"
 #include "kernels_opt.cuh"
+#include "kernels_prep.cuh"
 #include "host_map.h"
 
 #define CK(call)                                                                                          \
@@ -69,6 +70,13 @@ struct Slot {
     std::vector<int> block_begin;     // [nblocks + 1] host copy: first pair (in visiting order) of every block
     std::vector<int> chunk_begin;     // [nblocks + 1] host copy: first chunk of every block
     int expect_grid = 0;              // grid size the per-block CTA counts in off_bexpect were made for
+    // device-side batch preparation (b200_batch_upload_records_gpu): raw records, scratch, totals read-back
+    uint4* d_records = nullptr;
+    uint16_t* d_pair_block = nullptr;
+    int* d_cta_hist = nullptr;
+    int* d_totals = nullptr;
+    int* h_totals = nullptr;          // pinned: bin totals, bin bases, then the status word
+    cudaEvent_t totals_ready = nullptr;
     // derived from the indices alone, so built once per upload on the copy stream (or on first use):
     uint16_t* lists = nullptr;        // prepared per-pair row lists of the tiled kernels
     int* list_count = nullptr;
@@ -139,6 +147,11 @@ struct b200_net {
     b200::PeerFlags* d_peers = nullptr;  // device copy of the peers' counter arrays, for the backward's CTAs
     int* done_count = nullptr;           // [nblocks] backward CTAs finished per row block
     float* facc = nullptr;               // running block sum of this rank's share of the factoriser gradient
+    float* d_win_rate = nullptr;         // device-side preparation: sigmoid(score / scale) for every 16-bit score
+    float win_rate_scale = 0.f;          // the scale the table was made for (0: none yet)
+    int* d_expanded = nullptr;           // [64] 768 * king bucket per square, and the layout it was made from
+    int32_t expanded_layout[32] = {};
+    bool expanded_valid = false;
     int overlap_ctas = 20;               // SMs the overlapped exchange occupies
     bool overlap_mode = false;           // batches are cut for a backward that runs beside the exchange
     bool sig_on = false;                 // the running backward announces finished row blocks
@@ -596,6 +609,7 @@ ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true>) && load_kernel(b200:
     ok = ok && load_kernel(b200::adamw_exchange_kernel<4>) && load_kernel(b200::adamw_exchange_kernel<8>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<0>) && load_kernel(b200::adamw_exchange_overlap_kernel<2>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<4>) && load_kernel(b200::adamw_exchange_overlap_kernel<8>);
+    ok = ok && load_kernel(b200::prep_featurise_kernel) && load_kernel(b200::prep_scan_kernel) && load_kernel(b200::prep_scatter_kernel);
     ok = ok && load_kernel(b200::peer_signal_kernel) && load_kernel(b200::peer_wait_kernel) && load_kernel(b200::bucket_presignal_kernel);
     if (!ok) return b200::fail(B200_ERR_CUDA, "net_create: loading the kernels failed: %s", cudaGetErrorString(cudaGetLastError()));
     return 0;
@@ -808,6 +822,12 @@ int b200_net_destroy(b200_net* net) {
     for (auto& s : net->slots) {
         if (s.d_blob) cudaFree(s.d_blob);
         if (s.h_blob) cudaFreeHost(s.h_blob);
+        if (s.d_records) cudaFree(s.d_records);
+        if (s.d_pair_block) cudaFree(s.d_pair_block);
+        if (s.d_cta_hist) cudaFree(s.d_cta_hist);
+        if (s.d_totals) cudaFree(s.d_totals);
+        if (s.h_totals) cudaFreeHost(s.h_totals);
+        if (s.totals_ready) cudaEventDestroy(s.totals_ready);
         if (s.ready) cudaEventDestroy(s.ready);
         if (s.consumed) cudaEventDestroy(s.consumed);
     }
@@ -1063,59 +1083,26 @@ int b200_batch_upload_records(b200_net* net, int slot, const void* records, int3
     return upload_finish(net, s, n);
 }
 
-static int upload_finish(b200_net* net, Slot& s, int32_t n) {
+// Everything the kernels need beyond the batch itself, from two histograms: how many positions take each
+// output bucket and how many (position, perspective) pairs fall into each table row block.  Fills, in the
+// slot's pinned block: the dense kernels' tiles, the blocks' first pairs, the backward's chunks, their
+// first chunk per block and the per-block CTA counts of a whole-batch backward launch.
+static void derive_tables(b200_net* net, Slot& s, const int* bucket_count, const int* block_count) {
     const b200_net_desc& d = net->d;
-    const int O = d.n_out_buckets;
-    int* h_buckets = s.host<int>(s.off_buckets);
-    const uint16_t* h_stm = s.host<uint16_t>(s.off_stm);
-    const uint16_t* h_nstm = s.host<uint16_t>(s.off_nstm);
-    // visiting order of the dense weight-gradient kernel: positions grouped by output bucket
-    int* h_order = s.host<int>(s.off_order);
-    {
-        std::vector<int> begin(O + 1, 0);
-        for (int i = 0; i < n; i++) begin[h_buckets[i] + 1]++;
-        for (int k = 0; k < O; k++) begin[k + 1] += begin[k];
-        for (int i = 0; i < n; i++) h_order[begin[h_buckets[i]]++] = i;
-        // CTA tiles of the dense kernels: runs of up to kDenseTile positions of one bucket;
-        // after the scatter begin[k] is the END of bucket k's run
+    const int O = d.n_out_buckets, nb = net->nblocks;
+    {   // CTA tiles of the dense kernels: runs of up to kDenseTile positions of one bucket
         int2* h_tiles = s.host<int2>(s.off_dtiles);
         int nt = 0, at = 0;
         for (int k = 0; k < O; k++) {
-            for (; at < begin[k]; at += b200::kDenseTile) h_tiles[nt++] = make_int2(at, std::min(b200::kDenseTile, begin[k] - at));
-            at = begin[k];
+            const int end = at + bucket_count[k];
+            for (; at < end; at += b200::kDenseTile) h_tiles[nt++] = make_int2(at, std::min(b200::kDenseTile, end - at));
+            at = end;
         }
         s.n_dtiles = nt;
     }
-    // visiting order of the tiled feature-transformer kernels: (position, perspective)
-    // pairs grouped by the table row block their features live in
-    int* h_pairs = s.host<int>(s.off_pairs);
     int* h_blocks = s.host<int>(s.off_blocks);
-    const int nb = net->nblocks;
-    if (nb > 1) {
-        const int R = d.ft_block_rows, nnz = d.nnz;
-        std::vector<int> begin(nb + 1, 0);
-        std::vector<uint16_t> blk((size_t)2 * n);
-#pragma omp parallel for schedule(static) if (n > 8192)
-        for (int i = 0; i < n; i++) {
-            for (int p = 0; p < 2; p++) {
-                const uint16_t* list = (p ? h_nstm : h_stm) + (size_t)i * nnz;
-                int b = 0;
-                for (int k = 0; k < nnz; k++)
-                    if (list[k] != 0xFFFFu) {
-                        b = list[k] / R;
-                        break;
-                    }
-                blk[(size_t)2 * i + p] = (uint16_t)b;
-            }
-        }
-        for (size_t i = 0; i < blk.size(); i++) begin[blk[i] + 1]++;
-        for (int k = 0; k < nb; k++) begin[k + 1] += begin[k];
-        memcpy(h_blocks, begin.data(), (size_t)(nb + 1) * 4);
-        for (size_t i = 0; i < blk.size(); i++) h_pairs[begin[blk[i]]++] = (int)i;
-    } else {
-        h_blocks[0] = 0;
-        h_blocks[1] = 2 * n;
-    }
+    h_blocks[0] = 0;
+    for (int b = 0; b < nb; b++) h_blocks[b + 1] = h_blocks[b] + block_count[b];
     s.block_begin.assign(h_blocks, h_blocks + nb + 1);
     if (net->tiled_ok) {
         // chunks of the tiled backward: every block cut into the fewest equal runs of at most ft_bwd_chunk pairs
@@ -1133,28 +1120,20 @@ static int upload_finish(b200_net* net, Slot& s, int32_t n) {
         h_cbegin[nb] = nc;
         s.n_chunks = nc;
         s.chunk_begin.assign(h_cbegin, h_cbegin + nb + 1);
-        // How many CTAs of a whole-batch backward launch work on each block, for the data-parallel runs
-        // that announce finished blocks: the same cuts of the work line that the kernel makes.
+        // How many CTAs of a whole-batch backward launch work on each block, for the data-parallel runs that
+        // announce finished blocks: there CTA k takes the units k, k + grid, ... of the block-ordered numbering.
         int* h_expect = s.host<int>(s.off_bexpect);
-        std::fill(h_expect, h_expect + nb, 0);
         const int grid = ft_backward_grid(net, s, 0, nb, net->overlap_mode);
         s.expect_grid = grid;
-        const long long line = b200::ft_bwd_line(h_blocks, h_cbegin, 0, nb, net->nslabs);
-        for (int k = 0; k < grid; k++) {
-            const int u0 = b200::ft_bwd_unit_at(line * k / grid, h_blocks, h_cbegin, 0, nb, net->nslabs);
-            const int u1 = b200::ft_bwd_unit_at(line * (k + 1) / grid, h_blocks, h_cbegin, 0, nb, net->nslabs);
-            for (int blk = 0, base = 0; blk < nb && u0 < u1; blk++) {
-                const int units = net->nslabs * (h_cbegin[blk + 1] - h_cbegin[blk]);
-                if (units > 0 && u0 < base + units && u1 > base) h_expect[blk]++;
-                base += units;
-            }
-        }
+        for (int blk = 0; blk < nb; blk++) h_expect[blk] = std::min(grid, net->nslabs * (h_cbegin[blk + 1] - h_cbegin[blk]));
     }
     *s.host<int>(s.off_status) = 0;
-    CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
-    net->h2d_bytes += (int64_t)s.bytes;
-    // The row lists of the tiled kernels depend on the indices only: build them right behind the
-    // copy, on the copy stream, where they run beside the step that is still computing.
+}
+
+// The row lists of the tiled kernels depend on the indices only: build them right behind the copy, on
+// the copy stream, where they run beside the step that is still computing; then mark the slot ready.
+static int upload_launch_lists(b200_net* net, Slot& s, int32_t n) {
+    const b200_net_desc& d = net->d;
     s.prepared = s.csr_built = false;
     s.n = n;
     if (net->tiled_ok && (net->fwd_tiled() || net->bwd_tiled())) {
@@ -1173,6 +1152,174 @@ static int upload_finish(b200_net* net, Slot& s, int32_t n) {
     s.has_ready = true;
     s.has_consumed = false;
     s.n = n;
+    return 0;
+}
+
+static int upload_finish(b200_net* net, Slot& s, int32_t n) {
+    const b200_net_desc& d = net->d;
+    const int O = d.n_out_buckets, nb = net->nblocks;
+    int* h_buckets = s.host<int>(s.off_buckets);
+    const uint16_t* h_stm = s.host<uint16_t>(s.off_stm);
+    const uint16_t* h_nstm = s.host<uint16_t>(s.off_nstm);
+    // visiting order of the dense weight-gradient kernel: positions grouped by output bucket (stable)
+    std::vector<int> bucket_count(O, 0), block_count(nb, 0);
+    {
+        int* h_order = s.host<int>(s.off_order);
+        std::vector<int> begin(O + 1, 0);
+        for (int i = 0; i < n; i++) begin[h_buckets[i] + 1]++;
+        for (int k = 0; k < O; k++) bucket_count[k] = begin[k + 1];
+        for (int k = 0; k < O; k++) begin[k + 1] += begin[k];
+        for (int i = 0; i < n; i++) h_order[begin[h_buckets[i]]++] = i;
+    }
+    // visiting order of the tiled feature-transformer kernels: (position, perspective)
+    // pairs grouped by the table row block their features live in (stable)
+    if (nb > 1) {
+        int* h_pairs = s.host<int>(s.off_pairs);
+        const int R = d.ft_block_rows, nnz = d.nnz;
+        std::vector<int> begin(nb + 1, 0);
+        std::vector<uint16_t> blk((size_t)2 * n);
+#pragma omp parallel for schedule(static) if (n > 8192)
+        for (int i = 0; i < n; i++) {
+            for (int p = 0; p < 2; p++) {
+                const uint16_t* list = (p ? h_nstm : h_stm) + (size_t)i * nnz;
+                int b = 0;
+                for (int k = 0; k < nnz; k++)
+                    if (list[k] != 0xFFFFu) {
+                        b = list[k] / R;
+                        break;
+                    }
+                blk[(size_t)2 * i + p] = (uint16_t)b;
+            }
+        }
+        for (size_t i = 0; i < blk.size(); i++) begin[blk[i] + 1]++;
+        for (int k = 0; k < nb; k++) block_count[k] = begin[k + 1];
+        for (int k = 0; k < nb; k++) begin[k + 1] += begin[k];
+        for (size_t i = 0; i < blk.size(); i++) h_pairs[begin[blk[i]]++] = (int)i;
+    } else {
+        block_count[0] = 2 * n;
+    }
+    derive_tables(net, s, bucket_count.data(), block_count.data());
+    CK(cudaMemcpyAsync(s.d_blob, s.h_blob, s.bytes, cudaMemcpyHostToDevice, net->copy_stream));
+    net->h2d_bytes += (int64_t)s.bytes;
+    return upload_launch_lists(net, s, n);
+}
+
+// Records in, batch prepared ON the device: 32 bytes per position cross PCIe instead of the packed lists,
+// and the host only sizes the launches from two small histograms it reads back.
+int b200_batch_upload_records_gpu(b200_net* net, int slot, const void* records, int32_t n, int32_t game, const int32_t* layout32,
+                                  float scale, float blend) {
+    if (!net || !records) return b200::fail(B200_ERR_ARG, "batch_upload_records_gpu: null argument");
+    if (game < B200_GAME_CHESS768 || game > B200_GAME_ATAXX147) return b200::fail(B200_ERR_ARG, "batch_upload_records_gpu: unknown game %d", game);
+    if (game == B200_GAME_CHESS_BUCKETS_MIRRORED && !layout32) return b200::fail(B200_ERR_ARG, "batch_upload_records_gpu: the king-bucket layout is missing");
+    if (!(blend >= 0.f && blend <= 1.f) || !(scale > 0.f)) return b200::fail(B200_ERR_ARG, "batch_upload_records_gpu: bad scale or blend");
+    const b200_net_desc& d = net->d;
+    const int O = d.n_out_buckets, nb = net->nblocks, nbins = nb + O;
+    if (O > 1 && game == B200_GAME_ATAXX147) return b200::fail(B200_ERR_UNSUPPORTED, "batch_upload_records_gpu: no output buckets for ataxx records");
+    if (nb > b200::kPrepMaxBins || O > b200::kPrepMaxBins)
+        return b200::fail(B200_ERR_UNSUPPORTED, "batch_upload_records_gpu: at most %d row blocks and output buckets; use b200_batch_upload_records",
+                          b200::kPrepMaxBins);
+    if (int rc = upload_begin(net, slot, n, "batch_upload_records_gpu")) return rc;
+    Slot& s = net->slots[slot];
+    const size_t B = d.max_batch;
+    const int max_ctas = (int)((B + b200::kPrepPositions - 1) / b200::kPrepPositions);
+    if (!s.d_records) {  // first use of this slot by the device path: its scratch, sized for the largest batch
+        CK(cudaMalloc(&s.d_records, B * 32));
+        CK(cudaMalloc(&s.d_pair_block, 2 * B * sizeof(uint16_t)));
+        CK(cudaMalloc(&s.d_cta_hist, (size_t)max_ctas * nbins * sizeof(int)));
+        CK(cudaMalloc(&s.d_totals, (size_t)2 * nbins * sizeof(int)));
+        CK(cudaHostAlloc(&s.h_totals, ((size_t)2 * nbins + 1) * sizeof(int), cudaHostAllocDefault));
+        CK(cudaEventCreateWithFlags(&s.totals_ready, cudaEventDisableTiming));
+    }
+    if (!net->d_win_rate) {
+        CK(cudaMalloc(&net->d_win_rate, 65536 * sizeof(float)));
+        CK(cudaMalloc(&net->d_expanded, 64 * sizeof(int)));
+    }
+    if (net->win_rate_scale != scale) {  // the same function the host mapper evaluates, for every possible score
+        std::vector<float> table(65536);
+        const float rscale = 1.0f / scale;
+        for (int v = -32768; v < 32768; v++) table[v + 32768] = b200::blended_target((int16_t)v, 0, rscale, 0.0f);
+        CK(cudaStreamSynchronize(net->copy_stream));
+        CK(cudaMemcpy(net->d_win_rate, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
+        net->win_rate_scale = scale;
+    }
+    if (game == B200_GAME_CHESS_BUCKETS_MIRRORED && (!net->expanded_valid || memcmp(net->expanded_layout, layout32, sizeof net->expanded_layout))) {
+        int32_t expanded[64];
+        b200::expand_king_buckets(layout32, expanded);
+        CK(cudaStreamSynchronize(net->copy_stream));
+        CK(cudaMemcpy(net->d_expanded, expanded, sizeof expanded, cudaMemcpyHostToDevice));
+        memcpy(net->expanded_layout, layout32, sizeof net->expanded_layout);
+        net->expanded_valid = true;
+    }
+    // the records go through the slot's pinned block (its list sections are not used on the host here)
+    memcpy(s.h_blob, records, (size_t)n * 32);
+    CK(cudaMemcpyAsync(s.d_records, s.h_blob, (size_t)n * 32, cudaMemcpyHostToDevice, net->copy_stream));
+    CK(cudaMemsetAsync(s.dev<int>(s.off_status), 0, sizeof(int), net->copy_stream));
+    net->h2d_bytes += (int64_t)n * 32;
+    b200::PrepArgs p{};
+    p.records = s.d_records;
+    p.n = n;
+    p.nnz = d.nnz;
+    p.n_inputs = d.n_inputs;
+    p.game = game;
+    p.n_out_buckets = O;
+    p.block_rows = net->tiled_ok ? d.ft_block_rows : d.n_inputs;
+    p.nblocks = nb;
+    p.expanded = net->d_expanded;
+    p.win_rate = net->d_win_rate;
+    p.blend = blend;
+    p.stm = s.dev<uint16_t>(s.off_stm);
+    p.nstm = s.dev<uint16_t>(s.off_nstm);
+    p.buckets = s.dev<int>(s.off_buckets);
+    p.targets = s.dev<float>(s.off_targets);
+    p.pair_block = s.d_pair_block;
+    p.cta_hist = s.d_cta_hist;
+    p.totals = s.d_totals;
+    p.order = s.dev<int>(s.off_order);
+    p.pair_order = s.dev<int>(s.off_pairs);
+    p.status = s.dev<int>(s.off_status);
+    const int ctas = (n + b200::kPrepPositions - 1) / b200::kPrepPositions;
+    b200::prep_featurise_kernel<<<ctas, b200::kPrepPositions, 0, net->copy_stream>>>(p);
+    LAUNCHED(net);
+    b200::prep_scan_kernel<<<1, 512, 0, net->copy_stream>>>(p, ctas);
+    LAUNCHED(net);
+    CK(cudaMemcpyAsync(s.h_totals, s.d_totals, (size_t)2 * nbins * sizeof(int), cudaMemcpyDeviceToHost, net->copy_stream));
+    CK(cudaMemcpyAsync(s.h_totals + 2 * nbins, s.dev<int>(s.off_status), sizeof(int), cudaMemcpyDeviceToHost, net->copy_stream));
+    CK(cudaEventRecord(s.totals_ready, net->copy_stream));
+    b200::prep_scatter_kernel<<<ctas, 2 * b200::kPrepPositions, 0, net->copy_stream>>>(p);
+    LAUNCHED(net);
+    // the host needs the bin totals to lay out chunks and tiles and to size the step's launches
+    CK(cudaEventSynchronize(s.totals_ready));
+    const int status = s.h_totals[2 * nbins];
+    if (status & b200::kStatusTooManyPieces) return b200::fail(B200_ERR_DATA, "batch_upload_records_gpu: a record holds more than nnz=%d pieces", d.nnz);
+    if (status & b200::kStatusBadBucket) return b200::fail(B200_ERR_DATA, "batch_upload_records_gpu: a record has no valid output bucket");
+    derive_tables(net, s, s.h_totals + nb, s.h_totals);
+    // only the derived tables travel: they sit behind the lists and the two orders in the slot's block
+    const size_t tail = s.off_blocks;
+    CK(cudaMemcpyAsync(s.d_blob + tail, s.h_blob + tail, s.bytes - tail, cudaMemcpyHostToDevice, net->copy_stream));
+    net->h2d_bytes += (int64_t)(s.bytes - tail);
+    return upload_launch_lists(net, s, n);
+}
+
+int b200_slot_read(b200_net* net, int slot, uint16_t* stm, uint16_t* nstm, int32_t* buckets, float* targets, int32_t* order,
+                   int32_t* pair_order, int32_t* n) {
+    if (int rc = check_slot(net, slot, "slot_read")) return rc;
+    if (int rc = set_device(net)) return rc;
+    const Slot& s = net->slots[slot];
+    CK(cudaStreamSynchronize(net->copy_stream));
+    const size_t count = (size_t)s.n, list = count * net->d.nnz * sizeof(uint16_t);
+    if (stm) CK(cudaMemcpy(stm, s.d_blob + s.off_stm, list, cudaMemcpyDeviceToHost));
+    if (nstm) CK(cudaMemcpy(nstm, s.d_blob + s.off_nstm, list, cudaMemcpyDeviceToHost));
+    if (buckets) CK(cudaMemcpy(buckets, s.d_blob + s.off_buckets, count * 4, cudaMemcpyDeviceToHost));
+    if (targets) CK(cudaMemcpy(targets, s.d_blob + s.off_targets, count * 4, cudaMemcpyDeviceToHost));
+    if (order) CK(cudaMemcpy(order, s.d_blob + s.off_order, count * 4, cudaMemcpyDeviceToHost));
+    if (pair_order) {
+        if (net->nblocks > 1) {
+            CK(cudaMemcpy(pair_order, s.d_blob + s.off_pairs, count * 8, cudaMemcpyDeviceToHost));
+        } else {  // a single row block is visited in pair order and keeps no list
+            for (size_t i = 0; i < 2 * count; i++) pair_order[i] = (int32_t)i;
+        }
+    }
+    if (n) *n = s.n;
     return 0;
 }
 

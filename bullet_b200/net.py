@@ -84,13 +84,26 @@ class Net:
                                               _p(targets), n))
 
     # -------------------------------------------------------------------- step
-    def upload_records(self, slot: int, game: str, records: np.ndarray, scale: float = 400.0, blend: float = 0.5) -> None:
-        """Raw 32-byte records -> featurised, packed batch in the slot (one pass on all host cores)."""
+    def upload_records(self, slot: int, game: str, records: np.ndarray, scale: float = 400.0, blend: float = 0.5,
+                       on_device: bool = False) -> None:
+        """Raw 32-byte records -> featurised, packed batch in the slot: one pass on all host cores, or
+        (`on_device`) 32 bytes per position copied and everything else done by kernels on the copy stream."""
         records = np.ascontiguousarray(records)
         code = {"chess768": 0, "chess_buckets": 1, "ataxx147": 2}[game]
         layout = np.asarray(KING_BUCKETS_16, dtype=np.int32) if code == 1 else None
-        _lib.check(self.lib.b200_batch_upload_records(self._h, slot, _p(records), len(records), code,
-                                                      _p(layout) if layout is not None else None, scale, blend))
+        fn = self.lib.b200_batch_upload_records_gpu if on_device else self.lib.b200_batch_upload_records
+        _lib.check(fn(self._h, slot, _p(records), len(records), code, _p(layout) if layout is not None else None, scale, blend))
+
+    def slot_contents(self, slot: int) -> dict:
+        """Debug/inspection: what the slot holds on the device (packed lists, buckets, targets, the two orders)."""
+        count = ctypes.c_int32()
+        _lib.check(self.lib.b200_slot_read(self._h, slot, None, None, None, None, None, None, ctypes.byref(count)))
+        n, nnz = count.value, self.desc.nnz
+        out = {"stm": np.empty((n, nnz), np.uint16), "nstm": np.empty((n, nnz), np.uint16), "buckets": np.empty(n, np.int32),
+               "targets": np.empty(n, np.float32), "order": np.empty(n, np.int32), "pair_order": np.empty(2 * n, np.int32)}
+        _lib.check(self.lib.b200_slot_read(self._h, slot, _p(out["stm"]), _p(out["nstm"]), _p(out["buckets"]), _p(out["targets"]),
+                                           _p(out["order"]), _p(out["pair_order"]), None))
+        return out
 
     def step(self, slot: int, lr: float, grad_factor: float) -> None:
         _lib.check(self.lib.b200_step(self._h, slot, lr, grad_factor))

@@ -126,6 +126,24 @@ int b200_batch_upload(b200_net* net, int slot, const int32_t* stm, const int32_t
 int b200_batch_upload_records(b200_net* net, int slot, const void* records, int32_t n, int32_t game, const int32_t* layout32,
                               float scale, float blend);
 
+/* The same with the preparation on the DEVICE: the raw records (32 bytes per position) are copied and a kernel runs
+ * the featuriser, the output bucket and the target blend; two more group the positions by output bucket and the
+ * (position, perspective) pairs by table row block, in the same stable order the host path produces.  The slot
+ * ends up bit-identical to b200_batch_upload_records' (lists, buckets, targets, both orders), so training results
+ * are identical too.  The call waits once for two small histograms (it needs them to size the step's launches);
+ * everything runs on the library's copy stream, beside a step that is still computing.  What it replaces in the
+ * reference: the per-position mapper closure of ValueTrainerState::make_mapper (crates/bullet_lib/src/value.rs:77-117)
+ * run by the loader threads (crates/trainer/src/model/inputs.rs:86-109) plus the copy of its five arrays.
+ * At most 256 row blocks and 256 output buckets. */
+int b200_batch_upload_records_gpu(b200_net* net, int slot, const void* records, int32_t n, int32_t game, const int32_t* layout32,
+                                  float scale, float blend);
+
+/* Debug/inspection: copies what a slot holds on the device to the host (any pointer may be NULL): the packed index
+ * lists [n][nnz], buckets [n], targets [n], the positions grouped by output bucket [n] and the (position,
+ * perspective) pairs (id = 2 * position + perspective) grouped by row block [2n]; *n = positions in the slot. */
+int b200_slot_read(b200_net* net, int slot, uint16_t* stm, uint16_t* nstm, int32_t* buckets, float* targets, int32_t* order,
+                   int32_t* pair_order, int32_t* n);
+
 /* ---- the step.  b200_step = Function::execute on the backward graph followed by
  * Optimiser::update (crates/trainer/src/run.rs:185-192).  The split form lets a
  * data-parallel host all-reduce the flat gradient buffer between the halves:

@@ -170,9 +170,9 @@ def hundred_steps(oracle32, oracle64, tag, desc, game, B, steps, seed, lr, w, mo
     hp = AdamWParams()
     w32, _, _, losses32 = oracle32.train(desc, w, seq, lr, hp)
     w64, _, _, losses64 = oracle64.train(desc, w, seq, lr, hp)
-    # the run must move the weights by far more than the bound it is held to (per-batch losses are too
-    # noisy to compare the first with the last)
-    assert rel2(w64["l0w"], np.asarray(w["l0w"], dtype=np.float64)) > 1e-2
+    # the run must move weights by far more than the bound it is held to (per-batch losses are too noisy to
+    # compare the first with the last; the pairwise net's table moves slowly at first, its dense layers do not)
+    assert max(rel2(w64[k], np.asarray(w[k], dtype=np.float64)) for k in w64 if k.endswith("w")) > 1e-2
     rows, failures = [], []
     for mode in modes:
         net = make_net(desc, mode, w)
@@ -630,3 +630,38 @@ def test_upload_from_records_equals_featurise_then_upload(ci):
             small.close()
     a.close()
     b.close()
+
+
+@pytest.mark.parametrize("ci", [0, 1, 2, 3])
+def test_device_preparation_fills_the_slot_exactly_as_the_host_path(ci):
+    """b200_batch_upload_records_gpu (featuriser, bucket, target and both stable groupings as kernels) leaves the
+    slot bit-identical to b200_batch_upload_records: packed lists, buckets, targets, positions by output bucket,
+    pairs by row block.  Forward outputs are then bit-identical and a training step agrees to rounding."""
+    from bullet_b200._lib import B200Error
+
+    c = config(ci)
+    w = synth.init_weights(c.desc, seed=ci)
+    for n in (5000, 257, 1):   # several CTAs of the preparation kernels, a ragged last one, a single position
+        desc = dataclasses.replace(c.desc, max_batch=5000)
+        rec = synth.records(c.game, n, seed=161 + ci)
+        a, b = make_net(desc, 0, w), make_net(desc, 0, w)
+        a.upload_records(1, c.game, rec)
+        b.upload_records(1, c.game, rec, on_device=True)
+        sa, sb = a.slot_contents(1), b.slot_contents(1)
+        for k in sa:
+            assert np.array_equal(sa[k], sb[k]), (n, k)
+        assert np.array_equal(a.forward(1, n), b.forward(1, n))
+        a.step(1, 1e-3, 1.0 / n)
+        b.step(1, 1e-3, 1.0 / n)
+        assert abs(a.loss() - b.loss()) <= 1e-6 * abs(a.loss())
+        wa, wb = a.tensors(0), b.tensors(0)
+        for k in wa:
+            assert rel2(wb[k], wa[k]) <= 1e-6, (n, k)
+        a.close()
+        b.close()
+    if ci == 0:   # a record with more pieces than slots is refused, as on the host path
+        small = make_net(dataclasses.replace(c.desc, nnz=8, max_batch=64), 0, w)
+        with pytest.raises(B200Error) as e:
+            small.upload_records(0, c.game, synth.records(c.game, 64, seed=5), on_device=True)
+        assert e.value.code == -4
+        small.close()
