@@ -38,7 +38,19 @@ from bullet_b200.configs import AdamWParams  # noqa: E402
 METRIC = "train positions/sec (fwd+bwd+AdamW)"
 UNIT = "positions/s"
 GLOBAL_BATCH = 131072  # --global-batch overrides it for profiling runs on a smaller case
-WORKLOAD = "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), global batch {}"
+CONFIG = 4             # --config: which of the five benchmark configurations (4 = the headline, the default)
+WORKLOADS = {
+    0: "c0: 768->128 screlu, concat->1 (examples/simple.rs shape), batch {}",
+    1: "c1: 768x16(+768 factoriser)->1024 screlu, concat->8 buckets x 1, batch {}",
+    2: "c2: ataxx 147->256 crelu, concat->1, nnz 49, batch {}",
+    3: "c3: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), batch {}",
+    4: "c4: 768x16(+768 factoriser)->2048 crelu pairwise->8 buckets x (16->32->1), global batch {}",
+}
+
+
+def workload():
+    return WORKLOADS[CONFIG].format(GLOBAL_BATCH)
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two tiled feature-transformer kernels,
 # as a two-term model fitted to an ncu capture at 16384 positions per GPU: what is read or written once
 # per launch whatever the batch (the 100.7 MB table in the forward; 63 MB of gradient write-back in the
@@ -118,13 +130,15 @@ class ClockSampler:
 
 
 def make_host_batches(cfg, n_local, rank, count):
+    """`count` distinct batches of this rank: the raw 32-byte records and the arrays the host mapper makes of them."""
     from bullet_b200.net import featurise
 
-    out = []
+    records, arrays = [], []
     for i in range(count):
         rec = synth.records(cfg.game, n_local, seed=cfg.seed + 1000 * rank + i)
-        out.append(featurise(cfg.game, rec, cfg.desc))
-    return out
+        records.append(rec)
+        arrays.append(featurise(cfg.game, rec, cfg.desc))
+    return records, arrays
 
 
 def cpu_reference(cfg, sample, repeats, warmup):
@@ -184,7 +198,7 @@ def cpu_reference(cfg, sample, repeats, warmup):
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    cfg = config(4)
+    cfg = config(CONFIG)
     cpu = cpu_reference(cfg, args.cpu_sample, min(max(1, args.steps), CPU_REPEATS), min(max(1, args.warmup), 2))
     line = {
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": args.gpus,
@@ -193,7 +207,7 @@ def run_reference(args, rank, world):
         # (all positions) is cpu_baseline.modelled_step_ms
         "ms_per_step": cpu["measured_pass_ms"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "where": "host CPU cores, no GPU"},
+        "config": {"workload": workload(), "global_batch": GLOBAL_BATCH, "where": "host CPU cores, no GPU"},
         "cpu_baseline": cpu,
         "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -237,13 +251,13 @@ def run_ours(args, rank, world, local_rank):
         opts = dist.ProcessGroupNCCL.Options()
         opts.is_high_priority_stream = True  # collectives that run beside kernels get their SMs first
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
-    cfg = config(4)
+    cfg = config(CONFIG)
     if GLOBAL_BATCH % world:
         raise SystemExit("the global batch must divide evenly over the ranks")
     n_local = GLOBAL_BATCH // world
     desc = dataclasses.replace(cfg.desc, max_batch=n_local)
     cfg = dataclasses.replace(cfg, desc=desc)
-    batches = make_host_batches(cfg, n_local, rank, N_DISTINCT)
+    records, batches = make_host_batches(cfg, n_local, rank, N_DISTINCT)
 
     stream = torch.cuda.Stream()
     net = Net(desc, device=local_rank, stream=stream.cuda_stream)
@@ -313,10 +327,18 @@ def run_ours(args, rank, world, local_rank):
         loss_resident = net.loss() if world == 1 else None
 
         # ------------------------------------------------ end to end through the public API
-        net.upload(0, *batches[0])
+        # from the raw position records a data file holds: featurising, packing and grouping are inside the
+        # timed region (on the device by default: 32 bytes per position cross PCIe)
+        if args.e2e_source == "arrays":
+            def upload(slot, k):
+                net.upload(slot, *batches[k])
+        else:
+            def upload(slot, k):
+                net.upload_records(slot, cfg.game, records[k], on_device=args.e2e_source == "records")
+        upload(0, 0)
         for i in range(max(args.warmup, 1)):
             one_step(i % N_DISTINCT)
-            net.upload((i + 1) % N_DISTINCT, *batches[(i + 1) % N_DISTINCT])
+            upload((i + 1) % N_DISTINCT, (i + 1) % N_DISTINCT)
             net.loss()
         h2d0 = net.stat("h2d_bytes")
         first = max(args.warmup, 1) % N_DISTINCT
@@ -327,7 +349,7 @@ def run_ours(args, rank, world, local_rank):
             slot = (first + i) % N_DISTINCT
             nxt = (slot + 1) % N_DISTINCT
             one_step(slot)                                              # enqueue only
-            net.upload(nxt, *batches[nxt])                               # pack + H2D of the next batch
+            upload(nxt, nxt)                                             # H2D + preparation of the next batch
             if i:
                 last_loss = net.loss(steps_back=1)                       # D2H read of the previous step's loss
         last_loss = net.loss()                                           # ... and of the last step's
@@ -363,7 +385,8 @@ def run_ours(args, rank, world, local_rank):
         k["achieved_gbs"] = k["algorithmic_bytes"] / (k["ms"] * 1e-3) / 1e9 if k["ms"] > 0 else None
         k["frac_of_hbm_peak"] = k["achieved_gbs"] / peak if k["achieved_gbs"] else None
     dom = max(kernels, key=lambda n: kernels[n]["ms"])
-    traffic = FT_DRAM_MODEL[dom][0] + FT_DRAM_MODEL[dom][1] * n_local if dom in FT_DRAM_MODEL else None
+    # the DRAM model was fitted on the 2048-wide pairwise network only
+    traffic = FT_DRAM_MODEL[dom][0] + FT_DRAM_MODEL[dom][1] * n_local if dom in FT_DRAM_MODEL and CONFIG >= 3 else None
     # What bounds the tiled kernels: every active feature's 256-byte row piece passes the SM's
     # shared-memory data pipe (128 bytes per clock per SM) once per 64-column slab, while HBM sees the
     # table once per launch.  The HBM figure is kept beside it: it exceeds 1 because rows are served on chip.
@@ -382,7 +405,21 @@ def run_ours(args, rank, world, local_rank):
                     "peak_kind": f"{sm_count} SMs x 128 B/clk x {sm_mhz:.0f} MHz (median SM clock during the run)",
                     "hbm": hbm_view}
     else:
-        roofline = dict(hbm_view, bound="hbm", kernel=dom, traffic=traffic)
+        # the gather kernels read table rows (forward) or add to gradient rows (backward) straight in L2 when the
+        # table and its gradient fit there, else in HBM; the L2 rates are measured now, on a 32 MB buffer
+        table_bytes = desc.n_inputs * desc.ft_out * 4
+        if 2 * table_bytes <= 96 << 20:
+            from bullet_b200.net import probe_bandwidth
+
+            kind = "read" if dom == "ft_forward" else "atomic"
+            l2_gbs = probe_bandwidth(kind, 32 << 20, 40, local_rank)
+            roofline = {"bound": "l2", "kernel": dom, "achieved": achieved, "peak": l2_gbs, "unit": "GB/s",
+                        "frac": achieved / l2_gbs if achieved else None, "traffic": traffic,
+                        "peak_kind": ("measured now: 16-byte loads of an L2-resident 32 MB buffer" if kind == "read" else
+                                      "measured now: 16-byte vector reductions into an L2-resident 32 MB buffer"),
+                        "hbm": hbm_view}
+        else:
+            roofline = dict(hbm_view, bound="hbm", kernel=dom, traffic=traffic)
     roofline.update({"algorithmic_bytes_per_launch": kernels[dom]["algorithmic_bytes"], "launch_ms": kernels[dom]["ms"],
                      "note": "algorithmic bytes count every gathered/updated table row once per active feature; "
                              "traffic is the DRAM side (ncu capture at 16384 positions, scaled by a two-term model)"})
@@ -397,7 +434,7 @@ def run_ours(args, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD.format(GLOBAL_BATCH), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
+        "config": {"workload": workload(), "global_batch": GLOBAL_BATCH, "per_gpu_batch": n_local,
                    "parallelism": f"dp{world}",
                    "exchange": ("one kernel over peer memory, run under the feature-transformer backward on SMs of its own: "
                                 "finished row blocks are announced to all ranks; peer loads of all gradients, AdamW on 1/N, "
@@ -413,7 +450,12 @@ def run_ours(args, rank, world, local_rank):
                          f"{n_local * (desc.dense_in0 * 2 + 2 * desc.ft_out) * 4 / 1e6:.0f} MB",
                    "active_features_per_position": rows / n_local},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d_per_step) * world,
-                "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_s * 1e3 / args.steps,
+                "d2h_bytes_per_step": (8 + (4 * (2 * (desc.n_inputs // desc.ft_block_rows + desc.n_out_buckets) + 1)
+                                            if args.e2e_source == "records" else 0)) * world,
+                "ms_per_step": e2e_s * 1e3 / args.steps,
+                "source": {"records": "raw 32-byte records; featuriser, packing and grouping as kernels on the copy stream",
+                           "records-host": "raw 32-byte records; featuriser and packing on the host cores",
+                           "arrays": "index arrays made by the host mapper before the clock starts"}[args.e2e_source],
                 "loss_per_position": None if last_loss is None else last_loss / GLOBAL_BATCH},
         "gpu_launches": int(launches),
         "compute_only_ms_per_step": local_ms,
@@ -447,13 +489,19 @@ def main():
                     help="N > 1 with --dp-peer 1: 1 = the exchange kernel runs under the backward pass (b200_step_exchange)")
     ap.add_argument("--dp-parts", type=int, default=1,
                     help="N > 1: slices of l0w exchanged while the backward (and, with --dp-shard 1, the next forward) still runs")
+    ap.add_argument("--e2e-source", default="records", choices=["records", "records-host", "arrays"],
+                    help="what the end-to-end loop uploads every step: raw records prepared on the device (default), raw "
+                         "records prepared on the host, or ready-made index arrays")
     ap.add_argument("--cpu-sample", type=int, default=16384,
                     help="positions of the larger of the two timed CPU-oracle passes (the other takes half)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
-                    help="positions per step over all ranks (default: the benchmark's 131072)")
+    ap.add_argument("--config", type=int, default=4, choices=[0, 1, 2, 3, 4],
+                    help="benchmark configuration: 4 (default) is the headline; 0-3 give the roofline lines of the other networks")
+    ap.add_argument("--global-batch", type=int, default=None,
+                    help="positions per step over all ranks (default: the configuration's own, 131072 for the headline)")
     args = ap.parse_args()
-    globals()["GLOBAL_BATCH"] = args.global_batch
+    globals()["CONFIG"] = args.config
+    globals()["GLOBAL_BATCH"] = args.global_batch or config(args.config).batch
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

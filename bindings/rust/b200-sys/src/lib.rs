@@ -55,6 +55,25 @@ pub struct b200_net_desc {
     pub max_batch: i32,
 }
 
+pub const B200_OPT_ADAMW: i32 = 0;
+pub const B200_OPT_RADAM: i32 = 1;
+pub const B200_OPT_RANGER: i32 = 2;
+pub const B200_KIND_SLOW: c_int = 4;
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct b200_optimiser_params {
+    pub kind: i32,
+    pub decay: f32,
+    pub beta1: f32,
+    pub beta2: f32,
+    pub min_weight: f32,
+    pub max_weight: f32,
+    pub n_sma_threshold: f32,
+    pub alpha: f32,
+    pub k: i32,
+}
+
 #[repr(C)]
 #[derive(Clone, Copy, Debug)]
 pub struct b200_adamw_params {
@@ -166,6 +185,8 @@ extern "C" {
         pair_order: *mut i32,
         n: *mut i32,
     ) -> c_int;
+    pub fn b200_net_set_optimiser(net: *mut b200_net, name: *const c_char, params: *const b200_optimiser_params) -> c_int;
+    pub fn b200_probe_bandwidth(device: c_int, kind: c_int, bytes: i64, reps: c_int, gb_per_s: *mut f64) -> c_int;
     pub fn b200_step(net: *mut b200_net, slot: c_int, lr: f32, grad_factor: f32) -> c_int;
     pub fn b200_backward(net: *mut b200_net, slot: c_int) -> c_int;
     pub fn b200_update(net: *mut b200_net, lr: f32, grad_factor: f32) -> c_int;

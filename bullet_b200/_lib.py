@@ -24,12 +24,19 @@ SYMBOLS = (
     "b200_forward_begin", "b200_forward_ft", "b200_net_tensor_offset",
     "b200_exchange_export", "b200_exchange_import", "b200_update_exchange", "b200_update_exchange_range",
     "b200_grad_zero_range", "b200_batch_upload_records", "b200_set_host_threads", "b200_step_exchange",
-    "b200_batch_upload_records_gpu", "b200_slot_read",
+    "b200_batch_upload_records_gpu", "b200_slot_read", "b200_probe_bandwidth", "b200_net_set_optimiser",
 )
 
 
 class CAdamW(ctypes.Structure):
     _fields_ = [(n, ctypes.c_float) for n in ("decay", "beta1", "beta2", "min_weight", "max_weight")]
+
+
+class COptimiser(ctypes.Structure):
+    """b200_optimiser_params: kind 0 AdamW, 1 RAdam, 2 Ranger."""
+
+    _fields_ = [("kind", ctypes.c_int32)] + [(n, ctypes.c_float) for n in ("decay", "beta1", "beta2", "min_weight", "max_weight",
+                                                                         "n_sma_threshold", "alpha")] + [("k", ctypes.c_int32)]
 
 
 class CFtOp(ctypes.Structure):
@@ -84,6 +91,7 @@ def load() -> ctypes.CDLL:
         "b200_net_set_tensor": [vp, cp, ctypes.c_int, vp, i64],
         "b200_net_get_tensor": [vp, cp, ctypes.c_int, vp, i64],
         "b200_net_set_adamw": [vp, cp, ctypes.POINTER(CAdamW)],
+        "b200_net_set_optimiser": [vp, cp, ctypes.POINTER(COptimiser)],
         "b200_batch_upload": [vp, ctypes.c_int, vp, vp, vp, vp, i32],
         "b200_batch_upload_records": [vp, ctypes.c_int, vp, i32, i32, vp, f32, f32],
         "b200_batch_upload_records_gpu": [vp, ctypes.c_int, vp, i32, i32, vp, f32, f32],
@@ -132,6 +140,7 @@ def load() -> ctypes.CDLL:
         "b200_material_count": [vp, i32, i32, vp],
         "b200_make_targets": [vp, i32, f32, f32, vp],
         "b200_set_host_threads": [i32],
+        "b200_probe_bandwidth": [ctypes.c_int, ctypes.c_int, i64, ctypes.c_int, ctypes.POINTER(ctypes.c_double)],
         "b200_pack_indices_u16": [vp, i64, vp],
         "b200_unpack_indices_u16": [vp, i64, vp],
     }

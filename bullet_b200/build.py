@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbullet_b200.so")
-SOURCES = ["net.cu", "op_ft_forward.cu", "host_pack.cpp", "checkpoint.cpp", "saved_format.cpp"]
+SOURCES = ["net.cu", "op_ft_forward.cu", "probe.cu", "host_pack.cpp", "checkpoint.cpp", "saved_format.cpp"]
 
 
 def _nvcc() -> str:

@@ -31,6 +31,30 @@ class AdamWParams:
 
 
 @dataclass
+class RAdamParams:
+    """crates/trainer/src/optimiser/radam.rs:19-32 (same defaults; clip None = no clipping)."""
+
+    beta1: float = 0.9
+    beta2: float = 0.999
+    n_sma_threshold: float = 5.0
+    decay: float = 0.0
+    clip: tuple | None = None
+
+
+@dataclass
+class RangerParams:
+    """crates/trainer/src/optimiser/ranger.rs:137-151 (same defaults)."""
+
+    decay: float = 0.01
+    beta1: float = 0.99
+    beta2: float = 0.999
+    min_weight: float = -1.98
+    max_weight: float = 1.98
+    alpha: float = 0.5
+    k: int = 6
+
+
+@dataclass
 class NetDesc:
     n_inputs: int                 # sparse inputs per perspective
     nnz: int                      # index slots per position (max active features)

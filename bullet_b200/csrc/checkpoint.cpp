@@ -19,7 +19,14 @@
 
 namespace {
 
-const char* const kFiles[3] = {"weights.bin", "momentum.bin", "velocity.bin"};  // kinds 0, 1, 2
+// kinds 0, 1, 2, and Ranger's slow weights (ranger.rs:115-134 writes them as slow.bin beside the inner optimiser's files)
+const char* const kFiles[4] = {"weights.bin", "momentum.bin", "velocity.bin", "slow.bin"};
+const int kKinds[4] = {B200_KIND_WEIGHT, B200_KIND_MOMENTUM, B200_KIND_VELOCITY, B200_KIND_SLOW};
+int file_count(b200_net* net) {
+    int64_t slow = 0;
+    b200_net_get_stat(net, "slow_weights", &slow);
+    return slow ? 4 : 3;
+}
 const char* const kIds[] = {"l0b", "l0f", "l0w", "l1b", "l1w", "l2b", "l2w", "l3b", "l3w"};  // name order
 
 }  // namespace
@@ -29,7 +36,8 @@ extern "C" {
 int b200_checkpoint_save(b200_net* net, const char* dir) {
     if (!net || !dir) return b200::fail(B200_ERR_ARG, "checkpoint_save: null argument");
     std::vector<float> values;
-    for (int kind = 0; kind < 3; kind++) {
+    const int files = file_count(net);
+    for (int kind = 0; kind < files; kind++) {
         const std::string path = std::string(dir) + "/" + kFiles[kind];
         FILE* f = std::fopen(path.c_str(), "wb");
         if (!f) return b200::fail(B200_ERR_ARG, "checkpoint_save: cannot create %s", path.c_str());
@@ -37,7 +45,7 @@ int b200_checkpoint_save(b200_net* net, const char* dir) {
             int64_t n = 0;
             if (b200_net_tensor_size(net, id, &n) != 0) continue;  // this network has no such tensor
             values.resize((size_t)n);
-            if (int rc = b200_net_get_tensor(net, id, kind, values.data(), n)) {
+            if (int rc = b200_net_get_tensor(net, id, kKinds[kind], values.data(), n)) {
                 std::fclose(f);
                 return rc;
             }
@@ -64,9 +72,10 @@ int b200_checkpoint_load(b200_net* net, const char* dir) {
         size_t at;       // offset of the values inside the file's bytes
         int64_t count;
     };
-    std::vector<unsigned char> bytes[3];
-    std::vector<Record> records[3];
-    for (int kind = 0; kind < 3; kind++) {
+    std::vector<unsigned char> bytes[4];
+    std::vector<Record> records[4];
+    const int files = file_count(net);
+    for (int kind = 0; kind < files; kind++) {
         const std::string path = std::string(dir) + "/" + kFiles[kind];
         FILE* f = std::fopen(path.c_str(), "rb");
         if (!f) return b200::fail(B200_ERR_ARG, "checkpoint_load: cannot open %s", path.c_str());
@@ -108,11 +117,11 @@ int b200_checkpoint_load(b200_net* net, const char* dir) {
             return b200::fail(B200_ERR_DATA, "checkpoint_load: %s holds %d tensors, the network has %d", path.c_str(), (int)records[kind].size(), expected);
     }
     std::vector<float> values;
-    for (int kind = 0; kind < 3; kind++)
+    for (int kind = 0; kind < files; kind++)
         for (const Record& r : records[kind]) {
             values.resize((size_t)r.count);
             std::memcpy(values.data(), bytes[kind].data() + r.at, (size_t)r.count * 4);
-            if (int rc = b200_net_set_tensor(net, r.id.c_str(), kind, values.data(), r.count)) return rc;
+            if (int rc = b200_net_set_tensor(net, r.id.c_str(), kKinds[kind], values.data(), r.count)) return rc;
         }
     return 0;
 }

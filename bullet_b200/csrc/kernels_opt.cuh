@@ -24,6 +24,10 @@ constexpr int kMaxSegments = 12;
 struct AdamSegment {
     long long begin4, end4;  // range in float4 units within the flat buffer
     float decay, beta1, beta2, wmin, wmax;
+    // RAdam (crates/trainer/src/optimiser/radam.rs:35-52,295-314): the host computes, per step, a factor on
+    // the learning rate and whether the second moment divides the update yet.  AdamW: 1 and yes.
+    float rate_scale = 1.0f;
+    int use_denom = 1;
 };
 
 struct AdamArgs {
@@ -37,13 +41,42 @@ struct AdamArgs {
     AdamSegment seg[kMaxSegments];
 };
 
-__device__ __forceinline__ void adam_op(const AdamSegment& s, float rate, float g, float& p, float& m, float& v) {
+__device__ __forceinline__ void adam_op(const AdamSegment& s, float base_rate, float g, float& p, float& m, float& v) {
+    const float rate = base_rate * s.rate_scale;  // radam.rs: rate_ptr[0] * step_size_ptr[0]; AdamW: times one
     p *= 1.0f - s.decay * rate;
     m = s.beta1 * m + (1.0f - s.beta1) * g;
     v = s.beta2 * v + (1.0f - s.beta2) * g * g;
-    const float val = m / (sqrtf(v) + 0.00000001f);
+    float val = m;
+    if (s.use_denom) val /= sqrtf(v) + 0.00000001f;
     p -= rate * val;
     p = fminf(fmaxf(p, s.wmin), s.wmax);
+}
+
+// Ranger's lookahead (crates/trainer/src/optimiser/ranger.rs:23-43), every k-th step, on the tensors that use
+// it: w = alpha * w + (1 - alpha) * slow, and slow takes the same value.  `one_minus[k]` is 1 - alpha of
+// segment k as the host evaluates it; segments with alpha < 0 are left alone.
+struct LookaheadArgs {
+    float4* p;
+    float4* slow;
+    long long total4;
+    int nseg;
+    long long begin4[kMaxSegments], end4[kMaxSegments];
+    float alpha[kMaxSegments], one_minus[kMaxSegments];
+};
+static __global__ void __launch_bounds__(256) lookahead_kernel(const __grid_constant__ LookaheadArgs a) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < a.total4; i += (long long)gridDim.x * blockDim.x) {
+        int si = -1;
+#pragma unroll 1
+        for (int k = 0; k < a.nseg; k++)
+            if (i >= a.begin4[k] && i < a.end4[k] && a.alpha[k] >= 0.f) si = k;
+        if (si < 0) continue;
+        const float4 w = a.p[i], s = a.slow[i];
+        const float al = a.alpha[si], om = a.one_minus[si];
+        const float4 n = make_float4(__fadd_rn(__fmul_rn(al, w.x), __fmul_rn(om, s.x)), __fadd_rn(__fmul_rn(al, w.y), __fmul_rn(om, s.y)),
+                                     __fadd_rn(__fmul_rn(al, w.z), __fmul_rn(om, s.z)), __fadd_rn(__fmul_rn(al, w.w), __fmul_rn(om, s.w)));
+        a.p[i] = n;
+        a.slow[i] = n;
+    }
 }
 
 __global__ void __launch_bounds__(256) adamw_flat_kernel(const __grid_constant__ AdamArgs a) {

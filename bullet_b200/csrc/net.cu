@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -58,6 +59,10 @@ struct Tensor {
     int64_t n = 0, off = 0;
     int64_t rows = 0, cols = 0;  // column-major shape, as the reference's Shape(rows, cols)
     b200_adamw_params hp{0.01f, 0.9f, 0.999f, -1.98f, 1.98f};
+    // which update rule: AdamW, RAdam, or RAdam under Ranger's lookahead (crates/trainer/src/optimiser/{radam,ranger}.rs)
+    int opt_kind = B200_OPT_ADAMW;
+    float n_sma_threshold = 5.0f, alpha = 0.5f;
+    int lookahead_k = 6;
 };
 
 struct Slot {
@@ -165,6 +170,8 @@ struct b200_net {
     cudaEvent_t tev[kTimingRing][kTimingEvents] = {};
     int64_t steps_begun = 0, steps_done = 0, timing_origin = 0;
     bool step_open = false;
+    int64_t opt_step = 0;   // completed optimiser steps (RAdam's step count; reset when the rule changes)
+    float* S = nullptr;     // Ranger's slow weights, same layout as P (allocated when a tensor first uses Ranger)
     int64_t launches = 0, h2d_bytes = 0;
     std::vector<void*> allocations;
 
@@ -185,6 +192,33 @@ struct b200_net {
 };
 
 namespace {
+
+// The per-tensor table of the update kernels for the step that is being enqueued.  RAdam's step size and
+// its "second moment divides yet" flag depend on the step count only and are evaluated here in fp32, as
+// RAdam::update does on the host (radam.rs:295-314).
+void fill_segments(const b200_net* net, b200::AdamArgs& a) {
+    a.nseg = (int)net->tensors.size();
+    for (int i = 0; i < a.nseg; i++) {
+        const Tensor& t = net->tensors[i];
+        b200::AdamSegment seg{t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
+        if (t.opt_kind != B200_OPT_ADAMW) {
+            const float step = (float)(net->opt_step + 1);
+            const float beta2_t = powf(t.hp.beta2, step);
+            const float n_sma_max = 2.0f / (1.0f - t.hp.beta2) - 1.0f;
+            const float n_sma = n_sma_max - 2.0f * step * beta2_t / (1.0f - beta2_t);
+            const float denom = 1.0f - powf(t.hp.beta1, step);
+            if (n_sma > t.n_sma_threshold) {
+                const float p1 = (n_sma - 4.0f) / (n_sma_max - 4.0f), p2 = (n_sma - 2.0f) / n_sma, p3 = n_sma_max / (n_sma_max - 2.0f);
+                seg.rate_scale = sqrtf((1.0f - beta2_t) * p1 * p2 * p3) / denom;
+                seg.use_denom = 1;
+            } else {
+                seg.rate_scale = 1.0f / denom;
+                seg.use_denom = 0;
+            }
+        }
+        a.seg[i] = seg;
+    }
+}
 
 int set_device(const b200_net* net) {
     CK(cudaSetDevice(net->device));
@@ -604,7 +638,7 @@ ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true>) && load_kernel(b200:
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, false>);
     ok = ok && load_kernel(b200::ft_prepare_kernel) && load_kernel(b200::ft_csr_kernel);
     ok = ok && load_kernel(b200::factoriser_merge_kernel) && load_kernel(b200::factoriser_grad_kernel);
-    ok = ok && load_kernel(b200::adamw_flat_kernel);
+    ok = ok && load_kernel(b200::adamw_flat_kernel) && load_kernel(b200::lookahead_kernel);
     ok = ok && load_kernel(b200::adamw_exchange_kernel<0>) && load_kernel(b200::adamw_exchange_kernel<2>);
     ok = ok && load_kernel(b200::adamw_exchange_kernel<4>) && load_kernel(b200::adamw_exchange_kernel<8>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<0>) && load_kernel(b200::adamw_exchange_overlap_kernel<2>);
@@ -934,6 +968,7 @@ static float* kind_base(b200_net* net, int kind) {
         case B200_KIND_MOMENTUM: return net->M;
         case B200_KIND_VELOCITY: return net->V;
         case B200_KIND_GRAD: return net->G;
+        case B200_KIND_SLOW: return net->S;
         default: return nullptr;
     }
 }
@@ -943,7 +978,9 @@ int b200_net_set_tensor(b200_net* net, const char* name, int kind, const float* 
     const Tensor* t = net->find(name);
     if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
     if (n != t->n) return b200::fail(B200_ERR_ARG, "tensor '%s' holds %lld values, %lld given", name, (long long)t->n, (long long)n);
-    if (kind < B200_KIND_WEIGHT || kind > B200_KIND_VELOCITY) return b200::fail(B200_ERR_ARG, "set_tensor: kind %d is not writable", kind);
+    if ((kind < B200_KIND_WEIGHT || kind > B200_KIND_VELOCITY) && kind != B200_KIND_SLOW)
+        return b200::fail(B200_ERR_ARG, "set_tensor: kind %d is not writable", kind);
+    if (kind == B200_KIND_SLOW && !net->S) return b200::fail(B200_ERR_STATE, "set_tensor: no tensor of this network uses Ranger");
     if (int rc = set_device(net)) return rc;
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaMemcpy(kind_base(net, kind) + t->off, host, n * sizeof(float), cudaMemcpyHostToDevice));
@@ -957,7 +994,7 @@ int b200_net_get_tensor(b200_net* net, const char* name, int kind, float* host, 
     if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
     if (n != t->n) return b200::fail(B200_ERR_ARG, "tensor '%s' holds %lld values, %lld asked", name, (long long)t->n, (long long)n);
     float* base = kind_base(net, kind);
-    if (!base) return b200::fail(B200_ERR_ARG, "get_tensor: unknown kind %d", kind);
+    if (!base) return b200::fail(B200_ERR_ARG, "get_tensor: unknown kind %d (or no tensor uses Ranger's slow weights)", kind);
     if (int rc = set_device(net)) return rc;
     CK(cudaStreamSynchronize(net->stream));
     CK(cudaMemcpy(host, base + t->off, n * sizeof(float), cudaMemcpyDeviceToHost));
@@ -968,12 +1005,38 @@ int b200_net_set_adamw(b200_net* net, const char* name, const b200_adamw_params*
     if (!net || !params) return b200::fail(B200_ERR_ARG, "set_adamw: null argument");
     if (!(params->min_weight <= params->max_weight)) return b200::fail(B200_ERR_ARG, "set_adamw: min_weight > max_weight");
     if (!name) {
-        for (auto& t : net->tensors) t.hp = *params;
+        for (auto& t : net->tensors) t.hp = *params, t.opt_kind = B200_OPT_ADAMW;
         return 0;
     }
     Tensor* t = net->find(name);
     if (!t) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
     t->hp = *params;
+    t->opt_kind = B200_OPT_ADAMW;
+    return 0;
+}
+
+int b200_net_set_optimiser(b200_net* net, const char* name, const b200_optimiser_params* params) {
+    if (!net || !params) return b200::fail(B200_ERR_ARG, "set_optimiser: null argument");
+    if (params->kind < B200_OPT_ADAMW || params->kind > B200_OPT_RANGER) return b200::fail(B200_ERR_ARG, "set_optimiser: unknown kind %d", params->kind);
+    if (!(params->min_weight <= params->max_weight)) return b200::fail(B200_ERR_ARG, "set_optimiser: min_weight > max_weight");
+    if (params->kind == B200_OPT_RANGER && (params->k < 1 || !(params->alpha >= 0.f && params->alpha <= 1.f)))
+        return b200::fail(B200_ERR_ARG, "set_optimiser: Ranger needs k >= 1 and alpha in [0, 1]");
+    Tensor* only = nullptr;
+    if (name && !(only = net->find(name))) return b200::fail(B200_ERR_ARG, "no tensor named '%s' in this network", name);
+    if (int rc = set_device(net)) return rc;
+    if (params->kind == B200_OPT_RANGER && !net->S) {  // slow weights start at zero, as in the reference (ranger.rs:70)
+        if (int rc = dev_alloc(net, &net->S, (size_t)net->n_flat)) return rc;
+        CK(cudaMemset(net->S, 0, (size_t)net->n_flat * sizeof(float)));
+    }
+    for (auto& t : net->tensors) {
+        if (only && &t != only) continue;
+        t.hp = {params->decay, params->beta1, params->beta2, params->min_weight, params->max_weight};
+        t.opt_kind = params->kind;
+        t.n_sma_threshold = params->n_sma_threshold;
+        t.alpha = params->alpha;
+        t.lookahead_k = params->k;
+    }
+    net->opt_step = 0;  // OptimiserState::set_params of the lookahead resets its step (ranger.rs:107-113)
     return 0;
 }
 
@@ -1513,11 +1576,7 @@ int b200_update_range(b200_net* net, float lr, float grad_factor, int64_t first_
     a.total4 = n_floats / 4;
     a.rate = lr;
     a.adj = grad_factor;
-    a.nseg = (int)net->tensors.size();
-    for (int i = 0; i < a.nseg; i++) {
-        const Tensor& t = net->tensors[i];
-        a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
-    }
+    fill_segments(net, a);
     const long long blocks = std::min<long long>((a.total4 + 255) / 256, net->sm_count * 16);
     b200::adamw_flat_kernel<<<(unsigned)blocks, 256, 0, net->stream>>>(a);
     LAUNCHED(net);
@@ -1608,11 +1667,7 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     a.total4 = n_floats / 4;
     a.rate = lr;
     a.adj = grad_factor;
-    a.nseg = (int)net->tensors.size();
-    for (int i = 0; i < a.nseg; i++) {
-        const Tensor& t = net->tensors[i];
-        a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
-    }
+    fill_segments(net, a);
     x.world = net->xch_world;
     x.store_peers = gather ? 1 : 0;
     x.head4 = kAlignFloats / 4;
@@ -1698,13 +1753,11 @@ int b200_step_exchange(b200_net* net, int slot, float lr, float grad_factor) {
     a.v = reinterpret_cast<float4*>(net->V);
     a.rate = lr;
     a.adj = grad_factor;
-    a.nseg = (int)net->tensors.size();
+    fill_segments(net, a);
     o.l0f_seg = -1;
     for (int i = 0; i < a.nseg; i++) {
-        const Tensor& t = net->tensors[i];
-        a.seg[i] = {t.off / 4, (t.off + t.n + 3) / 4, t.hp.decay, t.hp.beta1, t.hp.beta2, t.hp.min_weight, t.hp.max_weight};
-        if (&t == l0w) o.l0w_seg = i;
-        if (&t == l0f) o.l0f_seg = i;
+        if (&net->tensors[i] == l0w) o.l0w_seg = i;
+        if (&net->tensors[i] == l0f) o.l0f_seg = i;
     }
     x.world = net->xch_world;
     x.store_peers = 1;
@@ -1793,6 +1846,29 @@ int b200_update_end(b200_net* net) {
     }
     CK(cudaEventRecord(net->loss_ev[ring], net->stream));
     net->updates++;
+    net->opt_step++;
+    {   // Ranger: every k-th step the fast weights are pulled towards the slow ones, which then follow
+        b200::LookaheadArgs la{};
+        la.p = reinterpret_cast<float4*>(net->P);
+        la.slow = reinterpret_cast<float4*>(net->S);
+        la.total4 = net->n_flat / 4;
+        la.nseg = (int)net->tensors.size();
+        bool any = false;
+        for (int i = 0; i < la.nseg; i++) {
+            const Tensor& t = net->tensors[i];
+            la.begin4[i] = t.off / 4;
+            la.end4[i] = (t.off + t.n + 3) / 4;
+            const bool due = t.opt_kind == B200_OPT_RANGER && net->opt_step % t.lookahead_k == 0;
+            la.alpha[i] = due ? t.alpha : -1.f;
+            la.one_minus[i] = 1.0f - t.alpha;
+            any = any || due;
+        }
+        if (any && net->S) {
+            b200::lookahead_kernel<<<net->sm_count * 8, 256, 0, net->stream>>>(la);
+            LAUNCHED(net);
+            net->table_dirty = true;
+        }
+    }
     if (int rc = refresh_table(net)) return rc;
     if (net->step_open) {  // close the timed step begun by the matching backward
         CK(cudaEventRecord(net->tev[net->steps_begun % b200_net::kTimingRing][7], net->stream));
@@ -1928,6 +2004,8 @@ int b200_net_get_stat(b200_net* net, const char* key, int64_t* value) {
     else if (!strcmp(key, "h2d_bytes")) *value = net->h2d_bytes;
     else if (!strcmp(key, "flat_floats")) *value = net->n_flat;
     else if (!strcmp(key, "ft_tiled")) *value = (net->fwd_tiled() ? 1 : 0) + (net->bwd_tiled() ? 2 : 0);
+    else if (!strcmp(key, "slow_weights")) *value = net->S ? 1 : 0;
+    else if (!strcmp(key, "optimiser_steps")) *value = net->opt_step;
     else return b200::fail(B200_ERR_ARG, "get_stat: unknown key '%s'", key);
     return 0;
 }

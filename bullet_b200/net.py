@@ -71,6 +71,22 @@ class Net:
         c = _lib.CAdamW(p.decay, p.beta1, p.beta2, p.min_weight, p.max_weight)
         _lib.check(self.lib.b200_net_set_adamw(self._h, name.encode() if name else None, ctypes.byref(c)))
 
+    def set_optimiser_for_weight(self, name: str | None, params) -> None:
+        """AdamWParams, RAdamParams or RangerParams for one weight (None: all), as the reference's
+        `Optimiser::set_params_for_weight` does for whichever optimiser the trainer was built with."""
+        from .configs import RAdamParams, RangerParams
+
+        big = float(np.finfo(np.float32).max)
+        if isinstance(params, RAdamParams):
+            lo, hi = params.clip if params.clip is not None else (-big, big)
+            c = _lib.COptimiser(1, params.decay, params.beta1, params.beta2, lo, hi, params.n_sma_threshold, 0.5, 6)
+        elif isinstance(params, RangerParams):
+            c = _lib.COptimiser(2, params.decay, params.beta1, params.beta2, params.min_weight, params.max_weight, 5.0,
+                                params.alpha, params.k)
+        else:
+            c = _lib.COptimiser(0, params.decay, params.beta1, params.beta2, params.min_weight, params.max_weight, 5.0, 0.5, 6)
+        _lib.check(self.lib.b200_net_set_optimiser(self._h, name.encode() if name else None, ctypes.byref(c)))
+
     # ------------------------------------------------------------------- batch
     def upload(self, slot: int, stm, nstm, buckets, targets) -> None:
         stm = np.ascontiguousarray(stm, dtype=np.int32)
@@ -284,6 +300,13 @@ def featurise(game: str, records: np.ndarray, desc: NetDesc, scale: float = 400.
     targets = np.empty(n, dtype=np.float32)
     _lib.check(lib.b200_make_targets(_p(records), n, scale, blend, _p(targets)))
     return stm, nstm, buckets, targets
+
+
+def probe_bandwidth(kind: str, nbytes: int, reps: int = 20, device: int = 0) -> float:
+    """GB/s of repeated 16-byte loads ("read") or vector reductions ("atomic") over a buffer of `nbytes`."""
+    out = ctypes.c_double()
+    _lib.check(_lib.load().b200_probe_bandwidth(device, {"read": 0, "atomic": 1}[kind], nbytes, reps, ctypes.byref(out)))
+    return out.value
 
 
 def pack_indices(idx: np.ndarray) -> np.ndarray:

@@ -42,6 +42,7 @@ extern "C" {
 #define B200_KIND_MOMENTUM 1
 #define B200_KIND_VELOCITY 2
 #define B200_KIND_GRAD 3
+#define B200_KIND_SLOW 4 /* Ranger's slow weights (only while a tensor uses Ranger) */
 
 #define B200_NUM_SLOTS 3 /* staging slots for double/triple-buffered upload */
 
@@ -106,6 +107,26 @@ int b200_net_set_tensor(b200_net* net, const char* name, int kind, const float* 
 int b200_net_get_tensor(b200_net* net, const char* name, int kind, float* host, int64_t n);
 /* Optimiser::set_params_for_weight (crates/trainer/src/optimiser.rs:204-206); NULL name = all. */
 int b200_net_set_adamw(b200_net* net, const char* name, const b200_adamw_params* params);
+
+/* The other update rules of the reference, per tensor or (NULL name) for all.  RAdam
+ * (crates/trainer/src/optimiser/radam.rs:20-52,295-314): rectified Adam; the host evaluates the step size and
+ * whether the second moment divides the update from the step count, the kernel is AdamW's with those two
+ * applied; defaults beta 0.9 / 0.999, threshold 5, decay 0, no clipping (pass -FLT_MAX / FLT_MAX).  Ranger
+ * (ranger.rs:45-167): RAdam plus lookahead: every k-th step w = alpha * w + (1 - alpha) * slow and slow = w,
+ * the slow weights starting at zero as in the reference; defaults decay 0.01, beta 0.99 / 0.999, clip +-1.98,
+ * alpha 0.5, k 6.  Setting a rule resets the step count.  The slow weights are tensor kind B200_KIND_SLOW
+ * and travel in `slow.bin` of a checkpoint. */
+#define B200_OPT_ADAMW 0
+#define B200_OPT_RADAM 1
+#define B200_OPT_RANGER 2
+typedef struct b200_optimiser_params {
+    int32_t kind; /* B200_OPT_* */
+    float decay, beta1, beta2, min_weight, max_weight;
+    float n_sma_threshold; /* RAdam, Ranger */
+    float alpha;           /* Ranger */
+    int32_t k;             /* Ranger */
+} b200_optimiser_params;
+int b200_net_set_optimiser(b200_net* net, const char* name, const b200_optimiser_params* params);
 
 /* ---- batch upload.  Stands in for PreparedBatchHost::copy_to_device_async
  * (crates/trainer/src/run/dataloader.rs:41-61): takes the mapper's output in
@@ -334,6 +355,13 @@ int b200_op_ft_forward(int device, void* stream, const b200_ft_op* op);
  * Calls on one device share the array, so calls whose GPU work overlaps race: serialise them. */
 #define B200_OP_NOALLOC_MAX_POSITIONS 16384
 int b200_op_ft_forward_noalloc(int device, void* stream, const b200_ft_op* op);
+
+/* ---- bandwidth probes: the measured denominators for kernels whose table stays in L2.  kind 0: every SM
+ * reads a buffer of `bytes` bytes `reps` times with 16-byte loads (a buffer well below the L2 size measures L2,
+ * one far above it measures HBM); kind 1: 16-byte vector reductions (red.global.add.v4.f32) into it.  Allocates
+ * the buffer for the duration of the call and returns GB/s of the best of three timed rounds.  (No counterpart
+ * in the reference.) */
+int b200_probe_bandwidth(int device, int kind, int64_t bytes, int reps, double* gb_per_s);
 
 /* ---- host featurisers (no device needed).  Records are the 32-byte layouts of
  * bulletformat's ChessBoard / AtaxxBoard as restated in examples/tests/test4.rs:8-36

@@ -140,6 +140,41 @@ class Oracle:
         self.lib.orc_adamw(_ptr(p), _ptr(m), _ptr(v), _ptr(g), ctypes.c_size_t(p.size), c(adj), c(rate),
                            c(hp.decay), c(hp.beta1), c(hp.beta2), c(hp.min_weight), c(hp.max_weight))
 
+    def radam_step(self, step: int, beta1: float, beta2: float, threshold: float = 5.0):
+        """(step size, use_denom) of RAdam's host-side schedule (radam.rs:295-314), in f32."""
+        flag = ctypes.c_int()
+        self.lib.orc_radam_step.restype = ctypes.c_float
+        size = self.lib.orc_radam_step(step, ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(threshold), ctypes.byref(flag))
+        return float(size), int(flag.value)
+
+    def radam(self, p, m, v, g, adj, rate, use_denom, hp):
+        """In place; `rate` = learning rate x step size (f32 product), hp with decay/beta1/beta2/min_weight/max_weight."""
+        c = self._scalar
+        self.lib.orc_radam(_ptr(p), _ptr(m), _ptr(v), _ptr(g), ctypes.c_size_t(p.size), c(adj), c(rate), int(use_denom),
+                           c(hp.decay), c(hp.beta1), c(hp.beta2), c(hp.min_weight), c(hp.max_weight))
+
+    def lookahead(self, w, slow, alpha):
+        self.lib.orc_lookahead(_ptr(w), _ptr(slow), ctypes.c_size_t(w.size), self._scalar(alpha))
+
+    def train_radam(self, desc, weights, batches, lr, params, ranger=None):
+        """RAdam (or, with `ranger` = (alpha, k), Ranger) steps over `batches`, every tensor with the same
+        parameters: -> (weights, m, v, slow or None, [loss_sum per step])."""
+        w = self.to_real(weights)
+        m, v = self.zeros_like(desc), self.zeros_like(desc)
+        slow = self.zeros_like(desc) if ranger else None
+        losses = []
+        for step, (stm, nstm, buckets, targets) in enumerate(batches, start=1):
+            loss, g, _ = self.net_grad(desc, w, stm, nstm, buckets, targets)
+            size, use_denom = self.radam_step(step, params.beta1, params.beta2)
+            rate = float(np.float32(lr) * np.float32(size))
+            for k in w:
+                self.radam(w[k], m[k], v[k], g[k], 1.0 / len(targets), rate, use_denom, params)
+            if ranger and step % ranger[1] == 0:
+                for k in w:
+                    self.lookahead(w[k], slow[k], ranger[0])
+            losses.append(loss)
+        return w, m, v, slow, losses
+
     # -------------------------------------------------------------- featurisers
     def map_chess(self, records, nnz=32, layout32=None):
         n = len(records)

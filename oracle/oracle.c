@@ -216,6 +216,56 @@ void orc_adamw(real* p, real* m, real* v, const real* grad, size_t n, real adj, 
     }
 }
 
+/* radam.rs:35-52 with adj*grad as the gradient.  `rate` is the learning rate already multiplied by the step
+ * size that RAdam::update computes on the host (orc_radam_step below); `use_denom` is its n_sma test. */
+void orc_radam(real* p, real* m, real* v, const real* grad, size_t n, real adj, real rate, int use_denom, real decay,
+               real beta1, real beta2, real wmin, real wmax) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) {
+        real g = adj * grad[i];
+        real pi = p[i];
+        pi = pi * ((real)1 - decay * rate);
+        m[i] = beta1 * m[i] + ((real)1 - beta1) * g;
+        v[i] = beta2 * v[i] + ((real)1 - beta2) * g * g;
+        real val = m[i];
+        if (use_denom) val = val / (R_SQRT(v[i]) + (real)0.00000001f);
+        pi = pi - rate * val;
+        pi = pi > wmin ? pi : wmin;
+        pi = pi < wmax ? pi : wmax;
+        p[i] = pi;
+    }
+}
+
+/* radam.rs:295-314: always in f32, as the reference's host code; returns the step size, *use_denom the flag. */
+float orc_radam_step(int step_count, float beta1, float beta2, float n_sma_threshold, int* use_denom) {
+    const float step = (float)step_count;
+    const float beta2_t = powf(beta2, step);
+    const float n_sma_max = 2.0f / (1.0f - beta2) - 1.0f;
+    const float n_sma = n_sma_max - 2.0f * step * beta2_t / (1.0f - beta2_t);
+    const float denom = 1.0f - powf(beta1, step);
+    *use_denom = n_sma > n_sma_threshold;
+    if (*use_denom) {
+        const float p1 = (n_sma - 4.0f) / (n_sma_max - 4.0f);
+        const float p2 = (n_sma - 2.0f) / n_sma;
+        const float p3 = n_sma_max / (n_sma_max - 2.0f);
+        return sqrtf((1.0f - beta2_t) * p1 * p2 * p3) / denom;
+    }
+    return 1.0f / denom;
+}
+
+/* ranger.rs:23-43: new = alpha * w + (1 - alpha) * slow, written to both. */
+void orc_lookahead(real* w, real* slow, size_t n, real alpha) {
+    const real one_minus = (real)((float)1 - (float)alpha);
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) {
+        real lhs = alpha * w[i];
+        real rhs = one_minus * slow[i];
+        real nw = lhs + rhs;
+        w[i] = nw;
+        slow[i] = nw;
+    }
+}
+
 /* ------------------------------------------------------------ featurisers */
 
 typedef struct {

@@ -291,6 +291,51 @@ def test_per_tensor_adamw_params_and_clipping(oracle32):
     net.close()
 
 
+def test_radam_and_ranger_match_the_oracle(oracle32, tmp_path):
+    """The other two update rules of the reference (radam.rs, ranger.rs): eight steps, so that RAdam passes from its
+    warm-up form (no second-moment division, steps 1-5) to the rectified one, and Ranger's lookahead (k = 3) fires
+    twice from slow weights that start at zero.  Also: Ranger's slow weights survive a checkpoint (slow.bin)."""
+    from bullet_b200.configs import RAdamParams, RangerParams
+
+    name, desc, game = NETS[4]
+    B, steps = 512, 8
+    desc = dataclasses.replace(desc, max_batch=B)
+    rec = synth.records(game, B * steps, seed=27)
+    seq = [oracle32.map_batch(game, rec[i * B:(i + 1) * B], desc) for i in range(steps)]
+    w = rich_weights(desc)
+    big = float(np.finfo(np.float32).max)
+    cases = [
+        ("radam", RAdamParams(), AdamWParams(decay=0.0, beta1=0.9, beta2=0.999, min_weight=-big, max_weight=big), None),
+        ("ranger", RangerParams(k=3), AdamWParams(decay=0.01, beta1=0.99, beta2=0.999, min_weight=-1.98, max_weight=1.98), (0.5, 3)),
+    ]
+    for label, params, inner, ranger in cases:
+        w_ref, m_ref, v_ref, slow_ref, losses_ref = oracle32.train_radam(desc, w, seq, 1e-3, inner, ranger)
+        net = make_net(desc, 0, w)
+        net.set_optimiser_for_weight(None, params)
+        losses = []
+        for i, b in enumerate(seq):
+            net.upload(i % 3, *b)
+            net.step(i % 3, 1e-3, 1.0 / B)
+            losses.append(net.loss())
+        np.testing.assert_allclose(losses, losses_ref, rtol=1e-4, err_msg=label)
+        p, m, v = net.tensors(0), net.tensors(1), net.tensors(2)
+        for k in w_ref:
+            assert rel2(p[k], w_ref[k]) <= 1e-4 and rel2(m[k], m_ref[k]) <= 1e-4 and rel2(v[k], v_ref[k]) <= 1e-4, (label, k)
+        if ranger:
+            slow = net.tensors(4)
+            for k in slow_ref:
+                assert rel2(slow[k], slow_ref[k]) <= 1e-4, k
+            assert not np.array_equal(slow["l1w"], np.zeros_like(slow["l1w"]))
+            net.save_checkpoint(str(tmp_path))
+            assert (tmp_path / "slow.bin").stat().st_size == (tmp_path / "weights.bin").stat().st_size
+            twin = make_net(desc, 0, synth.init_weights(desc, seed=99))
+            twin.set_optimiser_for_weight(None, params)
+            twin.load_checkpoint(str(tmp_path))
+            assert all(np.array_equal(slow[k], v2) for k, v2 in twin.tensors(4).items())
+            twin.close()
+        net.close()
+
+
 def test_phased_step_equals_one_piece_step(oracle32):
     """begin / ft parts / end / update_range / update_end give what step() gives (the factoriser
     gradient is summed per part, so it may differ in the last bits)."""

@@ -161,3 +161,52 @@ def test_thread_count_does_not_change_results(oracle32):
     assert a[0] == b[0]
     for k in a[1]:
         assert np.array_equal(a[1][k], b[1][k]), k
+
+
+def test_radam_schedule_and_update_against_numpy(oracle32):
+    """RAdam's host-side schedule (radam.rs:295-314) and element update (radam.rs:35-52) against the same formulas
+    written out in numpy float32; the first five steps use no second-moment division (n_sma <= 5)."""
+    from bullet_b200.configs import AdamWParams
+
+    f = np.float32
+    b1, b2, thr = f(0.9), f(0.999), f(5.0)
+    flags = []
+    for step in range(1, 12):
+        t = f(step)
+        b2t = np.power(b2, t, dtype=np.float32)
+        nmax = f(2.0) / (f(1.0) - b2) - f(1.0)
+        nsma = nmax - f(2.0) * t * b2t / (f(1.0) - b2t)
+        denom = f(1.0) - np.power(b1, t, dtype=np.float32)
+        if nsma > thr:
+            size = np.sqrt((f(1.0) - b2t) * ((nsma - f(4.0)) / (nmax - f(4.0))) * ((nsma - f(2.0)) / nsma) * (nmax / (nmax - f(2.0)))) / denom
+        else:
+            size = f(1.0) / denom
+        got, flag = oracle32.radam_step(step, 0.9, 0.999)
+        assert flag == int(nsma > thr)
+        # n_sma is a difference of two numbers near 2000 in f32: one ulp of powf moves it by 1e-3 relative, so the
+        # two libraries' powf may only be held together this loosely
+        assert abs(got - float(size)) <= 5e-3 * abs(float(size)), (step, got, size)
+        flags.append(flag)
+    assert flags[:5] == [0] * 5 and flags[5:] == [1] * 6
+    hp = AdamWParams(decay=0.01, beta1=0.9, beta2=0.999, min_weight=-0.5, max_weight=0.5)
+    for use_denom in (0, 1):
+        p, m, v = np.array([0.4, -0.2], np.float32), np.array([0.01, 0.0], np.float32), np.array([1e-4, 0.0], np.float32)
+        g = np.array([8.0, -4.0], np.float32)
+        rate, adj = f(0.05), f(0.25)
+        gg = adj * g
+        pe = p * (f(1) - f(0.01) * rate)
+        me = f(0.9) * m + (f(1) - f(0.9)) * gg
+        ve = f(0.999) * v + (f(1) - f(0.999)) * gg * gg
+        val = me / (np.sqrt(ve) + f(1e-8)) if use_denom else me
+        pe = np.clip(pe - rate * val, f(-0.5), f(0.5))
+        oracle32.radam(p, m, v, g, 0.25, 0.05, use_denom, hp)
+        np.testing.assert_allclose(p, pe, rtol=1e-6)
+        np.testing.assert_allclose(m, me, rtol=1e-6)
+        np.testing.assert_allclose(v, ve, rtol=1e-6)
+
+
+def test_lookahead_pulls_fast_weights_to_slow_ones(oracle32):
+    """ranger.rs:23-43: w = alpha * w + (1 - alpha) * slow, and slow takes the same value."""
+    w, slow = np.array([1.0, -2.0, 0.5], np.float32), np.array([0.0, 2.0, 0.5], np.float32)
+    oracle32.lookahead(w, slow, 0.25)
+    assert np.array_equal(w, np.array([0.25, 1.0, 0.5], np.float32)) and np.array_equal(w, slow)
