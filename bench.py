@@ -4,15 +4,17 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload: the 768x16 -> 2048 pairwise multi-layer net (8 output buckets, 16 -> 32 -> 1) at a
-GLOBAL batch of 131072 seeded synthetic positions per step, sharded evenly over the N ranks
-(strong scaling); one all-reduce of the flat gradient buffer per step when N > 1.
+Workload (--config 4, the default): the 768x16 -> 2048 pairwise multi-layer net (8 output buckets, 16 -> 32 -> 1)
+at a GLOBAL batch of 131072 seeded synthetic positions per step, sharded evenly over the N ranks (strong
+scaling).  For N > 1 the gradient exchange is the library's one kernel over peer memory, run under the
+feature-transformer backward.  --config 0..3 give the same line for the four single-GPU configurations.
 
-Prints ONE JSON line on rank 0.  `value` times the step with batches already resident in
-HBM; `e2e` times the public call sequence (upload from host arrays through pinned staging,
-step, loss read-back) with the next batch's packing and copy overlapped with the current
-step and each step's loss read while the next step runs.  `roofline` covers the dominant feature-transformer kernel, `cpu_baseline` is the CPU
-oracle on this box's host cores.  `--impl reference` times that CPU oracle alone.
+Prints ONE JSON line on rank 0.  `value` times the step with batches already resident in HBM; `e2e` times the
+public call sequence from the raw 32-byte position records a data file holds (copy through pinned staging,
+featurising / packing / grouping, step, loss read-back) with the next batch's upload overlapped with the current
+step and each step's loss read while the next step runs.  `roofline` covers the dominant feature-transformer
+kernel, `cpu_baseline` is the CPU oracle on this box's host cores, `exposed_exchange_ms` (N > 1) is the step
+time minus the time of the same kernels with the exchange taken out.  `--impl reference` times the CPU oracle alone.
 """
 from __future__ import annotations
 
@@ -51,13 +53,13 @@ WORKLOADS = {
 def workload():
     return WORKLOADS[CONFIG].format(GLOBAL_BATCH)
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two tiled feature-transformer kernels,
-# as a two-term model fitted to an ncu capture at 16384 positions per GPU: what is read or written once
-# per launch whatever the batch (the 100.7 MB table in the forward; 63 MB of gradient write-back in the
-# backward) plus a term per position.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two tiled feature-transformer kernels of the
+# 2048-wide pairwise network, as a two-term model through two ncu captures (16384 and 65536 positions per GPU:
+# forward 504.7 and 1829.9 MB, backward 592.7 and 1915.6 MB): what does not grow with the batch (the table, or
+# the gradient's write-back) plus a term per position (the activations written or read: 24.6 KB).
 FT_DRAM_MODEL = {  # kernel: (bytes per launch that do not grow with the batch, bytes per position)
-    "ft_forward": (100_663_296, 22_067),
-    "ft_backward": (63_200_000, 30_327),
+    "ft_forward": (63_000_000, 26_961),
+    "ft_backward": (151_700_000, 26_915),
 }
 CPU_REPEATS = 10  # timed repeats of the CPU oracle at most, in the reference arm and in the in-line baseline alike
 N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)
@@ -422,7 +424,7 @@ def run_ours(args, rank, world, local_rank):
             roofline = dict(hbm_view, bound="hbm", kernel=dom, traffic=traffic)
     roofline.update({"algorithmic_bytes_per_launch": kernels[dom]["algorithmic_bytes"], "launch_ms": kernels[dom]["ms"],
                      "note": "algorithmic bytes count every gathered/updated table row once per active feature; "
-                             "traffic is the DRAM side (ncu capture at 16384 positions, scaled by a two-term model)"})
+                             "traffic is the DRAM side (a two-term model through ncu captures at 16384 and 65536 positions)"})
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()

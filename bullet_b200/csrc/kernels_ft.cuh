@@ -384,27 +384,35 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
         const f32x2 bias = pack2(a.bias[col_a], a.bias[col_b]);
         float* x_out = a.x + col_a;  // with pairwise col_a is also the product's column within the perspective
         __syncthreads();
-        // pair id and list length are fetched one position ahead
+        // pair id, list length and the first four row indices are fetched one pair ahead, and inside a pair
+        // the next four indices before the current four rows are added: the index loads (global memory, the
+        // same address for every lane) are what a warp would otherwise wait for most
         const int seg_end = t.block_begin[block] + last;
         int i = t.block_begin[block] + first + warp;
         int pair = 0, cnt = 0;
+        uint2 g = make_uint2(0, 0);
         if (i < seg_end) {
             pair = t.pair_order ? t.pair_order[i] : i;
             cnt = t.list_count[i];
+            g = __ldg(reinterpret_cast<const uint2*>(t.lists + (size_t)i * t.list_len));
         }
         for (; i < seg_end; i += NW) {
             int pair_next = 0, cnt_next = 0;
+            uint2 g_next_pair = make_uint2(0, 0);
             if (i + NW < seg_end) {
                 pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
                 cnt_next = t.list_count[i + NW];
+                g_next_pair = __ldg(reinterpret_cast<const uint2*>(t.lists + (size_t)(i + NW) * t.list_len));
             }
             const uint2* list = reinterpret_cast<const uint2*>(t.lists + (size_t)i * t.list_len);
             f32x2 acc = 0;  // (+0.0f, +0.0f)
             for (int k = 0; k < cnt; k += 4) {
-                const uint2 g = __ldg(list + (k >> 2));  // the same for every lane
+                uint2 g_ahead = g;
+                if (k + 4 < cnt) g_ahead = __ldg(list + (k >> 2) + 1);  // the same for every lane
                 const f32x2 v0 = line_at(mine, g.x & 0xffffu), v1 = line_at(mine, g.x >> 16);
                 const f32x2 v2 = line_at(mine, g.y & 0xffffu), v3 = line_at(mine, g.y >> 16);
                 acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
+                g = g_ahead;
             }
             acc = add2(acc, bias);
             if (PAIRWISE) {
@@ -419,6 +427,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
             }
             pair = pair_next;
             cnt = cnt_next;
+            g = g_next_pair;
         }
     }
 }
@@ -701,11 +710,13 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
             const int len = (int)(sl & 0xffffu);
             const uint2* lp = reinterpret_cast<const uint2*>(ent + (sl >> 16) * 8);
             f32x2 acc = 0;
+            uint2 g = lp[0];  // (reads beyond a list's end stay inside the entry array, which has room to spare, and are never used)
             for (int k = 0; k < len; k += 4) {
-                const uint2 g = lp[k >> 2];
+                const uint2 g_ahead = lp[(k >> 2) + 1];  // the next four entries, before the current four lines are added
                 const f32x2 v0 = line_at(gl, g.x & 0xffffu), v1 = line_at(gl, g.x >> 16);
                 const f32x2 v2 = line_at(gl, g.y & 0xffffu), v3 = line_at(gl, g.y >> 16);
                 acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
+                g = g_ahead;
             }
             float* dst = a.g_table + (size_t)(block * R + row) * a.H;
             const float ga = lo2(acc), gb = hi2(acc);

@@ -188,8 +188,10 @@ int b200_grad_buffer(b200_net* net, void** device_ptr, int64_t* n_floats);
  * It fences itself: small kernels around it exchange counters with the peers (release stores over
  * NVLink, bounded local polling), so every rank's b200_backward is complete before its gradients are
  * read and every rank's kernel has finished before anyone goes on.  All ranks must call it the same
- * number of times.  A peer that does not arrive within about four seconds makes the wait give up: the
- * stream carries on and b200_loss reports B200_ERR_STATE for that step.  b200_update_end follows as usual. */
+ * number of times.  A peer that does not arrive within about four seconds ("exchange_wait_ms") makes the wait
+ * give up: the kernel returns without touching parameters, optimiser state or any peer's memory, raises a word
+ * on every rank, the stream carries on, and b200_loss reports B200_ERR_STATE for that step on every rank (the
+ * rank that waited also says which rank and which fence were missing).  b200_update_end follows as usual. */
 #define B200_EXCHANGE_HANDLE_BYTES 192
 int b200_exchange_export(b200_net* net, void* handles, int64_t bytes);
 int b200_exchange_import(b200_net* net, int rank, int world, const void* handles, int64_t bytes);
