@@ -287,7 +287,10 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
 template <bool PW>
 int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
-        b200::ft_forward_tiled_kernel<PW><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows), net->stream>>>(a, t);
+        if (b200::ft_fwd_two_lists(a.n))
+            b200::ft_forward_tiled_kernel<PW, true><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len, 2), net->stream>>>(a, t);
+        else
+            b200::ft_forward_tiled_kernel<PW, false><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len, 1), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -631,7 +634,8 @@ int preload_kernels(b200_net* net) {
     ok = ok && load_kernel(b200::dense_regroup_kernel) && load_kernel(b200::dense_small_grads_kernel);
     ok = ok && load_kernel(b200::ft_forward_gather_kernel<true>) && load_kernel(b200::ft_forward_gather_kernel<false>);
     ok = ok && load_kernel(b200::ft_backward_gather_kernel<true>) && load_kernel(b200::ft_backward_gather_kernel<false>);
-ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true>) && load_kernel(b200::ft_forward_tiled_kernel<false>);
+    ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true, true>) && load_kernel(b200::ft_forward_tiled_kernel<false, true>);
+    ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true, false>) && load_kernel(b200::ft_forward_tiled_kernel<false, false>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, true>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, true>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, false>);
@@ -725,7 +729,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
 
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
-                    b200::ft_fwd_smem(d.ft_block_rows) <= kMaxSmem &&
+                    b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2) <= kMaxSmem &&
                     b200::ft_bwd_smem(d.ft_block_rows, d.nnz, b200::ft_bwd_chunk(d.nnz, true)) <= kMaxSmem;
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
@@ -812,11 +816,13 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         if (int rc2 = set_dense(d.dense_out[0])) return bail(rc2);
     }
     if (net->tiled_ok) {
-        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows);
+        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2);
         const int wide = b200::ft_bwd_chunk(d.nnz, true), narrow = b200::ft_bwd_chunk(d.nnz, false);
         const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow);
-cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);

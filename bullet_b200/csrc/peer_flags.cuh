@@ -90,21 +90,24 @@ struct BucketSignal {
     int value;
 };
 
-// End of a backward CTA that worked on `block`: every thread's reductions are ordered before the
-// count, and the CTA that completes the count tells every rank.
+// The count itself, by one thread, once all reductions of the CTA into `block` are ordered before it (a fence by
+// every thread that issued them, then a barrier): the CTA that completes the count tells every rank.
+__device__ __forceinline__ void bucket_count_off(const BucketSignal& s, int block) {
+    const int before = atomicAdd(s.done_count + block, 1);
+    if (before + 1 == s.done_expect[block]) {
+        s.done_count[block] = 0;  // ready for the next launch
+        __threadfence_system();
+        const PeerFlags& f = *s.peers;
+        for (int r = 0; r < f.world; r++) st_release_sys(f.flags[r] + kFlagBucket + block * kMaxRanks + f.rank, s.value);
+    }
+}
+
+// A whole CTA leaves `block`: every thread's reductions are ordered before the count.
 __device__ __forceinline__ void bucket_signal(const BucketSignal& s, int block) {
     if (!s.done_count) return;
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        const int before = atomicAdd(s.done_count + block, 1);
-        if (before + 1 == s.done_expect[block]) {
-            s.done_count[block] = 0;  // ready for the next launch
-            __threadfence_system();
-            const PeerFlags& f = *s.peers;
-            for (int r = 0; r < f.world; r++) st_release_sys(f.flags[r] + kFlagBucket + block * kMaxRanks + f.rank, s.value);
-        }
-    }
+    if (threadIdx.x == 0) bucket_count_off(s, block);
 }
 
 // Blocks without any work item in this launch: nothing will ever count them, announce them now.
