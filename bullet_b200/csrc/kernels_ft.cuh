@@ -71,6 +71,7 @@ struct TileArgs {
     uint16_t* csr_ent;             // [nchunks][ent_cap] pairs of the chunk grouped by row, every list starting on 16 bytes
     int* csr_start;                // [nchunks][start_cap] per row (start / 8) << 16 | length; [R] = entries in all
     int ent_cap, start_cap;
+    int once;                      // table rows and activations through loads that claim no L1 line
     int chunk_len;  // CP: most pairs per chunk
     // backward only, data-parallel runs: the last CTA of every row block tells all ranks that the block's
     // gradient is complete (done_count null: nobody is told)
@@ -263,6 +264,24 @@ __device__ __forceinline__ int tile_col_b(int slab, int lane, int H) {
     return PAIRWISE ? H / 2 + slab * 32 + lane : slab * 64 + 2 * lane + 1;
 }
 
+// Loads of data that is read once per kernel and must not claim L1 lines: with 196-228 KB of the SM's 256 KB
+// configured as shared memory only 28-60 KB of L1 are left, less than these kernels keep in flight.
+__device__ __forceinline__ float4 ld_once4(const float4* p) {
+    float4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float2 ld_once2(const float2* p) {
+    float2 v;
+    asm("ld.global.nc.L1::no_allocate.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_once(const float* p) {
+    float v;
+    asm("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
@@ -372,10 +391,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
                 const float* frow = a.factor ? a.factor + (size_t)((block * R + row) % a.factor_rows) * a.H : nullptr;
                 if (PAIRWISE) {
                     const int c_lo = slab * 32 + q * 4, c_hi = a.H / 2 + c_lo;
-                    float4 lo = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_lo));
-                    float4 hi = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_hi));
+                    const float4* plo = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_lo);
+                    const float4* phi = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c_hi);
+                    float4 lo = t.once ? ld_once4(plo) : __ldg(plo);
+                    float4 hi = t.once ? ld_once4(phi) : __ldg(phi);
                     if (frow) {
-                        lo = add4(lo, __ldg(reinterpret_cast<const float4*>(frow + c_lo)));
+                        lo = add4(lo, __ldg(reinterpret_cast<const float4*>(frow + c_lo)));  // (these gain from L1)
                         hi = add4(hi, __ldg(reinterpret_cast<const float4*>(frow + c_hi)));
                     }
                     dst[0] = make_float4(lo.x, hi.x, lo.y, hi.y);
@@ -383,7 +404,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
                 } else {
                     const int c0 = slab * 64 + q * 8;
                     const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c0);
-                    float4 v0 = __ldg(g), v1 = __ldg(g + 1);
+                    float4 v0 = t.once ? ld_once4(g) : __ldg(g), v1 = t.once ? ld_once4(g + 1) : __ldg(g + 1);
                     if (frow) {
                         v0 = add4(v0, __ldg(reinterpret_cast<const float4*>(frow + c0)));
                         v1 = add4(v1, __ldg(reinterpret_cast<const float4*>(frow + c0 + 4)));
@@ -701,13 +722,18 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
                 if (pl < cn) {
                     const int pair = pairs_s[pl];
                     if (PAIRWISE) {
-                        q0[k] = a.u[(size_t)pair * a.H + col_a];
-                        q1[k] = a.u[(size_t)pair * a.H + col_b];
-                        q2[k] = a.dx[(size_t)pair * (a.H / 2) + col_a];
+                        const float* pa = a.u + (size_t)pair * a.H + col_a;
+                        const float* pb = a.u + (size_t)pair * a.H + col_b;
+                        const float* pd = a.dx + (size_t)pair * (a.H / 2) + col_a;
+                        q0[k] = t.once ? ld_once(pa) : *pa;
+                        q1[k] = t.once ? ld_once(pb) : *pb;
+                        q2[k] = t.once ? ld_once(pd) : *pd;
                     } else {
                         const size_t at = (size_t)pair * a.H + col_a;
-                        const float2 d = *reinterpret_cast<const float2*>(a.dx + at);
-                        const float2 y = *reinterpret_cast<const float2*>(a.x + at);
+                        const float2* pd = reinterpret_cast<const float2*>(a.dx + at);
+                        const float2* py = reinterpret_cast<const float2*>(a.x + at);
+                        const float2 d = t.once ? ld_once2(pd) : *pd;
+                        const float2 y = t.once ? ld_once2(py) : *py;
                         q0[k] = d.x * ft_act_bwd(a.act, y.x);
                         q1[k] = d.y * ft_act_bwd(a.act, y.y);
                     }
@@ -722,7 +748,14 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
                         ga = (q2[k] * q1[k]) * ft_act_bwd(1, q0[k]);
                         gb = (q2[k] * q0[k]) * ft_act_bwd(1, q1[k]);
                     }
-                    g_s[pl * 32 + lane] = pack2(ga, gb);
+                    if (PAIRWISE) {  // the line holds the 32 low-half columns, then the 32 high-half ones: a lane of the
+                                     // walk then owns two neighbouring columns of the table and reduces them at once
+                        float* gf = reinterpret_cast<float*>(g_s) + pl * kTileCols;
+                        gf[lane] = ga;
+                        gf[32 + lane] = gb;
+                    } else {
+                        g_s[pl * 32 + lane] = pack2(ga, gb);
+                    }
                     bsum_a += ga;
                     bsum_b += gb;
                 }
@@ -736,6 +769,8 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         }
         // accumulate: each warp walks the lists of the rows it owns, four entries per 8-byte load
         const unsigned char* gl = smem_raw + lane * 8;
+        // the two table columns this lane sums (see the staging above for the pairwise layout of a line)
+        const int col_w = !PAIRWISE ? col_a : lane < 16 ? slab * 32 + 2 * lane : a.H / 2 + slab * 32 + 2 * (lane - 16);
         for (int row = warp; row < R; row += NW) {
             const unsigned sl = (unsigned)start[row];
             const int len = (int)(sl & 0xffffu);
@@ -749,14 +784,9 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
                 acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
                 g = g_ahead;
             }
-            float* dst = a.g_table + (size_t)(block * R + row) * a.H;
+            float* dst = a.g_table + (size_t)(block * R + row) * a.H + col_w;
             const float ga = lo2(acc), gb = hi2(acc);
-            if (PAIRWISE) {
-                if (ga != 0.f) atomicAdd(dst + col_a, ga);
-                if (gb != 0.f) atomicAdd(dst + col_b, gb);
-            } else if (ga != 0.f || gb != 0.f) {
-                atomicAdd(reinterpret_cast<float2*>(dst + col_a), make_float2(ga, gb));
-            }
+            if (ga != 0.f || gb != 0.f) atomicAdd(reinterpret_cast<float2*>(dst), make_float2(ga, gb));
         }
         __syncthreads();
     }

@@ -130,6 +130,8 @@ struct b200_net {
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
+    int two_lists_min = 65536;  // positions per launch from which the forward keeps two list buffers per warp
+    int ft_once = 1;       // bit 0: the tiled kernels read table rows and activations with loads that claim no L1 line
     int bwd_chunk() const { return b200::ft_bwd_chunk(d.nnz, bwd_wide); }
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
     int fwd_slot = -1, fwd_parts_done = 0, fwd_parts = 0;  // progress of a forward pass run in pieces
@@ -287,7 +289,7 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
 template <bool PW>
 int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
-        if (b200::ft_fwd_two_lists(a.n))
+        if (a.n >= net->two_lists_min)
             b200::ft_forward_tiled_kernel<PW, true><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len, 2), net->stream>>>(a, t);
         else
             b200::ft_forward_tiled_kernel<PW, false><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len, 1), net->stream>>>(a, t);
@@ -417,6 +419,7 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, bool backward) {
     t.csr_ent = s.csr_ent;
     t.csr_start = s.csr_start;
     t.chunk_len = s.chunk_len;
+    t.once = net->ft_once;
     t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz, s.chunk_len);
     t.start_cap = b200::ft_bwd_start_cap(net->d.ft_block_rows);
     if (backward && net->sig_on) {
@@ -934,6 +937,14 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
     }
     if (!strcmp(key, "manual_grad_zero")) {
         net->manual_grad_zero = value != 0;
+        return 0;
+    }
+    if (!strcmp(key, "ft_two_lists_min")) {
+        net->two_lists_min = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "ft_once")) {
+        net->ft_once = (int)value;
         return 0;
     }
     if (!strcmp(key, "ft_bwd_wide")) {  // takes effect for batches uploaded afterwards

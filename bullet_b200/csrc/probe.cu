@@ -1,7 +1,8 @@
 // Bandwidth probes that give the roofline denominators this library quotes for kernels whose working set
 // stays in L2: repeated 16-byte loads of a buffer small enough to stay resident (the gather forward's
 // row reads) and repeated 16-byte vector reductions into such a buffer (the gather backward's
-// red.global.add.v4.f32).  With a buffer far larger than L2 the same loads measure HBM.
+// red.global.add.v4.f32; also with 4 and 8 bytes per lane, as the tiled backward issues them).  With a buffer
+// far larger than L2 the same loads measure HBM.
 // No counterpart in the reference; the numbers are reported by bench.py beside the kernels' achieved rates.
 #include <cuda_runtime.h>
 
@@ -48,11 +49,25 @@ __global__ void __launch_bounds__(512) probe_atomic_kernel(float4* buf, size_t n
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) atomicAdd(buf + i, one);
 }
 
+// the same with one float (kind 2) or two floats (kind 3) per lane: a warp's reduction still covers one
+// contiguous 128- or 256-byte run, as the tiled backward's per-row reductions do
+__global__ void __launch_bounds__(512) probe_atomic1_kernel(float* buf, size_t n, int reps) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (int r = 0; r < reps; r++)
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) atomicAdd(buf + i, 1.f);
+}
+__global__ void __launch_bounds__(512) probe_atomic2_kernel(float2* buf, size_t n2, int reps) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const float2 one = make_float2(1.f, 1.f);
+    for (int r = 0; r < reps; r++)
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += stride) atomicAdd(buf + i, one);
+}
+
 }  // namespace
 
 extern "C" int b200_probe_bandwidth(int device, int kind, int64_t bytes, int reps, double* gb_per_s) {
-    if (!gb_per_s || bytes < 4096 || bytes % 16 || reps < 1 || kind < 0 || kind > 1)
-        return b200::fail(B200_ERR_ARG, "probe_bandwidth: kind 0 (loads) or 1 (vector reductions), bytes a multiple of 16, reps >= 1");
+    if (!gb_per_s || bytes < 4096 || bytes % 16 || reps < 1 || kind < 0 || kind > 3)
+        return b200::fail(B200_ERR_ARG, "probe_bandwidth: kind 0 (loads), 1, 2 or 3 (reductions of 16, 4 or 8 bytes per lane), bytes a multiple of 16, reps >= 1");
     CK(cudaSetDevice(device));
     int sms = 0;
     CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -71,8 +86,12 @@ extern "C" int b200_probe_bandwidth(int device, int kind, int64_t bytes, int rep
         CK(cudaEventRecord(t0));
         if (kind == 0)
             probe_read_kernel<<<grid, 512>>>(buf, n4, reps, sink);
-        else
+        else if (kind == 1)
             probe_atomic_kernel<<<grid, 512>>>(buf, n4, reps);
+        else if (kind == 2)
+            probe_atomic1_kernel<<<grid, 512>>>(reinterpret_cast<float*>(buf), n4 * 4, reps);
+        else
+            probe_atomic2_kernel<<<grid, 512>>>(reinterpret_cast<float2*>(buf), n4 * 2, reps);
         CK(cudaEventRecord(t1));
         CK(cudaEventSynchronize(t1));
         CK(cudaGetLastError());

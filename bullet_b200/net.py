@@ -303,9 +303,11 @@ def featurise(game: str, records: np.ndarray, desc: NetDesc, scale: float = 400.
 
 
 def probe_bandwidth(kind: str, nbytes: int, reps: int = 20, device: int = 0) -> float:
-    """GB/s of repeated 16-byte loads ("read") or vector reductions ("atomic") over a buffer of `nbytes`."""
+    """GB/s of repeated 16-byte loads ("read") or of reductions with 16, 4 or 8 bytes per lane ("atomic",
+    "atomic4", "atomic8") over a buffer of `nbytes`."""
     out = ctypes.c_double()
-    _lib.check(_lib.load().b200_probe_bandwidth(device, {"read": 0, "atomic": 1}[kind], nbytes, reps, ctypes.byref(out)))
+    code = {"read": 0, "atomic": 1, "atomic4": 2, "atomic8": 3}[kind]
+    _lib.check(_lib.load().b200_probe_bandwidth(device, code, nbytes, reps, ctypes.byref(out)))
     return out.value
 
 

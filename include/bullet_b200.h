@@ -360,7 +360,8 @@ int b200_op_ft_forward_noalloc(int device, void* stream, const b200_ft_op* op);
 
 /* ---- bandwidth probes: the measured denominators for kernels whose table stays in L2.  kind 0: every SM
  * reads a buffer of `bytes` bytes `reps` times with 16-byte loads (a buffer well below the L2 size measures L2,
- * one far above it measures HBM); kind 1: 16-byte vector reductions (red.global.add.v4.f32) into it.  Allocates
+ * one far above it measures HBM); kind 1: 16-byte vector reductions (red.global.add.v4.f32) into it; kinds 2
+ * and 3: reductions of 4 and 8 bytes per lane, a warp covering one contiguous run.  Allocates
  * the buffer for the duration of the call and returns GB/s of the best of three timed rounds.  (No counterpart
  * in the reference.) */
 int b200_probe_bandwidth(int device, int kind, int64_t bytes, int reps, double* gb_per_s);
