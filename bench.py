@@ -55,11 +55,11 @@ def workload():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two tiled feature-transformer kernels of the
 # 2048-wide pairwise network, as a two-term model through two ncu captures (16384 and 65536 positions per GPU:
-# forward 504.7 and 1829.9 MB, backward 592.7 and 1915.6 MB): what does not grow with the batch (the table, or
+# forward 495.9 and 1817.5 MB, backward 569.0 and 1824.6 MB): what does not grow with the batch (the table, or
 # the gradient's write-back) plus a term per position (the activations written or read: 24.6 KB).
 FT_DRAM_MODEL = {  # kernel: (bytes per launch that do not grow with the batch, bytes per position)
-    "ft_forward": (63_000_000, 26_961),
-    "ft_backward": (151_700_000, 26_915),
+    "ft_forward": (55_400_000, 26_888),
+    "ft_backward": (150_500_000, 25_545),
 }
 CPU_REPEATS = 10  # timed repeats of the CPU oracle at most, in the reference arm and in the in-line baseline alike
 N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)

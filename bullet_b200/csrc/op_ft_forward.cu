@@ -162,6 +162,7 @@ int run_op(int device, cudaStream_t stream, const b200_ft_op* op, int* scratch) 
     t.lists = reinterpret_cast<uint16_t*>(lists);
     t.list_count = counts_per_pair;
     t.list_len = list_len(op->nnz);
+    t.once = 1;
     b200::ft_prepare_kernel<<<(2 * n + 7) / 8, 256, 0, stream>>>(a, t);
     CK(cudaGetLastError());
     const bool two = b200::ft_fwd_two_lists(n);
