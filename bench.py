@@ -487,8 +487,9 @@ def main():
     ap.add_argument("--dp-peer", type=int, default=1,
                     help="N > 1: 1 = the exchange as one library kernel over peer memory (reduce + AdamW + gather); "
                          "0, or a box that refuses the peer mapping = NCCL collectives (--dp-shard)")
-    ap.add_argument("--dp-overlap", type=int, default=1,
-                    help="N > 1 with --dp-peer 1: 1 = the exchange kernel runs under the backward pass (b200_step_exchange)")
+    ap.add_argument("--dp-overlap", type=int, default=0,
+                    help="N > 1 with --dp-peer 1: 1 = the exchange kernel runs under the backward pass (b200_step_exchange); "
+                         "measured slower than the exchange behind the backward on 2 GPUs, hence off")
     ap.add_argument("--dp-parts", type=int, default=1,
                     help="N > 1: slices of l0w exchanged while the backward (and, with --dp-shard 1, the next forward) still runs")
     ap.add_argument("--e2e-source", default="records", choices=["records", "records-host", "arrays"],

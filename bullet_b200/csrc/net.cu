@@ -130,9 +130,11 @@ struct b200_net {
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
+    bool exchange_bulk = false;  // the peer exchange moves gradients and weights with bulk asynchronous copies (measured no faster)
     int two_lists_min = 65536;  // positions per launch from which the forward keeps two list buffers per warp
     int ft_once = 1;       // bit 0: the tiled kernels read table rows and activations with loads that claim no L1 line
-    int bwd_chunk() const { return b200::ft_bwd_chunk(d.nnz, bwd_wide); }
+    int wide_chunk = 0;    // pairs per chunk of the 1024-thread backward: the largest of the two candidates that fits
+    int bwd_chunk() const { return bwd_wide ? wide_chunk : b200::ft_bwd_chunk(d.nnz, false); }
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
     int fwd_slot = -1, fwd_parts_done = 0, fwd_parts = 0;  // progress of a forward pass run in pieces
     // peers of the fused data-parallel update: every rank's gradient and parameter buffer mapped here
@@ -306,7 +308,7 @@ template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
         const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len);
-        const bool wide = t.chunk_len == b200::ft_bwd_chunk(a.nnz, true);
+        const bool wide = t.chunk_len == net->wide_chunk;
 // data-parallel runs that announce finished row blocks take an instantiation of their own: the
         // fence it ends with makes every CTA wait for its reductions to land (measured: +18 %)
         if (wide && t.sig.done_count)
@@ -372,7 +374,7 @@ int ft_forward_grid(const b200_net* net, const Slot& s, int first, int last) {
 }
 int ft_backward_grid(const b200_net* net, const Slot& s, int first, int last, bool beside_exchange) {
     const long long units = (long long)net->nslabs * (s.chunk_begin[last] - s.chunk_begin[first]);
-    const int per_sm = s.chunk_len == b200::ft_bwd_chunk(net->d.nnz, true) ? 1 : 2;
+    const int per_sm = s.chunk_len == net->wide_chunk ? 1 : 2;
     const int sms = net->sm_count - (beside_exchange ? std::min(net->overlap_ctas, net->sm_count - 1) : 0);
     return (int)std::max<long long>(1, std::min<long long>((long long)sms * per_sm, units));
 }
@@ -648,6 +650,7 @@ int preload_kernels(b200_net* net) {
     ok = ok && load_kernel(b200::adamw_flat_kernel) && load_kernel(b200::lookahead_kernel);
     ok = ok && load_kernel(b200::adamw_exchange_kernel<0>) && load_kernel(b200::adamw_exchange_kernel<2>);
     ok = ok && load_kernel(b200::adamw_exchange_kernel<4>) && load_kernel(b200::adamw_exchange_kernel<8>);
+    ok = ok && load_kernel(b200::adamw_exchange_bulk_kernel<0>) && load_kernel(b200::adamw_exchange_bulk_kernel<2>) && load_kernel(b200::adamw_exchange_bulk_kernel<4>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<0>) && load_kernel(b200::adamw_exchange_overlap_kernel<2>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<4>) && load_kernel(b200::adamw_exchange_overlap_kernel<8>);
     ok = ok && load_kernel(b200::prep_featurise_kernel) && load_kernel(b200::prep_scan_kernel) && load_kernel(b200::prep_scatter_kernel);
@@ -734,6 +737,10 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
                     b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2) <= kMaxSmem &&
                     b200::ft_bwd_smem(d.ft_block_rows, d.nnz, b200::ft_bwd_chunk(d.nnz, true)) <= kMaxSmem;
+    if (net->tiled_ok) {
+        const int larger = b200::ft_bwd_chunk_large(d.nnz);
+        net->wide_chunk = b200::ft_bwd_smem(d.ft_block_rows, d.nnz, larger) <= kMaxSmem ? larger : b200::ft_bwd_chunk(d.nnz, true);
+    }
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
 
@@ -765,7 +772,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         // sized for whichever backward shape needs more: every block may end in a partly filled chunk
         size_t ent_total = 0, max_chunks = 0;
         for (int wide = 0; wide < 2; wide++) {
-            const int cp = b200::ft_bwd_chunk(d.nnz, wide != 0);
+            const int cp = wide ? net->wide_chunk : b200::ft_bwd_chunk(d.nnz, false);
             const size_t chunks = 2 * B / cp + net->nblocks + 1;
             max_chunks = std::max(max_chunks, chunks);
             ent_total = std::max(ent_total, chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz, cp));
@@ -820,7 +827,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     }
     if (net->tiled_ok) {
         const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2);
-        const int wide = b200::ft_bwd_chunk(d.nnz, true), narrow = b200::ft_bwd_chunk(d.nnz, false);
+        const int wide = net->wide_chunk, narrow = b200::ft_bwd_chunk(d.nnz, false);
         const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
@@ -837,6 +844,9 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         cudaFuncSetAttribute(b200::ft_csr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)b200::ft_csr_smem(d.ft_block_rows, d.nnz, wide));
     }
+    cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)b200::exchange_bulk_smem<2>());
+    cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)b200::exchange_bulk_smem<4>());
+    cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)b200::exchange_bulk_smem<0>());
     cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
     cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
     cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
@@ -937,6 +947,10 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
     }
     if (!strcmp(key, "manual_grad_zero")) {
         net->manual_grad_zero = value != 0;
+        return 0;
+    }
+    if (!strcmp(key, "exchange_bulk")) {  // 0: the exchange kernel fetches peer gradients with per-thread loads
+        net->exchange_bulk = value != 0;
         return 0;
     }
     if (!strcmp(key, "ft_two_lists_min")) {
@@ -1703,6 +1717,20 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     const long long cap = stream ? (net->exchange_ctas > 0 ? net->exchange_ctas : net->sm_count) : net->sm_count * 8;
     const long long blocks = std::min<long long>((a.total4 + 127) / 128, cap);
     cudaStream_t on = stream ? static_cast<cudaStream_t>(stream) : net->stream;
+    if (net->exchange_bulk && !stream && x.store_peers) {
+        // gradients fetched and weights sent by bulk copies: one CTA per SM over the tiles of this rank's share
+        const long long tiles = (a.total4 + b200::kBulkTile - 1) / b200::kBulkTile;
+        const unsigned ctas = (unsigned)std::min<long long>(net->sm_count, tiles);
+        switch (x.world) {
+            case 2: b200::adamw_exchange_bulk_kernel<2><<<ctas, b200::kBulkTile, b200::exchange_bulk_smem<2>(), on>>>(x); break;
+            case 4: b200::adamw_exchange_bulk_kernel<4><<<ctas, b200::kBulkTile, b200::exchange_bulk_smem<4>(), on>>>(x); break;
+            default: b200::adamw_exchange_bulk_kernel<0><<<ctas, b200::kBulkTile, b200::exchange_bulk_smem<0>(), on>>>(x); break;
+        }
+        LAUNCHED(net);
+        net->table_dirty = true;
+        if (first_float == 0) net->loss_in_param = true;
+        return 0;
+    }
     switch (x.world) {
         case 2: b200::adamw_exchange_kernel<2><<<(unsigned)blocks, 128, 0, on>>>(x); break;
         case 4: b200::adamw_exchange_kernel<4><<<(unsigned)blocks, 128, 0, on>>>(x); break;

@@ -19,7 +19,9 @@ pytestmark = pytest.mark.gpu
 
 MODES = {"allreduce": dict(), "sharded": dict(shard_optimiser=True), "pipelined": dict(shard_optimiser=True, parts=4),
          "allreduce_parts": dict(parts=4), "peer": dict(peer_exchange=True),
-         "peer_pipelined": dict(peer_exchange=True, parts=4), "peer_overlap": dict(peer_overlap=True)}
+         "peer_pipelined": dict(peer_exchange=True, parts=4), "peer_overlap": dict(peer_overlap=True),
+         # the peer kernel with bulk asynchronous copies in place of per-thread loads and stores
+         "peer_bulk": dict(peer_exchange=True, net_options={"exchange_bulk": 1})}
 GLOBAL, STEPS, LR = 2048, 4, 1e-2
 ORACLE_GLOBAL, ORACLE_STEPS, ORACLE_MODES = 4096, 100, ("peer", "peer_overlap")
 
@@ -53,6 +55,9 @@ def _worker(rank, world, port, out_dir):
             print(f"rank {rank}: exchange form {mode}", flush=True)
             net = Net(dataclasses.replace(desc, max_batch=GLOBAL // world), device=rank, stream=stream.cuda_stream)
             net.load_weights(weights)
+            kw = dict(kw)
+            for key, value in kw.pop("net_options", {}).items():
+                net.set_option(key, value)
             dp = DataParallelStep(NetEngine(net, torch.device("cuda", rank)), GLOBAL, **kw)
             losses = []
             for s in range(STEPS):
