@@ -187,24 +187,25 @@ __global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------
-// The same exchange with the gradients fetched by bulk asynchronous copies (cp.async.bulk, the TMA
-// engine without a tensor map) instead of per-thread loads.  Plain 16-byte loads of peer memory reached
-// about 270 GB/s per GPU in this kernel's place however many were in flight (53.5 MB in 0.17 ms on two
-// GPUs, 93.6 MB in 0.33 ms on eight), a third of what a peer copy reaches; a bulk copy moves 4 KB per
-// instruction and keeps no load slot of the SM busy while it is under way.
-// One CTA of 256 threads per SM; the rank's share is cut into tiles of 256 float4s.  Per tile and stage:
-// thread 0 arms the stage's mbarrier with the byte count and issues one bulk load per rank (that rank's
-// gradients of the tile, peer memory -> this CTA's shared memory); four stages are in flight.  When the
-// barrier flips every thread sums its float4 over the ranks in rank order from shared memory, runs AdamW on
-// the local p, m, v (loaded before the wait), and puts the new p into the stage's output line; after a
-// proxy fence and a barrier thread 0 sends that line to every rank's parameter buffer with one bulk
-// store per rank.  No multicast, no tensor maps, no cluster: plain bulk copies of linear memory.
+// The same exchange with every operand moved by bulk asynchronous copies (cp.async.bulk, the TMA engine
+// without a tensor map) instead of per-thread loads and stores.  Timed alone on two GPUs the per-thread
+// kernel needs 0.186 ms for what a local update of the same share does in 0.078 ms: a thread's loads wait
+// two to three microseconds for peer memory, its stores follow behind them, and what an SM can keep in flight
+// through registers bounds the rate (with a quarter of the CTAs the kernel takes three times as long).  Bulk
+// copies cost no registers and no load slots: everything a tile needs is under way several tiles ahead, and
+// the stores leave asynchronously as well.
+// One CTA per SM; the rank's share is cut into tiles of kBulkTile float4s, one per thread.  Per tile and
+// stage thread 0 arms the stage's mbarrier with the byte count and issues one bulk load per rank (that
+// rank's gradients of the tile, peer memory -> this CTA's shared memory) and three for the local p, m and v;
+// kBulkStages tiles are in flight.  When the barrier flips every thread sums its float4 over the ranks in
+// rank order, runs AdamW, and puts the new p, m, v into the stage's three output lines; after a proxy fence
+// and a barrier thread 0 sends p to every rank's parameter buffer and m, v home, one bulk store each.
+// No multicast, no tensor maps, no cluster: plain bulk copies of linear memory.
 // Every wait is bounded: an mbarrier that does not flip within the budget raises the timeout word on every
 // rank (detail code -2), the CTA waits for its stores and leaves.
-constexpr int kBulkTile = 256, kBulkStages = 4;
-template <int WORLD>
+template <int WORLD, int kBulkTile, int kBulkStages>
 __host__ __device__ constexpr size_t exchange_bulk_smem() {
-    return (size_t)kBulkStages * ((WORLD > 0 ? WORLD : kMaxRanks) + 1) * kBulkTile * sizeof(float4) + kBulkStages * 8;
+    return (size_t)kBulkStages * ((WORLD > 0 ? WORLD : kMaxRanks) + 6) * kBulkTile * sizeof(float4) + kBulkStages * 8;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -238,13 +239,14 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int WORLD>
+template <int WORLD, int kBulkTile, int kBulkStages>
 __global__ void __launch_bounds__(kBulkTile, 1) adamw_exchange_bulk_kernel(const __grid_constant__ ExchangeArgs x) {
     constexpr int W = WORLD > 0 ? WORLD : kMaxRanks;
+    constexpr int kIn = W + 3, kOut = 3;  // lines per stage: gradients by rank, p, m, v; new p, m, v
     extern __shared__ __align__(128) unsigned char bulk_smem[];
-    float4* in = reinterpret_cast<float4*>(bulk_smem);                      // [stage][rank][kBulkTile]
-    float4* out = in + (size_t)kBulkStages * W * kBulkTile;                 // [stage][kBulkTile]
-    uint64_t* bar = reinterpret_cast<uint64_t*>(out + (size_t)kBulkStages * kBulkTile);
+    float4* in = reinterpret_cast<float4*>(bulk_smem);                  // [stage][kIn][kBulkTile]
+    float4* out = in + (size_t)kBulkStages * kIn * kBulkTile;           // [stage][kOut][kBulkTile]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(out + (size_t)kBulkStages * kOut * kBulkTile);
     __shared__ int gave_up;
     const AdamArgs& a = x.adam;
     if (x.wait_ready > 0 && !peer_wait_cta(x.flags, kFlagReady, x.wait_ready)) return;
@@ -256,10 +258,14 @@ __global__ void __launch_bounds__(kBulkTile, 1) adamw_exchange_bulk_kernel(const
     __syncthreads();
     const long long tiles = (a.total4 + kBulkTile - 1) / kBulkTile;
     auto fetch = [&](long long tile, int stage) {  // thread 0
-        const long long j0 = tile * kBulkTile;
+        const long long j0 = tile * kBulkTile, i0 = a.first4 + j0;
         const uint32_t bytes = (uint32_t)min((long long)kBulkTile, a.total4 - j0) * 16u;
-        mbar_expect_tx(bar + stage, bytes * (uint32_t)x.world);
-        for (int r = 0; r < x.world; r++) bulk_load(in + ((size_t)stage * W + r) * kBulkTile, x.g[r] + a.first4 + j0, bytes, bar + stage);
+        float4* dst = in + (size_t)stage * kIn * kBulkTile;
+        mbar_expect_tx(bar + stage, bytes * (uint32_t)(x.world + 3));
+        for (int r = 0; r < x.world; r++) bulk_load(dst + (size_t)r * kBulkTile, x.g[r] + i0, bytes, bar + stage);
+        bulk_load(dst + (size_t)W * kBulkTile, a.p + i0, bytes, bar + stage);
+        bulk_load(dst + (size_t)(W + 1) * kBulkTile, a.m + i0, bytes, bar + stage);
+        bulk_load(dst + (size_t)(W + 2) * kBulkTile, a.v + i0, bytes, bar + stage);
     };
     if (threadIdx.x == 0)
         for (int s = 0; s < kBulkStages; s++) {
@@ -273,17 +279,14 @@ __global__ void __launch_bounds__(kBulkTile, 1) adamw_exchange_bulk_kernel(const
         const long long j = tile * kBulkTile + threadIdx.x, i = a.first4 + j;
         const bool live = j < a.total4;
         int si = -1;
-        float4 p = make_float4(0.f, 0.f, 0.f, 0.f), m = p, v = p;
         if (live) {
 #pragma unroll 1
             for (int q = 0; q < a.nseg; q++)
                 if (i >= a.seg[q].begin4 && i < a.seg[q].end4) si = q;
-            p = a.p[i];
-            if (si >= 0) m = a.m[i], v = a.v[i];
         }
-        // the stores that last read this stage's output line (tile k - kBulkStages) have left shared memory
+        // the stores that last read this stage's output lines (tile k - kBulkStages) have left shared memory
         if (threadIdx.x == 0) bulk_wait_read<kBulkStages - 1>();
-        {   // wait for this tile's gradients, bounded
+        {   // wait for this tile's operands, bounded
             long long spins = 0;
             while (!mbar_try_wait(bar + stage, parity)) {
                 if (++spins > x.flags.spin_limit) {
@@ -305,8 +308,9 @@ __global__ void __launch_bounds__(kBulkTile, 1) adamw_exchange_bulk_kernel(const
             }
             return;
         }
+        float4* dst = out + (size_t)stage * kOut * kBulkTile + threadIdx.x;
         if (live) {
-            const float4* src = in + (size_t)stage * W * kBulkTile + threadIdx.x;
+            const float4* src = in + (size_t)stage * kIn * kBulkTile + threadIdx.x;
             float4 g = src[0];
 #pragma unroll
             for (int r = 1; r < W; r++)
@@ -314,25 +318,29 @@ __global__ void __launch_bounds__(kBulkTile, 1) adamw_exchange_bulk_kernel(const
                     const float4 t = src[(size_t)r * kBulkTile];
                     g.x += t.x, g.y += t.y, g.z += t.z, g.w += t.w;
                 }
+            float4 p = src[(size_t)W * kBulkTile], m = src[(size_t)(W + 1) * kBulkTile], v = src[(size_t)(W + 2) * kBulkTile];
             if (si >= 0) {
                 const AdamSegment& s = a.seg[si];
                 adam_op(s, a.rate, a.adj * g.x, p.x, m.x, v.x);
                 adam_op(s, a.rate, a.adj * g.y, p.y, m.y, v.y);
                 adam_op(s, a.rate, a.adj * g.z, p.z, m.z, v.z);
                 adam_op(s, a.rate, a.adj * g.w, p.w, m.w, v.w);
-                a.m[i] = m;
-                a.v[i] = v;
             } else if (i < x.head4) {
                 p = g;  // the summed loss (and zeros)
             }           // else: alignment padding between tensors keeps what it holds
-            out[(size_t)stage * kBulkTile + threadIdx.x] = p;
+            dst[0] = p;
+            dst[kBulkTile] = m;
+            dst[2 * kBulkTile] = v;
         }
-        fence_proxy_async();  // the output line must be visible to the bulk stores
-        __syncthreads();      // ... and every thread has read this stage's gradients
+        fence_proxy_async();  // the output lines must be visible to the bulk stores
+        __syncthreads();      // ... and every thread has read this stage's operands
         if (threadIdx.x == 0) {
-            const long long j0 = tile * kBulkTile;
+            const long long j0 = tile * kBulkTile, i0 = a.first4 + j0;
             const uint32_t bytes = (uint32_t)min((long long)kBulkTile, a.total4 - j0) * 16u;
-            for (int r = 0; r < x.world; r++) bulk_store(x.p_out[r] + a.first4 + j0, out + (size_t)stage * kBulkTile, bytes);
+            const float4* line = out + (size_t)stage * kOut * kBulkTile;
+            for (int r = 0; r < x.world; r++) bulk_store(x.p_out[r] + i0, line, bytes);
+            bulk_store(a.m + i0, line + kBulkTile, bytes);
+            bulk_store(a.v + i0, line + 2 * kBulkTile, bytes);
             bulk_commit();
             const long long next = tile + (long long)kBulkStages * gridDim.x;
             if (next < tiles) fetch(next, stage);

@@ -130,11 +130,17 @@ struct b200_net {
     Slot slots[B200_NUM_SLOTS];
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
-    bool exchange_bulk = false;  // the peer exchange moves gradients and weights with bulk asynchronous copies (measured no faster)
+    int exchange_bulk = 0;  // the peer exchange moves gradients and weights with bulk asynchronous copies (measured no faster)
     int two_lists_min = 65536;  // positions per launch from which the forward keeps two list buffers per warp
     int ft_once = 1;       // bit 0: the tiled kernels read table rows and activations with loads that claim no L1 line
-    int wide_chunk = 0;    // pairs per chunk of the 1024-thread backward: the largest of the two candidates that fits
-    int bwd_chunk() const { return bwd_wide ? wide_chunk : b200::ft_bwd_chunk(d.nnz, false); }
+    int wide_chunk = 0;    // the larger chunk of the 1024-thread backward where it fits into shared memory, else the standard one
+    // Pairs per chunk for a batch of n positions.  The larger chunk saves list copies, barriers and reductions,
+    // but needs enough units to keep every SM's share even: measured faster from about eight units per SM.
+    int bwd_chunk(int n) const {
+        if (!bwd_wide) return b200::ft_bwd_chunk(d.nnz, false);
+        const long long units = (long long)nslabs * ((2LL * n + wide_chunk - 1) / wide_chunk);
+        return units >= 8LL * sm_count ? wide_chunk : b200::ft_bwd_chunk(d.nnz, true);
+    }
     int bwd_slot = -1, bwd_parts_done = 0, bwd_parts = 0;  // progress of a phased backward
     int fwd_slot = -1, fwd_parts_done = 0, fwd_parts = 0;  // progress of a forward pass run in pieces
     // peers of the fused data-parallel update: every rank's gradient and parameter buffer mapped here
@@ -308,7 +314,7 @@ template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
         const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len);
-        const bool wide = t.chunk_len == net->wide_chunk;
+        const bool wide = t.chunk_len > b200::ft_bwd_chunk(a.nnz, false);
 // data-parallel runs that announce finished row blocks take an instantiation of their own: the
         // fence it ends with makes every CTA wait for its reductions to land (measured: +18 %)
         if (wide && t.sig.done_count)
@@ -374,7 +380,7 @@ int ft_forward_grid(const b200_net* net, const Slot& s, int first, int last) {
 }
 int ft_backward_grid(const b200_net* net, const Slot& s, int first, int last, bool beside_exchange) {
     const long long units = (long long)net->nslabs * (s.chunk_begin[last] - s.chunk_begin[first]);
-    const int per_sm = s.chunk_len == net->wide_chunk ? 1 : 2;
+    const int per_sm = s.chunk_len > b200::ft_bwd_chunk(net->d.nnz, false) ? 1 : 2;
     const int sms = net->sm_count - (beside_exchange ? std::min(net->overlap_ctas, net->sm_count - 1) : 0);
     return (int)std::max<long long>(1, std::min<long long>((long long)sms * per_sm, units));
 }
@@ -650,7 +656,10 @@ int preload_kernels(b200_net* net) {
     ok = ok && load_kernel(b200::adamw_flat_kernel) && load_kernel(b200::lookahead_kernel);
     ok = ok && load_kernel(b200::adamw_exchange_kernel<0>) && load_kernel(b200::adamw_exchange_kernel<2>);
     ok = ok && load_kernel(b200::adamw_exchange_kernel<4>) && load_kernel(b200::adamw_exchange_kernel<8>);
-    ok = ok && load_kernel(b200::adamw_exchange_bulk_kernel<0>) && load_kernel(b200::adamw_exchange_bulk_kernel<2>) && load_kernel(b200::adamw_exchange_bulk_kernel<4>);
+    ok = ok && load_kernel(b200::adamw_exchange_bulk_kernel<2, 256, 6>) && load_kernel(b200::adamw_exchange_bulk_kernel<2, 512, 3>);
+    ok = ok && load_kernel(b200::adamw_exchange_bulk_kernel<2, 128, 12>) && load_kernel(b200::adamw_exchange_bulk_kernel<4, 256, 5>);
+    ok = ok && load_kernel(b200::adamw_exchange_bulk_kernel<0, 256, 3>) && load_kernel(b200::adamw_exchange_bulk_kernel<0, 512, 1>);
+    ok = ok && load_kernel(b200::adamw_exchange_bulk_kernel<0, 128, 6>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<0>) && load_kernel(b200::adamw_exchange_overlap_kernel<2>);
     ok = ok && load_kernel(b200::adamw_exchange_overlap_kernel<4>) && load_kernel(b200::adamw_exchange_overlap_kernel<8>);
     ok = ok && load_kernel(b200::prep_featurise_kernel) && load_kernel(b200::prep_scan_kernel) && load_kernel(b200::prep_scatter_kernel);
@@ -771,8 +780,8 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (net->tiled_ok) {
         // sized for whichever backward shape needs more: every block may end in a partly filled chunk
         size_t ent_total = 0, max_chunks = 0;
-        for (int wide = 0; wide < 2; wide++) {
-            const int cp = wide ? net->wide_chunk : b200::ft_bwd_chunk(d.nnz, false);
+        for (int shape = 0; shape < 3; shape++) {
+            const int cp = shape == 2 ? net->wide_chunk : b200::ft_bwd_chunk(d.nnz, shape != 0);
             const size_t chunks = 2 * B / cp + net->nblocks + 1;
             max_chunks = std::max(max_chunks, chunks);
             ent_total = std::max(ent_total, chunks * b200::ft_bwd_ent_cap(d.ft_block_rows, d.nnz, cp));
@@ -844,9 +853,6 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         cudaFuncSetAttribute(b200::ft_csr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)b200::ft_csr_smem(d.ft_block_rows, d.nnz, wide));
     }
-    cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)b200::exchange_bulk_smem<2>());
-    cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)b200::exchange_bulk_smem<4>());
-    cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)b200::exchange_bulk_smem<0>());
     cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
     cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
     cudaFuncSetAttribute(b200::adamw_exchange_overlap_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, b200::kOverlapSmem);
@@ -950,7 +956,7 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
         return 0;
     }
     if (!strcmp(key, "exchange_bulk")) {  // 0: the exchange kernel fetches peer gradients with per-thread loads
-        net->exchange_bulk = value != 0;
+        net->exchange_bulk = (int)value;
         return 0;
     }
     if (!strcmp(key, "ft_two_lists_min")) {
@@ -1202,7 +1208,7 @@ static void derive_tables(b200_net* net, Slot& s, const int* bucket_count, const
         // chunks of the tiled backward: every block cut into the fewest equal runs of at most ft_bwd_chunk pairs
         int4* h_chunks = s.host<int4>(s.off_chunks);
         int* h_cbegin = s.host<int>(s.off_cbegin);
-        const int cp = net->bwd_chunk();
+        const int cp = net->bwd_chunk(h_blocks[nb] / 2);  // (all pairs of the batch = two per position)
         s.chunk_len = cp;
         int nc = 0;
         for (int b = 0; b < nb; b++) {
@@ -1719,13 +1725,27 @@ int b200_update_exchange_range(b200_net* net, float lr, float grad_factor, int64
     cudaStream_t on = stream ? static_cast<cudaStream_t>(stream) : net->stream;
     if (net->exchange_bulk && !stream && x.store_peers) {
         // gradients fetched and weights sent by bulk copies: one CTA per SM over the tiles of this rank's share
-        const long long tiles = (a.total4 + b200::kBulkTile - 1) / b200::kBulkTile;
-        const unsigned ctas = (unsigned)std::min<long long>(net->sm_count, tiles);
-        switch (x.world) {
-            case 2: b200::adamw_exchange_bulk_kernel<2><<<ctas, b200::kBulkTile, b200::exchange_bulk_smem<2>(), on>>>(x); break;
-            case 4: b200::adamw_exchange_bulk_kernel<4><<<ctas, b200::kBulkTile, b200::exchange_bulk_smem<4>(), on>>>(x); break;
-            default: b200::adamw_exchange_bulk_kernel<0><<<ctas, b200::kBulkTile, b200::exchange_bulk_smem<0>(), on>>>(x); break;
+#define BULK(W, T, S)                                                                                                           \
+    do {                                                                                                                        \
+        const long long tiles = (a.total4 + (T)-1) / (T);                                                                       \
+        const unsigned ctas = (unsigned)std::min<long long>(net->sm_count, tiles);                                              \
+        cudaFuncSetAttribute(b200::adamw_exchange_bulk_kernel<W, T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                             (int)b200::exchange_bulk_smem<W, T, S>());                                                         \
+        b200::adamw_exchange_bulk_kernel<W, T, S><<<ctas, T, b200::exchange_bulk_smem<W, T, S>(), on>>>(x);                     \
+    } while (0)
+        const int variant = net->exchange_bulk;
+        if (x.world == 2) {
+            if (variant == 2) BULK(2, 512, 3);
+            else if (variant == 3) BULK(2, 128, 12);
+            else BULK(2, 256, 6);
+        } else if (x.world == 4) {
+            BULK(4, 256, 5);
+        } else {
+            if (variant == 2) BULK(0, 512, 1);
+            else if (variant == 3) BULK(0, 128, 6);
+            else BULK(0, 256, 3);
         }
+#undef BULK
         LAUNCHED(net);
         net->table_dirty = true;
         if (first_float == 0) net->loss_in_param = true;
