@@ -138,11 +138,13 @@ def test_one_step_parity(oracle32, oracle64, name, desc, game):
 
 
 def record_parity(rows):
-    """Append measured parity figures to gpurun_out/parity_100_steps.jsonl (scratch, not tracked)."""
+    """Append the measured parity figures, one JSON object per line, to parity_100_steps.jsonl in the folder
+    B200_PARITY_LOG_DIR names (default: the system's temporary folder); a scratch record, not tracked."""
     import json
     import os
+    import tempfile
 
-    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    out_dir = os.environ.get("B200_PARITY_LOG_DIR") or tempfile.gettempdir()
     try:
         os.makedirs(out_dir, exist_ok=True)
         with open(os.path.join(out_dir, "parity_100_steps.jsonl"), "a") as f:
@@ -642,6 +644,35 @@ def test_full_size_properties_without_the_oracle():
     # the weights did not move
     assert all(np.array_equal(v, w[k]) for k, v in net.tensors(0).items())
     net.close()
+
+
+@pytest.mark.parametrize("option,value", [("ft_two_lists_min", 0), ("ft_once", 0), ("ft_bwd_wide", 0)])
+def test_kernel_forms_chosen_by_size_give_the_same_numbers(option, value):
+    """The tiled kernels come in forms the library picks by launch size (one or two list buffers per warp in the
+    forward, loads with or without L1 allocation, one or two backward CTAs per SM): forcing the other form must
+    leave the forward outputs bit-identical and the step within the noise of the reduction order."""
+    from bullet_b200.net import featurise
+
+    c = config(3)
+    n = 4096
+    desc = dataclasses.replace(c.desc, max_batch=n)
+    batch = featurise(c.game, synth.records(c.game, n, seed=17), desc)
+    w = rich_weights(desc, seed=9)
+    results = []
+    for forced in (False, True):
+        net = make_net(desc, 0, w)
+        if forced:
+            net.set_option(option, value)
+        net.upload(0, *batch)
+        out = net.forward(0, n)
+        net.step(0, 1e-3, 1.0 / n)
+        results.append((out, net.loss(), net.tensors(0)))
+        net.close()
+    (out_a, loss_a, w_a), (out_b, loss_b, w_b) = results
+    assert np.array_equal(out_a, out_b)
+    assert abs(loss_a - loss_b) <= 1e-6 * abs(loss_a)
+    for k in w_a:
+        assert rel2(w_b[k], w_a[k]) <= 1e-6, k
 
 
 @pytest.mark.parametrize("ci", [0, 2, 3])
