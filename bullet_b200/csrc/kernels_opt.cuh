@@ -188,12 +188,13 @@ __global__ void __launch_bounds__(128, 8) adamw_exchange_kernel(const __grid_con
 
 // ---------------------------------------------------------------------------------------------
 // The same exchange with every operand moved by bulk asynchronous copies (cp.async.bulk, the TMA engine
-// without a tensor map) instead of per-thread loads and stores.  Timed alone on two GPUs the per-thread
-// kernel needs 0.186 ms for what a local update of the same share does in 0.078 ms: a thread's loads wait
-// two to three microseconds for peer memory, its stores follow behind them, and what an SM can keep in flight
-// through registers bounds the rate (with a quarter of the CTAs the kernel takes three times as long).  Bulk
-// copies cost no registers and no load slots: everything a tile needs is under way several tiles ahead, and
-// the stores leave asynchronously as well.
+// without a tensor map) instead of per-thread loads and stores: no registers and no load slots are held
+// while a tile is under way, everything a tile needs is requested several tiles ahead, and the stores leave
+// asynchronously as well.  Measured, it is as fast as the per-thread kernel and no faster (alone on eight
+// GPUs 0.293 against 0.300 ms, on two 0.184 against 0.189 ms): the exchange is bound by the links, which per
+// direction carry this rank's own transfers plus its peers' (pulled gradients in and pushed weights out, the
+// replies to the peers' pulls out and their pushed weights in), at 87 % of the rate of a peer copy.  Off by
+// default (option "exchange_bulk").
 // One CTA per SM; the rank's share is cut into tiles of kBulkTile float4s, one per thread.  Per tile and
 // stage thread 0 arms the stage's mbarrier with the byte count and issues one bulk load per rank (that
 // rank's gradients of the tile, peer memory -> this CTA's shared memory) and three for the local p, m and v;
