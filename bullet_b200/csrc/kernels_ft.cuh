@@ -644,7 +644,7 @@ __host__ __device__ inline int ft_bwd_unit_at(long long at, const int* block_beg
 // numbering, so that all CTAs move through the blocks together, and announces a block it has left after
 // the staging phase of its next unit, when that block's reductions have had time to land (the fence
 // that must precede the announcement then finds little to wait for).
-template <bool PAIRWISE, int THREADS, bool SIGNAL, int DEPTH = 4>
+template <bool PAIRWISE, int THREADS, bool SIGNAL>
 __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -716,10 +716,10 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
         __syncthreads();
         // stage this chunk's gradients at the feature-transformer pre-activation
-        for (int pl0 = warp; pl0 < cn; pl0 += DEPTH * NW) {
-            float q0[DEPTH], q1[DEPTH], q2[DEPTH];
+        for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
+            float q0[4], q1[4], q2[4];
 #pragma unroll
-            for (int k = 0; k < DEPTH; k++) {
+            for (int k = 0; k < 4; k++) {
                 const int pl = pl0 + k * NW;
                 q0[k] = q1[k] = q2[k] = 0.f;
                 if (pl < cn) {
@@ -743,7 +743,7 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
                 }
             }
 #pragma unroll
-            for (int k = 0; k < DEPTH; k++) {
+            for (int k = 0; k < 4; k++) {
                 const int pl = pl0 + k * NW;
                 if (pl < cn) {
                     float ga = q0[k], gb = q1[k];

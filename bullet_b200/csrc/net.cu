@@ -132,7 +132,6 @@ struct b200_net {
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
     int exchange_bulk = 0;  // the peer exchange moves gradients and weights with bulk asynchronous copies (measured no faster)
     int two_lists_min = 65536;  // positions per launch from which the forward keeps two list buffers per warp
-    int bwd_stage_depth = 4;  // pairs whose loads a warp of the 1024-thread backward keeps in flight while staging
     int ft_once = 1;       // bit 0: the tiled kernels read table rows and activations with loads that claim no L1 line
     int wide_chunk = 0;    // the larger chunk of the 1024-thread backward where it fits into shared memory, else the standard one
     // Pairs per chunk for a batch of n positions.  The larger chunk saves list copies, barriers and reductions,
@@ -320,10 +319,6 @@ int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArg
         // fence it ends with makes every CTA wait for its reductions to land (measured: +18 %)
         if (wide && t.sig.done_count)
             b200::ft_backward_tiled_kernel<PW, 1024, true><<<grid, 1024, smem, net->stream>>>(a, t);
-        else if (wide && net->bwd_stage_depth == 8)
-            b200::ft_backward_tiled_kernel<PW, 1024, false, 8><<<grid, 1024, smem, net->stream>>>(a, t);
-        else if (wide && net->bwd_stage_depth == 5)
-            b200::ft_backward_tiled_kernel<PW, 1024, false, 5><<<grid, 1024, smem, net->stream>>>(a, t);
         else if (wide)
             b200::ft_backward_tiled_kernel<PW, 1024, false><<<grid, 1024, smem, net->stream>>>(a, t);
         else if (t.sig.done_count)
@@ -656,8 +651,6 @@ int preload_kernels(b200_net* net) {
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, true>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, false>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, false>);
-    ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, false, 8>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, false, 8>);
-    ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, false, 5>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, false, 5>);
     ok = ok && load_kernel(b200::ft_prepare_kernel) && load_kernel(b200::ft_csr_kernel);
     ok = ok && load_kernel(b200::factoriser_merge_kernel) && load_kernel(b200::factoriser_grad_kernel);
     ok = ok && load_kernel(b200::adamw_flat_kernel) && load_kernel(b200::lookahead_kernel);
@@ -854,10 +847,6 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, false, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
-        cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, false, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
@@ -972,10 +961,6 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
     }
     if (!strcmp(key, "ft_two_lists_min")) {
         net->two_lists_min = (int)value;
-        return 0;
-    }
-    if (!strcmp(key, "ft_bwd_stage_depth")) {
-        net->bwd_stage_depth = (int)value;
         return 0;
     }
     if (!strcmp(key, "ft_once")) {
