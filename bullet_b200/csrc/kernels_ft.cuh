@@ -508,8 +508,9 @@ __host__ __device__ inline int ft_bwd_chunk_large(int nnz) { return 640 / (nnz <
 // entries per chunk: every slot of every pair plus up to seven padding entries per row (lists start on 16 bytes)
 __host__ __device__ inline int ft_bwd_ent_cap(int R, int nnz, int cp) { return (cp * nnz + 8 * R + 7) & ~7; }
 __host__ __device__ inline int ft_bwd_start_cap(int R) { return (R + 1 + 3) & ~3; }
-__host__ __device__ inline size_t ft_bwd_smem(int R, int nnz, int cp) {
-    return (size_t)(cp + 1) * kTileRowBytes + (size_t)ft_bwd_ent_cap(R, nnz, cp) * 2 + (size_t)ft_bwd_start_cap(R) * 4 + (size_t)cp * 4;
+__host__ __device__ inline size_t ft_bwd_smem(int R, int nnz, int cp, int nslabs) {
+    return (size_t)(cp + 1) * kTileRowBytes + (size_t)ft_bwd_ent_cap(R, nnz, cp) * 2 + (size_t)ft_bwd_start_cap(R) * 4 + (size_t)cp * 4 +
+           (size_t)nslabs * kTileRowBytes;  // staged lines, row lists, their starts, pair ids, bias-gradient sums per slab
 }
 __host__ __device__ inline size_t ft_csr_smem(int R, int nnz, int cp) {
     return (size_t)ft_bwd_ent_cap(R, nnz, cp) * 2 + (size_t)(2 * (R + 2) + 32 + cp) * 4;
@@ -606,8 +607,10 @@ static __global__ void __launch_bounds__(kCsrThreads) ft_csr_kernel(FtArgs a, Ti
 }
 
 // The backward's work line: block b contributes, per column slab, its pairs plus a fixed amount per chunk
-// (the list copy and the one reduction per row cost about as much as this many pairs).  A unit is one
-// (block, slab, chunk); units are numbered block by block, slab by slab, chunk by chunk.
+// (the one reduction per row costs about as much as this many pairs).  A unit is one (block, chunk, slab);
+// units are numbered block by block, chunk by chunk, and slab by slab INSIDE a chunk: a CTA that takes
+// consecutive units keeps the chunk's row lists (which do not depend on the slab) in shared memory for all
+// slabs, and reads neighbouring 128- or 256-byte pieces of the same activation rows from one unit to the next.
 constexpr int kChunkFixed = 96;
 __host__ __device__ inline long long ft_bwd_block_weight(int pairs, int chunks) { return pairs + (long long)kChunkFixed * chunks; }
 __host__ __device__ inline long long ft_bwd_line(const int* block_begin, const int* chunk_begin, int first_block, int last_block, int nslabs) {
@@ -625,11 +628,8 @@ __host__ __device__ inline int ft_bwd_unit_at(long long at, const int* block_beg
         const int nch = chunk_begin[b + 1] - chunk_begin[b];
         const long long wb = ft_bwd_block_weight(block_begin[b + 1] - block_begin[b], nch);
         if (nch > 0 && at < base + nslabs * wb) {
-            const long long local = at - base, within = local % wb;
-            const int slab = (int)(local / wb);
-            const int pairs = block_begin[b + 1] - block_begin[b];
-            const long long j = within / ((pairs + nch - 1) / nch + kChunkFixed);  // a block's chunks are of equal size
-            return units + slab * nch + (int)(j < nch - 1 ? j : nch - 1);
+            const long long j = (at - base) * nch / wb;  // a block's chunks are of equal size, so its units weigh the same
+            return units + (int)(j < (long long)nslabs * nch - 1 ? j : (long long)nslabs * nch - 1);
         }
         base += nslabs * wb;
         units += nslabs * nch;
@@ -655,32 +655,17 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
     uint16_t* ent = reinterpret_cast<uint16_t*>(smem_raw + (size_t)(CP + 1) * kTileRowBytes);  // lists of the chunk
     int* start = reinterpret_cast<int*>(ent + t.ent_cap);                                     // [R + 1]
     int* pairs_s = start + t.start_cap;                                                       // [CP] pair ids of the chunk
+    float* bias_s = reinterpret_cast<float*>(pairs_s + CP);                                   // [nslabs][64] bias-gradient sums
     if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line that list padding points at
+    for (int i = threadIdx.x; i < t.nslabs * kTileCols; i += kBwdThreads) bias_s[i] = 0.f;
 
     const long long line = ft_bwd_line(t.block_begin, t.chunk_begin, t.first_block, t.last_block, t.nslabs);
     const int u_begin = ft_bwd_unit_at(line * blockIdx.x / gridDim.x, t.block_begin, t.chunk_begin, t.first_block, t.last_block, t.nslabs);
     const int u_end = ft_bwd_unit_at(line * (blockIdx.x + 1) / gridDim.x, t.block_begin, t.chunk_begin, t.first_block, t.last_block, t.nslabs);
 
-    // sums of the bias gradient live in registers while the slab stays the same
-    float bsum_a = 0.f, bsum_b = 0.f;
-    int col_a = 0, col_b = 0, slab = -1, block = -1;
-    auto flush_bias = [&]() {  // every pair's gradient once, summed over the warps (all threads call this)
-        float* red = reinterpret_cast<float*>(smem_raw);
-        red[warp * kTileCols + lane] = bsum_a;
-        red[warp * kTileCols + 32 + lane] = bsum_b;
-        __syncthreads();
-        if (warp == 0) {
-            float sa = 0.f, sb = 0.f;
-            for (int k = 0; k < NW; k++) {
-                sa += red[k * kTileCols + lane];
-                sb += red[k * kTileCols + 32 + lane];
-            }
-            if (sa != 0.f) atomicAdd(a.g_bias + col_a, sa);
-            if (sb != 0.f) atomicAdd(a.g_bias + col_b, sb);
-        }
-        bsum_a = bsum_b = 0.f;
-    };
-
+    // Bias gradient: a warp adds the sums of the pairs it staged to the slab's line of bias_s (shared-memory
+    // atomics); the CTA adds the lines to global memory once, at the end.
+    int col_a = 0, col_b = 0, slab = -1, block = -1, ch_loaded = -1;
     int scan_block = t.first_block, scan_base = 0;  // units before scan_block
     int all_units = 0, left_block = -1;             // SIGNAL: a block this CTA has left and not yet announced
     if (SIGNAL) all_units = t.nslabs * (t.chunk_begin[t.last_block] - t.chunk_begin[t.first_block]);
@@ -691,9 +676,8 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
             scan_block++;
             nch = t.chunk_begin[scan_block + 1] - t.chunk_begin[scan_block];
         }
-        const int local = u - scan_base, new_slab = local / nch, ch = t.chunk_begin[scan_block] + local % nch;
+        const int local = u - scan_base, new_slab = local % t.nslabs, ch = t.chunk_begin[scan_block] + local / t.nslabs;
         if (new_slab != slab || scan_block != block) {
-            if (slab >= 0 && new_slab != slab) flush_bias();
             if (SIGNAL && block >= 0 && scan_block != block) {
                 if (left_block >= 0) bucket_signal(t.sig, left_block);  // (only if a whole block went by within one unit)
                 left_block = block;
@@ -705,16 +689,19 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         }
         const int4 chunk = t.chunks[ch];
         const int c0 = chunk.y, cn = chunk.z;
-        // the chunk's row lists: asynchronous copy into shared memory, overlapped with the staging below
-        {
+        // the chunk's row lists, unless the unit before left them here: asynchronous copy into shared memory,
+        // overlapped with the staging below
+        if (ch != ch_loaded) {
             const int* start_in = t.csr_start + (size_t)ch * t.start_cap;
             for (int i = threadIdx.x; i < t.start_cap / 4; i += kBwdThreads) cp_async16(start + 4 * i, start_in + 4 * i);
             const int total = __ldg(start_in + R);
             const uint16_t* ent_in = t.csr_ent + (size_t)ch * t.ent_cap;
             for (int i = threadIdx.x; i < (total + 7) / 8; i += kBwdThreads) cp_async16(ent + 8 * i, ent_in + 8 * i);
+            for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
+            ch_loaded = ch;
         }
-        for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
         __syncthreads();
+        float bsum_a = 0.f, bsum_b = 0.f;
         // stage this chunk's gradients at the feature-transformer pre-activation
         for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
             float q0[4], q1[4], q2[4];
@@ -764,6 +751,8 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
                 }
             }
         }
+        if (bsum_a != 0.f) atomicAdd(bias_s + slab * kTileCols + lane, bsum_a);
+        if (bsum_b != 0.f) atomicAdd(bias_s + slab * kTileCols + 32 + lane, bsum_b);
         cp_async_wait_all();
         __syncthreads();
         if (SIGNAL && left_block >= 0) {
@@ -793,7 +782,12 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         }
         __syncthreads();
     }
-    if (slab >= 0) flush_bias();
+    // entry [slab][j] holds, for j < 32, lane j's first column of that slab, for j >= 32 lane (j - 32)'s second
+    for (int i = threadIdx.x; i < t.nslabs * kTileCols; i += kBwdThreads) {
+        const float v = bias_s[i];
+        const int sl = i / kTileCols, j = i % kTileCols;
+        if (v != 0.f) atomicAdd(a.g_bias + (j < 32 ? tile_col_a<PAIRWISE>(sl, j, a.H) : tile_col_b<PAIRWISE>(sl, j - 32, a.H)), v);
+    }
     if (SIGNAL && left_block >= 0) bucket_signal(t.sig, left_block);
     if (SIGNAL && block >= 0) bucket_signal(t.sig, block);
 }

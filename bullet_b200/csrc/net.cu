@@ -313,7 +313,7 @@ int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs
 template <bool PW>
 int launch_ft_backward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
-        const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len);
+        const size_t smem = b200::ft_bwd_smem(t.block_rows, a.nnz, t.chunk_len, t.nslabs);
         const bool wide = t.chunk_len > b200::ft_bwd_chunk(a.nnz, false);
 // data-parallel runs that announce finished row blocks take an instantiation of their own: the
         // fence it ends with makes every CTA wait for its reductions to land (measured: +18 %)
@@ -745,10 +745,10 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
                     b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2) <= kMaxSmem &&
-                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz, b200::ft_bwd_chunk(d.nnz, true)) <= kMaxSmem;
+                    b200::ft_bwd_smem(d.ft_block_rows, d.nnz, b200::ft_bwd_chunk(d.nnz, true), d.ft_out / b200::kTileCols) <= kMaxSmem;
     if (net->tiled_ok) {
         const int larger = b200::ft_bwd_chunk_large(d.nnz);
-        net->wide_chunk = b200::ft_bwd_smem(d.ft_block_rows, d.nnz, larger) <= kMaxSmem ? larger : b200::ft_bwd_chunk(d.nnz, true);
+        net->wide_chunk = b200::ft_bwd_smem(d.ft_block_rows, d.nnz, larger, d.ft_out / b200::kTileCols) <= kMaxSmem ? larger : b200::ft_bwd_chunk(d.nnz, true);
     }
     net->nblocks = net->tiled_ok ? d.n_inputs / d.ft_block_rows : 1;
     net->nslabs = d.ft_out / b200::kTileCols;
@@ -837,7 +837,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
     if (net->tiled_ok) {
         const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2);
         const int wide = net->wide_chunk, narrow = b200::ft_bwd_chunk(d.nnz, false);
-        const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow);
+        const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide, net->nslabs), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow, net->nslabs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);

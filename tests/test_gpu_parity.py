@@ -731,8 +731,8 @@ def test_device_preparation_fills_the_slot_exactly_as_the_host_path(ci):
         b.step(1, 1e-3, 1.0 / n)
         assert abs(a.loss() - b.loss()) <= 1e-6 * abs(a.loss())
         wa, wb = a.tensors(0), b.tensors(0)
-        for k in wa:
-            assert rel2(wb[k], wa[k]) <= 1e-6, (n, k)
+        for k in wa:  # identical inputs: what is left is the order of the floating-point reductions of two runs
+            assert rel2(wb[k], wa[k]) <= 1e-5, (n, k)
         a.close()
         b.close()
     if ci == 0:   # a record with more pieces than slots is refused, as on the host path
