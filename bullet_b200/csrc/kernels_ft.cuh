@@ -699,8 +699,8 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
             for (int i = threadIdx.x; i < (total + 7) / 8; i += kBwdThreads) cp_async16(ent + 8 * i, ent_in + 8 * i);
             for (int k = threadIdx.x; k < cn; k += kBwdThreads) pairs_s[k] = t.pair_order ? t.pair_order[c0 + k] : c0 + k;
             ch_loaded = ch;
+            __syncthreads();  // the pair ids (and, on the first unit, the zeroed lines) are in place
         }
-        __syncthreads();
         float bsum_a = 0.f, bsum_b = 0.f;
         // stage this chunk's gradients at the feature-transformer pre-activation
         for (int pl0 = warp; pl0 < cn; pl0 += 4 * NW) {
