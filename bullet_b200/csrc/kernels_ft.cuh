@@ -282,6 +282,8 @@ __device__ __forceinline__ float ld_once(const float* p) {
     return v;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
@@ -758,6 +760,23 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         if (SIGNAL && left_block >= 0) {
             bucket_signal(t.sig, left_block);
             left_block = -1;
+        }
+        // The next unit of a CTA that walks consecutive units is the same chunk's next slab: ask L2 for the lines
+        // its staging will read (the neighbours of the ones just staged) now, so that they arrive during the walk.
+        if (!SIGNAL && t.once && new_slab + 1 < t.nslabs && u + 1 < u_end && (int)threadIdx.x < cn) {
+            const int pair = pairs_s[threadIdx.x];
+            if (PAIRWISE) {
+                const float* pu = a.u + (size_t)pair * a.H + (slab + 1) * 32;
+                prefetch_l2(pu);
+                prefetch_l2(pu + a.H / 2);
+                prefetch_l2(a.dx + (size_t)pair * (a.H / 2) + (slab + 1) * 32);
+            } else {
+                const size_t at = (size_t)pair * a.H + (slab + 1) * 64;
+                prefetch_l2(a.dx + at);
+                prefetch_l2(a.dx + at + 32);
+                prefetch_l2(a.x + at);
+                prefetch_l2(a.x + at + 32);
+            }
         }
         // accumulate: each warp walks the lists of the rows it owns, four entries per 8-byte load
         const unsigned char* gl = smem_raw + lane * 8;
