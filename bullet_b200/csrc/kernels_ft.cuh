@@ -72,6 +72,7 @@ struct TileArgs {
     int* csr_start;                // [nchunks][start_cap] per row (start / 8) << 16 | length; [R] = entries in all
     int ent_cap, start_cap;
     int once;                      // table rows and activations through loads that claim no L1 line
+    int grab;                      // rows a warp of the backward takes from the row counter at a time
     int chunk_len;  // CP: most pairs per chunk
     // backward only, data-parallel runs: the last CTA of every row block tells all ranks that the block's
     // gradient is complete (done_count null: nobody is told)
@@ -658,6 +659,7 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
     int* start = reinterpret_cast<int*>(ent + t.ent_cap);                                     // [R + 1]
     int* pairs_s = start + t.start_cap;                                                       // [CP] pair ids of the chunk
     float* bias_s = reinterpret_cast<float*>(pairs_s + CP);                                   // [nslabs][64] bias-gradient sums
+    __shared__ int next_rows;  // the walk's row counter
     if (threadIdx.x < 32) g_s[CP * 32 + threadIdx.x] = 0;  // the all-zero line that list padding points at
     for (int i = threadIdx.x; i < t.nslabs * kTileCols; i += kBwdThreads) bias_s[i] = 0.f;
 
@@ -753,6 +755,7 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
                 }
             }
         }
+        if (threadIdx.x == 0) next_rows = 0;
         if (bsum_a != 0.f) atomicAdd(bias_s + slab * kTileCols + lane, bsum_a);
         if (bsum_b != 0.f) atomicAdd(bias_s + slab * kTileCols + 32 + lane, bsum_b);
         cp_async_wait_all();
@@ -782,7 +785,13 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
         const unsigned char* gl = smem_raw + lane * 8;
         // the two table columns this lane sums (see the staging above for the pairwise layout of a line)
         const int col_w = !PAIRWISE ? col_a : lane < 16 ? slab * 32 + 2 * lane : a.H / 2 + slab * 32 + 2 * (lane - 16);
-        for (int row = warp; row < R; row += NW) {
+        // rows are handed out a few at a time to whichever warp is free: list lengths differ a lot from row to row
+        for (;;) {
+            int row2 = 0;
+            if (lane == 0) row2 = atomicAdd(&next_rows, t.grab);
+            row2 = __shfl_sync(0xffffffffu, row2, 0);
+            if (row2 >= R) break;
+            for (int row = row2; row < min(R, row2 + t.grab); row++) {
             const unsigned sl = (unsigned)start[row];
             const int len = (int)(sl & 0xffffu);
             const uint2* lp = reinterpret_cast<const uint2*>(ent + (sl >> 16) * 8);
@@ -798,6 +807,7 @@ __global__ void __launch_bounds__(THREADS, 2048 / (2 * THREADS)) ft_backward_til
             float* dst = a.g_table + (size_t)(block * R + row) * a.H + col_w;
             const float ga = lo2(acc), gb = hi2(acc);
             if (ga != 0.f || gb != 0.f) atomicAdd(reinterpret_cast<float2*>(dst), make_float2(ga, gb));
+            }
         }
         __syncthreads();
     }

@@ -132,6 +132,7 @@ struct b200_net {
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
     int exchange_bulk = 0;  // the peer exchange moves gradients and weights with bulk asynchronous copies (measured no faster)
     int two_lists_min = 65536;  // positions per launch from which the forward keeps two list buffers per warp
+    int bwd_grab = 0;  // rows a warp of the tiled backward takes from the row counter at a time (0: chosen by block size)
     int ft_once = 1;       // bit 0: the tiled kernels read table rows and activations with loads that claim no L1 line
     int wide_chunk = 0;    // the larger chunk of the 1024-thread backward where it fits into shared memory, else the standard one
     // Pairs per chunk for a batch of n positions.  The larger chunk saves list copies, barriers and reductions,
@@ -428,6 +429,9 @@ b200::TileArgs tile_args(b200_net* net, const Slot& s, bool backward) {
     t.csr_start = s.csr_start;
     t.chunk_len = s.chunk_len;
     t.once = net->ft_once;
+    // rows per grab: measured best at eight for 768-row blocks (runs of neighbouring rows per warp, and still four
+    // grabs per warp and unit to even out the list lengths), two to four for the 147-row ataxx table
+    t.grab = net->bwd_grab > 0 ? net->bwd_grab : std::max(2, std::min(8, net->d.ft_block_rows / 96));
     t.ent_cap = b200::ft_bwd_ent_cap(net->d.ft_block_rows, net->d.nnz, s.chunk_len);
     t.start_cap = b200::ft_bwd_start_cap(net->d.ft_block_rows);
     if (backward && net->sig_on) {
@@ -961,6 +965,11 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
     }
     if (!strcmp(key, "ft_two_lists_min")) {
         net->two_lists_min = (int)value;
+        return 0;
+    }
+    if (!strcmp(key, "ft_bwd_grab")) {
+        if (value < 0 || value > 64) return b200::fail(B200_ERR_ARG, "ft_bwd_grab must be in [0, 64]");
+        net->bwd_grab = (int)value;
         return 0;
     }
     if (!strcmp(key, "ft_once")) {
