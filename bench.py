@@ -55,11 +55,12 @@ def workload():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two tiled feature-transformer kernels of the
 # 2048-wide pairwise network, as a two-term model through two ncu captures (16384 and 65536 positions per GPU:
-# forward 495.9 and 1817.5 MB, backward 569.0 and 1824.6 MB): what does not grow with the batch (the table, or
-# the gradient's write-back) plus a term per position (the activations written or read: 24.6 KB).
+# forward 495.9 and 1817.5 MB, backward 884.6 and 2987.8 MB): what does not grow with the batch (the table, or
+# the gradient's write-back) plus a term per position (the activations written or read, 24.6 KB, and for the backward
+# the table-gradient lines that L2 writes back and reads again between a row's reductions).
 FT_DRAM_MODEL = {  # kernel: (bytes per launch that do not grow with the batch, bytes per position)
     "ft_forward": (55_400_000, 26_888),
-    "ft_backward": (150_500_000, 25_545),
+    "ft_backward": (183_500_000, 42_790),
 }
 CPU_REPEATS = 10  # timed repeats of the CPU oracle at most, in the reference arm and in the in-line baseline alike
 N_DISTINCT = 3  # distinct host batches cycled through (each far larger than L2 once expanded on device)
