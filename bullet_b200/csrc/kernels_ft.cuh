@@ -333,28 +333,21 @@ __device__ __forceinline__ f32x2 line_at(const unsigned char* mine, uint32_t ind
 }
 
 // Forward.  One CTA of 1024 threads per SM; dynamic shared memory = (R+1) tile rows, the extra row all
-// zero, then per warp one or two copies of a prepared list (and 16 bytes that a read-ahead may touch).
-// A CTA walks its piece of the work line segment by segment; a segment is a run of pairs of one
-// (block, slab), whose tile the CTA loads first.  Each warp serves one (position, perspective) at a time:
-// the pair's prepared list arrives in the warp's own shared memory by an asynchronous copy, so the walk
-// itself reads no global memory; it takes four row indices per (warp-uniform) 8-byte shared-memory load,
-// and every lane adds its column pair with one 64-bit shared-memory load and one packed add per row, in
+// zero, then per warp one prepared list (and 16 bytes that a read-ahead may touch).  A CTA walks its piece of
+// the work line segment by segment; a segment is a run of pairs of one (block, slab), whose tile the CTA loads
+// first.  Each warp serves one (position, perspective) at a time.  The pair's prepared list reaches the warp
+// one pair ahead: every lane loads one 32-bit word of it (two row indices) into a register while the pair
+// before is still being walked, and stores it into the warp's list buffer afterwards, so the walk itself
+// reads no global memory and the buffer costs one shared-memory wavefront per pair (a cp.async of the same 64
+// bytes by four lanes cost seven).  The walk takes four row indices per (warp-uniform) 8-byte shared-memory
+// load, and every lane adds its column pair with one 64-bit shared-memory load and one packed add per row, in
 // slot order — the same order and arithmetic as the interpreter (adding the zero row changes nothing).
-// TWO_LISTS: the copy of the next pair's list is issued before the walk of this one (into the warp's
-// other buffer) instead of behind it.  That hides the copy completely, but with 768-row tiles the second
-// buffer pushes the CTA past 196 KB of shared memory, the SM then keeps only 28 KB instead of 60 KB as
-// L1, and the tile fill (whose loads pass through L1) slows down: measured faster from about 64 K
-// positions per launch upwards, slower below, so the host chooses by launch size.
 constexpr int kFwdThreads = 1024;
-inline bool ft_fwd_two_lists(int n_positions) { return n_positions >= 65536; }
-__host__ __device__ inline size_t ft_fwd_smem(int R, int list_len, int copies) {
-    return (size_t)(R + 1) * kTileRowBytes + (size_t)(kFwdThreads / 32) * copies * list_len * 2 + 16;
+__host__ __device__ inline size_t ft_fwd_smem(int R, int list_len) {
+    return (size_t)(R + 1) * kTileRowBytes + (size_t)(kFwdThreads / 32) * list_len * 2 + 16;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <bool PAIRWISE, bool TWO_LISTS>
+template <bool PAIRWISE>
 __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs a, TileArgs t) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -421,54 +414,40 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
         const f32x2 bias = pack2(a.bias[col_a], a.bias[col_b]);
         float* x_out = a.x + col_a;  // with pairwise col_a is also the product's column within the perspective
         __syncthreads();
-        // pair id and list length are fetched one pair ahead into registers, the list into the warp's list buffer
+        // pair id, list length and the list itself are fetched one pair ahead into registers: every lane holds one
+        // 32-bit word (two row indices) of the next pair's list and puts it into the warp's list buffer when the walk
+        // of the current pair is over, so the walk reads its indices from shared memory and never waits for global memory
         const int seg_end = t.block_begin[block] + last;
-        const int list_bytes = t.list_len * 2;
-        unsigned char* ring = smem_raw + (size_t)(R + 1) * kTileRowBytes + (size_t)warp * (TWO_LISTS ? 2 : 1) * list_bytes;
-        const unsigned char* lists_b = reinterpret_cast<const unsigned char*>(t.lists);
+        const int list_words = t.list_len / 2;
+        uint32_t* ring = reinterpret_cast<uint32_t*>(smem_raw + (size_t)(R + 1) * kTileRowBytes) + warp * list_words;
+        const uint32_t* lists_w = reinterpret_cast<const uint32_t*>(t.lists);
         int i = t.block_begin[block] + first + warp;
-        int pair = 0, cnt = 0, buf = 0;
+        int pair = 0, cnt = 0;
+        uint32_t word = 0;
         if (i < seg_end) {
             pair = t.pair_order ? t.pair_order[i] : i;
             cnt = t.list_count[i];
-            if (lane * 16 < list_bytes) cp_async16(ring + lane * 16, lists_b + (size_t)i * list_bytes + lane * 16);
+            if (lane < list_words) word = __ldg(lists_w + (size_t)i * list_words + lane);
         }
-        cp_async_commit();
-        for (; i < seg_end; i += NW, buf ^= (TWO_LISTS ? 1 : 0)) {
+        for (; i < seg_end; i += NW) {
             int pair_next = 0, cnt_next = 0;
-            if (TWO_LISTS) {
-                __syncwarp();  // every lane has finished with the buffer that the next copy overwrites
-                if (i + NW < seg_end) {
-                    pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
-                    cnt_next = t.list_count[i + NW];
-                    if (lane * 16 < list_bytes)
-                        cp_async16(ring + (buf ^ 1) * list_bytes + lane * 16, lists_b + (size_t)(i + NW) * list_bytes + lane * 16);
-                }
-                cp_async_commit();
-                cp_async_wait<1>();  // all but the copy just issued have landed: this pair's list is in place
-            } else {
-                if (i + NW < seg_end) {
-                    pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
-                    cnt_next = t.list_count[i + NW];
-                }
-                cp_async_wait<0>();
+            __syncwarp();  // every lane has finished with the list of the pair before
+            if (lane < list_words) ring[lane] = word;
+            if (i + NW < seg_end) {
+                pair_next = t.pair_order ? t.pair_order[i + NW] : i + NW;
+                cnt_next = t.list_count[i + NW];
+                if (lane < list_words) word = __ldg(lists_w + (size_t)(i + NW) * list_words + lane);
             }
             __syncwarp();
             f32x2 acc = 0;  // (+0.0f, +0.0f)
-            const uint2* list = reinterpret_cast<const uint2*>(ring + buf * list_bytes);
+            const uint2* list = reinterpret_cast<const uint2*>(ring);
             uint2 g = list[0];
             for (int k = 0; k < cnt; k += 4) {
-                const uint2 g_ahead = list[(k >> 2) + 1];  // (past the last group: another buffer or the spare 16 bytes, unused)
+                const uint2 g_ahead = list[(k >> 2) + 1];  // (past the last group: the next warp's buffer or the spare 16 bytes, unused)
                 const f32x2 v0 = line_at(mine, g.x & 0xffffu), v1 = line_at(mine, g.x >> 16);
                 const f32x2 v2 = line_at(mine, g.y & 0xffffu), v3 = line_at(mine, g.y >> 16);
                 acc = add2(add2(add2(add2(acc, v0), v1), v2), v3);
                 g = g_ahead;
-            }
-            if (!TWO_LISTS) {  // the one buffer is free again: fetch the next pair's list behind the epilogue
-                __syncwarp();
-                if (i + NW < seg_end && lane * 16 < list_bytes)
-                    cp_async16(ring + lane * 16, lists_b + (size_t)(i + NW) * list_bytes + lane * 16);
-                cp_async_commit();
             }
             acc = add2(acc, bias);
             if (PAIRWISE) {

@@ -131,7 +131,6 @@ struct b200_net {
     int ft_fwd_mode = B200_FT_AUTO, ft_bwd_mode = B200_FT_AUTO;
     bool bwd_wide = true;  // shape of the tiled backward (see ft_bwd_chunk)
     int exchange_bulk = 0;  // the peer exchange moves gradients and weights with bulk asynchronous copies (measured no faster)
-    int two_lists_min = 65536;  // positions per launch from which the forward keeps two list buffers per warp
     int bwd_grab = 0;  // rows a warp of the tiled backward takes from the row counter at a time (0: chosen by block size)
     int ft_once = 1;       // bit 0: the tiled kernels read table rows and activations with loads that claim no L1 line
     int wide_chunk = 0;    // the larger chunk of the 1024-thread backward where it fits into shared memory, else the standard one
@@ -298,10 +297,7 @@ void slot_layout(const b200_net* net, Slot& s, int n) {
 template <bool PW>
 int launch_ft_forward(b200_net* net, const b200::FtArgs& a, const b200::TileArgs& t, bool tiled, int grid) {
     if (tiled) {
-        if (a.n >= net->two_lists_min)
-            b200::ft_forward_tiled_kernel<PW, true><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len, 2), net->stream>>>(a, t);
-        else
-            b200::ft_forward_tiled_kernel<PW, false><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len, 1), net->stream>>>(a, t);
+        b200::ft_forward_tiled_kernel<PW><<<grid, b200::kFwdThreads, b200::ft_fwd_smem(t.block_rows, t.list_len), net->stream>>>(a, t);
     } else {
         const int unit = PW ? a.H / 2 : a.H;
         dim3 grid((2 * a.n + 63) / 64, (unit + 127) / 128);
@@ -649,8 +645,7 @@ int preload_kernels(b200_net* net) {
     ok = ok && load_kernel(b200::dense_regroup_kernel) && load_kernel(b200::dense_small_grads_kernel);
     ok = ok && load_kernel(b200::ft_forward_gather_kernel<true>) && load_kernel(b200::ft_forward_gather_kernel<false>);
     ok = ok && load_kernel(b200::ft_backward_gather_kernel<true>) && load_kernel(b200::ft_backward_gather_kernel<false>);
-    ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true, true>) && load_kernel(b200::ft_forward_tiled_kernel<false, true>);
-    ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true, false>) && load_kernel(b200::ft_forward_tiled_kernel<false, false>);
+    ok = ok && load_kernel(b200::ft_forward_tiled_kernel<true>) && load_kernel(b200::ft_forward_tiled_kernel<false>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, true>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 512, true>) && load_kernel(b200::ft_backward_tiled_kernel<false, 512, true>);
     ok = ok && load_kernel(b200::ft_backward_tiled_kernel<true, 1024, false>) && load_kernel(b200::ft_backward_tiled_kernel<false, 1024, false>);
@@ -748,7 +743,7 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
 
     constexpr size_t kMaxSmem = 227 * 1024;
     net->tiled_ok = d.ft_block_rows > 0 && d.n_inputs % d.ft_block_rows == 0 && d.ft_out % b200::kTileCols == 0 &&
-                    b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2) <= kMaxSmem &&
+                    b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7) <= kMaxSmem &&
                     b200::ft_bwd_smem(d.ft_block_rows, d.nnz, b200::ft_bwd_chunk(d.nnz, true), d.ft_out / b200::kTileCols) <= kMaxSmem;
     if (net->tiled_ok) {
         const int larger = b200::ft_bwd_chunk_large(d.nnz);
@@ -839,13 +834,11 @@ int b200_net_create(int device, void* stream, const b200_net_desc* desc, b200_ne
         if (int rc2 = set_dense(d.dense_out[0])) return bail(rc2);
     }
     if (net->tiled_ok) {
-        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7, 2);
+        const int fs = (int)b200::ft_fwd_smem(d.ft_block_rows, (d.nnz + 7) & ~7);
         const int wide = net->wide_chunk, narrow = b200::ft_bwd_chunk(d.nnz, false);
         const int bs = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, wide, net->nslabs), bn = (int)b200::ft_bwd_smem(d.ft_block_rows, d.nnz, narrow, net->nslabs);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
-        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
+        cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<false, 1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bs);
         cudaFuncSetAttribute(b200::ft_backward_tiled_kernel<true, 512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bn);
@@ -961,10 +954,6 @@ int b200_net_set_option(b200_net* net, const char* key, int64_t value) {
     }
     if (!strcmp(key, "exchange_bulk")) {  // 0: the exchange kernel fetches peer gradients with per-thread loads
         net->exchange_bulk = (int)value;
-        return 0;
-    }
-    if (!strcmp(key, "ft_two_lists_min")) {
-        net->two_lists_min = (int)value;
         return 0;
     }
     if (!strcmp(key, "ft_bwd_grab")) {

@@ -112,7 +112,7 @@ int check_op(const b200_ft_op* op, const char* who) {
     if (op->pairwise && op->ft_act != B200_ACT_CRELU) return b200::fail(B200_ERR_UNSUPPORTED, "%s: pairwise needs CReLU", who);
     const int R = op->ft_block_rows;
     if (R < 1 || op->n_inputs % R || op->ft_out < 64 || op->ft_out % b200::kTileCols || op->n_inputs / R > kMaxBlocks ||
-        b200::ft_fwd_smem(R, list_len(op->nnz), 2) > 227 * 1024)
+        b200::ft_fwd_smem(R, list_len(op->nnz)) > 227 * 1024)
         return b200::fail(B200_ERR_UNSUPPORTED,
                           "%s: needs ft_block_rows > 0 dividing n_inputs (at most about 800 rows, at most %d blocks) "
                           "and ft_out a multiple of 64",
@@ -165,23 +165,18 @@ int run_op(int device, cudaStream_t stream, const b200_ft_op* op, int* scratch) 
     t.once = 1;
     b200::ft_prepare_kernel<<<(2 * n + 7) / 8, 256, 0, stream>>>(a, t);
     CK(cudaGetLastError());
-    const bool two = b200::ft_fwd_two_lists(n);
-    const size_t smem = b200::ft_fwd_smem(R, t.list_len, two ? 2 : 1);
+    const size_t smem = b200::ft_fwd_smem(R, t.list_len);
     // one CTA per SM, each taking an equal piece of the (block, slab, pair) work line
     int sms = 0;
     CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     const int ctas = (int)std::max<long long>(1, std::min<long long>(sms, (long long)2 * n * t.nslabs / 128));
-#define FORWARD(PW, TWO)                                                                                                       \
-    do {                                                                                                                       \
-        CK(cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<PW, TWO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        b200::ft_forward_tiled_kernel<PW, TWO><<<ctas, b200::kFwdThreads, smem, stream>>>(a, t);                                \
-    } while (0)
     if (op->pairwise) {
-        if (two) FORWARD(true, true); else FORWARD(true, false);
+        CK(cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        b200::ft_forward_tiled_kernel<true><<<ctas, b200::kFwdThreads, smem, stream>>>(a, t);
     } else {
-        if (two) FORWARD(false, true); else FORWARD(false, false);
+        CK(cudaFuncSetAttribute(b200::ft_forward_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        b200::ft_forward_tiled_kernel<false><<<ctas, b200::kFwdThreads, smem, stream>>>(a, t);
     }
-#undef FORWARD
     CK(cudaGetLastError());
     int host_status = 0;
     CK(cudaMemcpyAsync(&host_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));

@@ -100,7 +100,6 @@ int b200_net_destroy(b200_net* net);
  *   "ft_mode" / "ft_fwd_mode" / "ft_bwd_mode"  B200_FT_*; "ft_bwd_wide" 0 = two 512-thread backward CTAs per SM;
  *   "ft_once" 0 = table rows and activations through ordinary (L1-allocating) loads;
  *   "ft_bwd_grab" rows a warp of the tiled backward takes from the row counter at a time (0 = by block size);
- *   "ft_two_lists_min" positions per launch from which the forward keeps two list buffers per warp (65536);
  *   "exchange_bulk" 1 = the peer exchange moves gradients and weights with bulk asynchronous copies;
  *   "overlap_ctas", "overlap_mode", "exchange_ctas", "exchange_wait_ms", "exchange_step", "manual_grad_zero": see the
  *   data-parallel entry points below. */

@@ -646,11 +646,11 @@ def test_full_size_properties_without_the_oracle():
     net.close()
 
 
-@pytest.mark.parametrize("option,value", [("ft_two_lists_min", 0), ("ft_once", 0), ("ft_bwd_wide", 0)])
+@pytest.mark.parametrize("option,value", [("ft_once", 0), ("ft_bwd_wide", 0), ("ft_bwd_grab", 3)])
 def test_kernel_forms_chosen_by_size_give_the_same_numbers(option, value):
-    """The tiled kernels come in forms the library picks by launch size (one or two list buffers per warp in the
-    forward, loads with or without L1 allocation, one or two backward CTAs per SM): forcing the other form must
-    leave the forward outputs bit-identical and the step within the noise of the reduction order."""
+    """The tiled kernels come in forms the library picks for speed (loads with or without L1 allocation, one or two
+    backward CTAs per SM, how many rows a warp of the backward takes at a time): forcing another form must leave
+    the forward outputs bit-identical and the step within the noise of the reduction order."""
     from bullet_b200.net import featurise
 
     c = config(3)
