@@ -395,8 +395,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
                         lo = add4(lo, __ldg(reinterpret_cast<const float4*>(frow + c_lo)));  // (these gain from L1)
                         hi = add4(hi, __ldg(reinterpret_cast<const float4*>(frow + c_hi)));
                     }
-                    dst[0] = make_float4(lo.x, hi.x, lo.y, hi.y);
-                    dst[1] = make_float4(lo.z, hi.z, lo.w, hi.w);
+                    // (the work items of a row lie 32 bytes apart: the upper four of a row store their second half
+                    // first, so that the eight 16-byte stores of a quarter warp fall into eight different bank groups)
+                    const int h = q >> 2;
+                    const float4 first = make_float4(lo.x, hi.x, lo.y, hi.y), second = make_float4(lo.z, hi.z, lo.w, hi.w);
+                    dst[h] = h ? second : first;
+                    dst[h ^ 1] = h ? first : second;
                 } else {
                     const int c0 = slab * 64 + q * 8;
                     const float4* g = reinterpret_cast<const float4*>(src + (size_t)row * a.H + c0);
@@ -405,8 +409,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ft_forward_tiled_kernel(FtArgs
                         v0 = add4(v0, __ldg(reinterpret_cast<const float4*>(frow + c0)));
                         v1 = add4(v1, __ldg(reinterpret_cast<const float4*>(frow + c0 + 4)));
                     }
-                    dst[0] = v0;
-                    dst[1] = v1;
+                    const int h = q >> 2;
+                    dst[h] = h ? v1 : v0;
+                    dst[h ^ 1] = h ? v0 : v1;
                 }
             }
         }
